@@ -1,0 +1,194 @@
+/*
+ * lct_b200.h - C ABI of the B200 (sm_100a) BF16 lossless codec library.
+ *
+ * One entry point per kernel launch wrapper of the reference's
+ * LCT/kernels/dispatch.py (the layer its host pipelines call), plus the
+ * allocator launches of LCT/tensor_buffer.py.  Each declaration cites the
+ * reference interface it replaces.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless said otherwise; sizes are in
+ *     elements of the pointed-to type unless the name says bytes;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  All work is enqueued on it; no entry point synchronises,
+ *     allocates or frees device memory;
+ *   - return value: 0 on success, a positive cudaError_t if a launch failed,
+ *     or one of the negative LCT_E_* codes for a rejected argument.  Device
+ *     side conditions (arena exhausted, stale descriptor, ...) are reported
+ *     through the status words documented below, never by trapping;
+ *   - payload, side-byte, output and dense-operand buffers handed to the
+ *     vectorised kernels must be 16-byte aligned except where noted.
+ *
+ * Format recap (identical to the reference's):
+ *   BF16 bits v: exponent byte (v >> 7) & 0xFF, side byte (v & 0x7F) | ((v >> 8) & 0x80).
+ *   A tensor is cut into blocks of `block_symbols` elements = `steps` rows of
+ *   256 lanes.  Lane l at row n = block*steps + step holds logical element
+ *   n*256 + (l ^ (n & 254)).  Stream s = block*256 + l owns `fixed_words`
+ *   32-bit words, word w at encoded[w*streams + s], filled LSB first.
+ */
+#ifndef LCT_B200_H
+#define LCT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LCT_E_BAD_GEOMETRY (-1)  /* steps/block_symbols/fixed_words not a supported layout */
+#define LCT_E_NULL_POINTER (-2)
+#define LCT_E_ALIGNMENT (-3)     /* a buffer that must be 16-byte aligned is not */
+#define LCT_E_BAD_ARGUMENT (-4)
+#define LCT_E_TOO_LARGE (-5)
+
+/* Overflow ("fallback") storage of one compressed tensor, as the decoders see
+ * it.  mode 0: the tensor has no overflow streams, the other fields are
+ * ignored.  mode 1: private tensors lanes/starts/tail (tail bytes start at
+ * tail + base).  mode 2: shared arena; lanes == starts == tail == arena
+ * payload, and the region [descriptor[0], +descriptor[1]) holds
+ * lanes[count] | starts[count] | tails.  Reference: FallbackStorage,
+ * LCT/kernels/backends.py:36-50, and fallback_tail_args, dispatch.py:133-144. */
+typedef struct lct_overflow {
+  const uint8_t *lanes;
+  const uint8_t *starts;
+  const uint8_t *tail;
+  const int32_t *descriptor; /* int32[4] = offset|-1, aligned size|0, status, generation */
+  const int32_t *count;      /* int32[1]: number of overflow streams */
+  const int32_t *blocks;     /* int32[3*blocks]: count | first entry | first tail byte */
+  int64_t base;
+  int32_t mode;
+  int32_t reserved;
+} lct_overflow;
+
+/* One compressed operand for the decoders and fused operations. */
+typedef struct lct_operand {
+  const int32_t *encoded;        /* int32[streams*fixed_words + 4] */
+  const uint8_t *side;           /* uint8[size] sign+mantissa bytes, storage order */
+  const int32_t *shifted_decode; /* int32[1024], built at encode time */
+  const int32_t *center;         /* int32[1] */
+  const uint32_t *pair_table;    /* uint32[4096] from lct_build_pair_table for this codebook */
+  lct_overflow overflow;
+} lct_operand;
+
+/* Library identity: "lct-b200 <version> sm_100a". Host pointer, static storage. */
+const char *lct_version(void);
+/* Text for a return code of this library (host pointer, static storage). */
+const char *lct_error_string(int code);
+
+/* ---- codebook preparation ------------------------------------------------ */
+
+/* Two-symbol lookup table over 12 stream bits, in table-index space, derived
+ * from a codebook's first-level decode table (int32[1024]).  Depends only on
+ * the Distribution, so callers build it once per codebook and device.  No
+ * counterpart in the reference (its decoders look up one symbol at a time,
+ * LCT/kernels/primitives.py:17-36). */
+int lct_build_pair_table(const int32_t *decode_table, int rare_length, uint32_t *pair_table,
+                         void *stream);
+
+/* Sample the exponent center of `src` (int16 BF16 bits, or uint8 exponent
+ * bytes when precomputed) and write center[1], shifted_encode[256] and
+ * shifted_decode[1024].  Replaces dispatch.estimate_and_shift_encoding_table,
+ * LCT/kernels/dispatch.py:33-48 (kernel: common/tables.py:86-99).  src needs
+ * only its natural alignment. */
+int lct_center_and_tables(const void *src, int64_t logical_numel, int precomputed,
+                          const int32_t *encode_table, const int32_t *decode_table,
+                          int32_t *center, int32_t *shifted_encode, int32_t *shifted_decode,
+                          void *stream);
+
+/* Same tables for a given center.  Either output may be NULL.  Replaces
+ * dispatch.shift_encoding_table / shift_decoding_table, dispatch.py:16-30, 51-62. */
+int lct_shift_tables(const int32_t *encode_table, const int32_t *decode_table,
+                     const int32_t *center, int32_t *shifted_encode, int32_t *shifted_decode,
+                     void *stream);
+
+/* ---- encode --------------------------------------------------------------- */
+
+/* Field split + fixed-budget Huffman encode of every block.  Writes
+ * side[size] (skipped when precomputed), encoded[streams*fixed_words + 4]
+ * (every word, unused ones zero), extra_starts[streams] (first overflow step,
+ * 255 = none) and summaries[0 .. 2*blocks) = per-block overflow count and tail
+ * bytes.  Replaces dispatch.encode_kernel, dispatch.py:294-316 (kernel:
+ * generic/encode.py:10-169).  src may have any alignment. */
+int lct_encode(const void *src, uint8_t *side, int32_t *encoded, const int32_t *shifted_encode,
+               uint8_t *extra_starts, int32_t *summaries, int64_t size, int64_t logical_numel,
+               int block_symbols, int steps, int fixed_words, int precomputed, void *stream);
+
+/* Exclusive scan of the block summaries into summaries[2*blocks .. 4*blocks),
+ * totals into counts[0..1] (counts[2..3] = 0) and, when arena_storage is not
+ * NULL, a first-fit reservation of tail bytes + 2*count (rounded up to 16) in
+ * that arena, reported in descriptor[4].  Replaces dispatch.prefix_allocate,
+ * dispatch.py:70-85 (kernel: generic/metadata.py:13-38). */
+int lct_scan_allocate(int32_t *summaries, int32_t *counts, int32_t *descriptor,
+                      void *arena_storage, int64_t blocks, int max_free_regions, void *stream);
+
+/* Write the compact overflow list (lanes, starts), the raw exponent tails and
+ * blocks_out[3*blocks].  descriptor == NULL: private storage (lanes, starts,
+ * tail are exact-size tensors).  Otherwise the three pointers are the arena
+ * payload and nothing is written unless descriptor[2] == 0.  Replaces
+ * dispatch.compact_extra with build_meta=True, dispatch.py:113-130 (kernel:
+ * generic/compaction.py:135-190). */
+int lct_compact_tails(const void *src, uint8_t *lanes, uint8_t *starts, uint8_t *tail,
+                      const int32_t *descriptor, const int32_t *counts, int32_t *blocks_out,
+                      const uint8_t *extra_starts, const int32_t *summaries, int64_t size,
+                      int64_t logical_numel, int block_symbols, int steps, int precomputed,
+                      void *stream);
+
+/* ---- decode and fused operations ------------------------------------------ */
+
+/* Decode to int16 BF16 bits out[logical_numel], overflow tails substituted in
+ * place.  Replaces dispatch.decode_kernel, dispatch.py:319-361 (kernels:
+ * generic/decode.py:259-308). */
+int lct_decode(const lct_operand *a /* host pointer */, int16_t *out, int64_t size,
+               int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+               int rare_length, void *stream);
+
+#define LCT_OP_ADD 0            /* bf16(a + b)            generic/pointwise.py:340-343 */
+#define LCT_OP_MULTIPLY 1       /* bf16(a * b)            generic/pointwise.py:346-349 */
+#define LCT_OP_SCALAR_MUL_ADD 2 /* bf16(fma-ordered alpha*a + beta*b), pointwise.py:352-363 */
+
+/* compA (op) B with B dense BF16 in logical order.  compressed_output == 0:
+ * output = BF16[logical_numel].  Otherwise output = side bytes uint8[size]
+ * (storage order) and auxiliary = exponent bytes uint8[size] (logical order,
+ * padding untouched), ready for lct_encode(precomputed=1).  alpha/beta are
+ * device float32 scalars, read only when the matching *_is_one flag is 0.
+ * Overflow rows are computed in the same launch.  Replaces
+ * dispatch.pointwise_dense + dispatch.pointwise_fallback, dispatch.py:168-212
+ * (kernels: generic/pointwise.py:84-337).  `other` may have any alignment. */
+int lct_pointwise(const lct_operand *a /* host pointer */, const void *other, void *output,
+                  uint8_t *auxiliary, const float *alpha, const float *beta, int op,
+                  int alpha_is_one, int beta_is_one, int compressed_output, int64_t size,
+                  int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                  int rare_length, void *stream);
+
+/* alpha * compA + compB, both compressed with the same geometry.  Outputs as
+ * lct_pointwise.  Replaces dispatch.dual_maps_init, dual_tables_and_maps and
+ * dual_mapped, dispatch.py:215-286 (kernels: generic/pointwise_scalar_dual.py). */
+int lct_dual_scale_add(const lct_operand *a, const lct_operand *b /* host pointers */,
+                       void *output, uint8_t *auxiliary, const float *alpha,
+                       int compressed_output, int64_t size, int64_t logical_numel,
+                       int block_symbols, int steps, int fixed_words, int rare_length,
+                       void *stream);
+
+/* ---- shared overflow arena (TensorBuffer) ---------------------------------- */
+/* storage layout: int32 free_starts[R] | free_sizes[R] | free_count | lock |
+ * generation | pad to 16 bytes | payload[capacity]  (LCT/tensor_buffer.py:58-82).
+ * Descriptor status: 0 ok, 1 no fit, 2 empty request, 5 freed, 7 lock wait
+ * gave up.  Free status: 0 ok, 3 free list full, 4 invalid or stale, 7 lock
+ * wait gave up.  (LCT/kernels/tensor_buffer.py:84-90, 171-178; 7 is new: the
+ * reference spins without bound.) */
+
+/* Replaces TensorBuffer.reset, tensor_buffer.py:130-136 (kernel :18-34). */
+int lct_buffer_reset(void *storage, int max_free_regions, int32_t capacity_bytes, void *stream);
+/* request = *requested_bytes + *item_count * item_bytes, rounded up to 16.
+ * Replaces TensorBuffer.allocate / allocate_with_items, tensor_buffer.py:93-120. */
+int lct_buffer_allocate(void *storage, const int32_t *requested_bytes,
+                        const int32_t *item_count, int item_bytes, int32_t *descriptor,
+                        int max_free_regions, void *stream);
+/* Replaces the lct::tensor_buffer_free op, LCT/kernels/tensor_buffer_ops.py:5-15. */
+int lct_buffer_free(void *storage, int32_t *descriptor, int32_t *status, int max_free_regions,
+                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LCT_B200_H */

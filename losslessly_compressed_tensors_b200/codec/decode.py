@@ -1,0 +1,74 @@
+"""Host side of decoding: output allocation and the operand view for the decoder.
+
+Follows ``LCT/codec/decode.py:18-92`` of the reference.  The overflow tails are
+always substituted inside the decode launch; there is no second scatter pass.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..comp_tensor import CompressedTensor
+from ..compression.huffman_tables import get_distribution_tables
+from ..kernels import dispatch
+from ..kernels.backends import FallbackStorage
+
+
+def _buffered(data: CompressedTensor) -> bool:
+    return data.fallback_descriptor is not None
+
+
+def _storage(data: CompressedTensor) -> FallbackStorage:
+    """Overflow view of a compressed tensor: arena region or private tensors."""
+    if _buffered(data):
+        arena = data.fallback_buffer
+        return FallbackStorage(
+            tail=arena, count=data.fallback_count, lanes=arena, starts=arena,
+            blocks=data.fallback_blocks, descriptor=data.fallback_descriptor,
+            allocation=data.fallback_descriptor,
+        )
+    return FallbackStorage(
+        tail=data.fallback_buffer, count=data.fallback_count,
+        lanes=data.fallback_lanes, starts=data.fallback_starts,
+        blocks=data.fallback_blocks, allocation=data.fallback_lanes,
+        base=data.fallback_base,
+    )
+
+
+def has_fallback(data: CompressedTensor) -> bool:
+    """True when the decoder has to consult overflow storage (always for buffered tensors,
+    whose overflow count lives on the device)."""
+    if data.layout != data.layout.COMPRESSED:
+        return False
+    if _buffered(data):
+        return True
+    return data.fallback_lanes is not None and data.fallback_lanes.numel() > 0
+
+
+def operand_of(data: CompressedTensor):
+    """The ``struct lct_operand`` describing ``data`` for the decoder and the fused operations."""
+    device = data.data.device
+    overflow = dispatch.fallback_tail_args(_storage(data) if has_fallback(data) else None)
+    pair_table = dispatch.pair_table_for(data.distribution, device)
+    shifted = data.decode_table
+    if shifted is None:
+        _, decode_table, _ = get_distribution_tables(data.distribution, device)
+        shifted = dispatch.shift_decoding_table(decode_table, data.center)
+    operand = dispatch.make_operand(data.data, data.sign_mantissa, shifted, data.center,
+                                    pair_table, overflow)
+    operand.keepalive = (shifted, pair_table)  # raw pointers inside: keep the tensors referenced
+    return operand
+
+
+def decode(data: CompressedTensor) -> torch.Tensor:
+    """Decode to a BF16 tensor of the original shape."""
+    logical_numel = data.logical_numel
+    output = torch.empty(logical_numel, dtype=torch.int16, device=data.data.device)
+    if logical_numel:
+        _, _, rare_length = get_distribution_tables(data.distribution, data.data.device)
+        block_symbols, lanes, steps, fixed_words = data.codec_geometry
+        dispatch.decode_kernel(
+            operand_of(data), output, data.size, logical_numel=logical_numel,
+            block_symbols=block_symbols, lanes=lanes, steps=steps, fixed_words=fixed_words,
+            rare_length=rare_length,
+        )
+    return output.view(torch.bfloat16).reshape(data.shape)

@@ -1,0 +1,153 @@
+"""Host pipeline that turns BF16 values (or already split components) into a ``CompressedTensor``.
+
+Launch order and every output allocation follow the reference's
+``LCT/codec/encode.py:22-218`` so that the result holds the same tensors with
+the same sizes:
+
+1. center sample + shifted tables                       (1 CTA)
+2. field split + fixed-budget Huffman encode            (1 CTA per block)
+3. scan of per-block overflow summaries (+ arena reservation when buffered)
+4. compact overflow entries and raw exponent tails      (1 CTA per block)
+
+With a shared ``TensorBuffer`` nothing synchronises the host.  Without one the
+overflow tensors are allocated at their exact size, which needs the two totals
+on the host (one 8-byte copy), exactly like the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..comp_format import Distribution, StorageLayout
+from ..comp_tensor import CompressedTensor
+from ..compression.huffman_tables import get_distribution_tables
+from ..kernels import dispatch
+from ..kernels.backends import FallbackStorage
+from ..tensor_buffer import TensorBuffer
+from .geometry import geometry
+
+CENTER_SAMPLE_SIZE = 4096
+
+
+def encode_components(
+    source_values: torch.Tensor,
+    sign_mantissa: torch.Tensor,
+    size: int,
+    distribution: Distribution,
+    buffer: TensorBuffer | None,
+    shape: tuple[int, ...],
+    *,
+    precomputed: bool,
+    center: torch.Tensor | None = None,
+    logical_numel: int,
+) -> CompressedTensor:
+    """Encode int16 BF16 bits, or (``precomputed``) uint8 exponent bytes in logical order
+    whose side bytes already sit in ``sign_mantissa``.  ``size`` is the padded element count."""
+    if buffer is not None and buffer.capacity_bytes % 4:
+        raise ValueError("TensorBuffer capacity must be divisible by 4")
+    device = source_values.device
+    stream_geometry = geometry(distribution)
+    block_symbols, lanes, steps, fixed_words = stream_geometry
+    blocks = -(-size // block_symbols)
+    streams = blocks * lanes
+    encode_table, decode_table, _ = get_distribution_tables(distribution, device)
+
+    def scratch(n, dtype):
+        return torch.empty(n, dtype=dtype, device=device)
+
+    shifted_encode = scratch(256, torch.int32)
+    shifted_decode = torch.empty_like(decode_table)
+    if center is None:
+        center = scratch(1, torch.int32)
+        dispatch.estimate_and_shift_encoding_table(
+            source_values, center, logical_numel, encode_table, shifted_encode,
+            decode_table, shifted_decode, min(logical_numel, CENTER_SAMPLE_SIZE), precomputed,
+        )
+    else:
+        dispatch.shift_encoding_table(encode_table, center, shifted_encode, decode_table,
+                                      shifted_decode)
+
+    encoded = scratch(streams * fixed_words + 4, torch.int32)
+    extra_starts = scratch(streams, torch.uint8)
+    summaries = scratch(4 * blocks, torch.int32)
+    counts = scratch(4, torch.int32)
+    blocks_out = scratch(3 * blocks, torch.int32)
+    if blocks == 0:
+        # Nothing to encode: an empty tensor keeps well-defined (zero) metadata.
+        encoded.zero_()
+        counts.zero_()
+    else:
+        dispatch.encode_kernel(
+            source_values, sign_mantissa, encoded, shifted_encode, extra_starts, summaries,
+            size, streams, precomputed=precomputed, logical_numel=logical_numel,
+            block_symbols=block_symbols, lanes=lanes, steps=steps, fixed_words=fixed_words,
+        )
+    final_count, final_total = counts[:1], counts[1:2]
+
+    buffered = buffer is not None
+    if buffered:
+        descriptor = scratch(4, torch.int32)
+        if blocks:
+            dispatch.prefix_allocate(summaries, counts, descriptor, buffer, blocks, True,
+                                     buffer.max_free_regions)
+        else:
+            descriptor.copy_(torch.tensor([-1, 0, 2, 0], dtype=torch.int32))
+        arena = buffer.data
+        storage = FallbackStorage(tail=arena, count=final_count, lanes=arena, starts=arena,
+                                  blocks=blocks_out, descriptor=descriptor, allocation=descriptor)
+    else:
+        descriptor = None
+        if blocks:
+            dispatch.prefix_allocate(summaries, counts, counts, None, blocks, False, 256)
+        # Exact-size private overflow tensors need the two totals on the host.
+        count, tail_bytes = (int(v) for v in counts[:2].tolist())
+        storage = FallbackStorage(
+            tail=scratch(tail_bytes, torch.uint8), count=final_count,
+            lanes=scratch(count, torch.uint8), starts=scratch(count, torch.uint8),
+            blocks=blocks_out, allocation=counts[2:3], base=0,
+        )
+    if blocks:
+        dispatch.compact_extra(
+            source_values, storage, final_count, blocks, size,
+            precomputed=precomputed, buffered=buffered, logical_numel=logical_numel,
+            block_symbols=block_symbols, lanes=lanes, steps=steps,
+            extra_starts=extra_starts, summaries=summaries, n_streams=streams,
+        )
+    return CompressedTensor(
+        encoded, size, sign_mantissa,
+        fallback_starts=None if buffered else storage.starts,
+        fallback_lanes=None if buffered else storage.lanes,
+        fallback_blocks=storage.blocks,
+        fallback_buffer=storage.tail,
+        fallback_descriptor=descriptor,
+        buffer=buffer,
+        fallback_count=final_count,
+        fallback_used=final_total,
+        distribution=distribution, center=center, decode_table=shifted_decode,
+        shape=shape,
+        layout=StorageLayout.COMPRESSED,
+        stream_geometry=stream_geometry,
+    )
+
+
+def encode(data: torch.Tensor, distribution: Distribution, buffer: TensorBuffer | None = None, *,
+           allow_raw: bool = False) -> CompressedTensor:
+    """Compress a BF16 tensor of any shape through the flattened, block-padded layout."""
+    if data.dtype != torch.bfloat16:
+        raise TypeError(f"the codec compresses bfloat16 tensors, got {data.dtype}")
+    shape = tuple(data.shape)
+    source = data.contiguous().view(-1)
+    logical_numel = source.numel()
+    block_symbols, lanes, _, fixed_words = geometry(distribution)
+    blocks = -(-logical_numel // block_symbols)
+    storage_numel = blocks * block_symbols
+    if allow_raw:
+        # Keep the dense bytes when even an overflow-free encoding would be larger.
+        smallest = storage_numel + (blocks * lanes * fixed_words + 4) * 4
+        if smallest > logical_numel * data.element_size():
+            return CompressedTensor(source, logical_numel, buffer=buffer, distribution=distribution,
+                                    shape=shape, layout=StorageLayout.RAW)
+    sign_mantissa = torch.empty(storage_numel, dtype=torch.uint8, device=source.device)
+    return encode_components(
+        source.view(torch.int16), sign_mantissa, storage_numel, distribution, buffer, shape,
+        precomputed=False, logical_numel=logical_numel,
+    )

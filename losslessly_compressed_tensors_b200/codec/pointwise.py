@@ -1,0 +1,175 @@
+"""Fused arithmetic on compressed tensors: ``compA (op) B`` and ``alpha * compA + compB``.
+
+Interface of the reference's ``LCT/codec/pointwise.py:28-304``.  A fused launch decodes the
+compressed operand(s), applies the operation with the reference's rounding (one BF16
+rounding for add/multiply; float32 ``fma`` then round-to-nearest-even for the scaled forms)
+and writes either dense BF16 or the split components, which then go through the normal
+encode pipeline (new center sampled from the result).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from ..comp_format import Distribution, StorageLayout
+from ..comp_tensor import CompressedTensor
+from ..compression.huffman_tables import get_distribution_tables
+from ..kernels import dispatch
+from ..tensor_buffer import TensorBuffer
+from .decode import decode as decode_dense, operand_of
+from .encode import encode as compress_dense, encode_components as compress_components
+from .geometry import geometry
+
+
+@dataclass(frozen=True)
+class PointwiseOp:
+    """An in-kernel operation code and the PyTorch expression with the same result."""
+
+    name: str
+    code: int
+    torch_fn: object
+
+
+ADD = PointwiseOp("add", dispatch.OP_ADD, torch.add)
+MULTIPLY = PointwiseOp("multiply", dispatch.OP_MULTIPLY, torch.mul)
+SCALAR_MUL_ADD = PointwiseOp(
+    "scalar_mul_add", dispatch.OP_SCALAR_MUL_ADD,
+    lambda left, right, alpha=1.0: (left.float() * alpha + right.float()).to(torch.bfloat16),
+)
+POINTWISE_OPS = {op.name: op for op in (ADD, MULTIPLY, SCALAR_MUL_ADD)}
+
+
+def _outputs(data: CompressedTensor, dense_output: bool):
+    device = data.data.device
+    if dense_output:
+        output = torch.empty(data.logical_numel, dtype=torch.bfloat16, device=device)
+        return output, output
+    output = torch.empty(data.size, dtype=torch.uint8, device=device)
+    return output, torch.empty_like(output)
+
+
+def _scalar(value: Tensor | None, device) -> Tensor | None:
+    if value is None:
+        return None
+    if value.dtype != torch.float32 or value.device != device:
+        value = value.to(device=device, dtype=torch.float32)
+    return value.reshape(-1)[:1].contiguous()
+
+
+def _launch_pointwise_compressed_dense(data, other, operation, dense_output, *, alpha=None,
+                                       beta=None, alpha_is_one=False):
+    scaled = operation.name == "scalar_mul_add"
+    device = data.data.device
+    other = other.contiguous().view(-1)
+    if other.dtype != torch.bfloat16:
+        raise TypeError("the dense operand must be bfloat16")
+    alpha = _scalar(alpha, device) if scaled and not alpha_is_one else None
+    beta = _scalar(beta, device) if scaled else None
+    _, _, rare_length = get_distribution_tables(data.distribution, device)
+    block_symbols, lanes, steps, fixed_words = data.codec_geometry
+    output, auxiliary = _outputs(data, dense_output)
+    if data.logical_numel:
+        dispatch.pointwise_dense(
+            operand_of(data), other, output, auxiliary, data.size, alpha, beta,
+            op=operation.code, alpha_is_one=not scaled or alpha_is_one,
+            beta_is_one=not scaled or beta is None, compressed_output=not dense_output,
+            rare_length=rare_length, logical_numel=data.logical_numel,
+            block_symbols=block_symbols, lanes=lanes, steps=steps, fixed_words=fixed_words,
+        )
+    return output, auxiliary
+
+
+def _launch_scalar_mul_add_compressed_compressed(data, other, alpha, dense_output):
+    device = data.data.device
+    _, _, rare_a = get_distribution_tables(data.distribution, device)
+    _, _, rare_b = get_distribution_tables(other.distribution, device)
+    if rare_a != rare_b:
+        raise ValueError("two-compressed path requires matching RARE_LENGTH")
+    block_symbols, lanes, steps, fixed_words = data.codec_geometry
+    output, auxiliary = _outputs(data, dense_output)
+    if data.logical_numel:
+        dispatch.dual_scale_add(
+            operand_of(data), operand_of(other), output, auxiliary, _scalar(alpha, device),
+            data.size, compressed_output=not dense_output, rare_length=rare_a,
+            logical_numel=data.logical_numel, block_symbols=block_symbols, lanes=lanes,
+            steps=steps, fixed_words=fixed_words,
+        )
+    return output, auxiliary
+
+
+def pointwise_scale_add_compressed(
+    data: CompressedTensor, other: CompressedTensor, alpha: Tensor, *,
+    dense_output: bool = True, buffer: TensorBuffer | None = None,
+    distribution: Distribution | None = None,
+) -> Tensor | CompressedTensor:
+    """``alpha * compA + compB``, dense BF16 or compressed result."""
+    both_compressed = (data.layout == StorageLayout.COMPRESSED
+                       and other.layout == StorageLayout.COMPRESSED)
+    assert (data.fallback_descriptor is None) == (other.fallback_descriptor is None), (
+        "pointwise_scale_add_compressed requires both inputs to be buffer-backed "
+        "or both to be non-buffer-backed"
+    )
+    if both_compressed and data.codec_geometry == other.codec_geometry:
+        result_distribution = distribution or data.distribution
+        if not dense_output and geometry(result_distribution) != data.codec_geometry:
+            raise ValueError("matrix compressed output must preserve the input stream geometry")
+        values, auxiliary = _launch_scalar_mul_add_compressed_compressed(
+            data, other, alpha, dense_output)
+        if dense_output:
+            return values.reshape(data.shape)
+        return compress_components(
+            auxiliary, values, data.size, result_distribution, buffer, data.shape,
+            precomputed=True, logical_numel=data.logical_numel,
+        )
+    other_dense = (other.data.reshape(other.shape) if other.layout == StorageLayout.RAW
+                   else decode_dense(other))
+    return pointwise_compressed_dense(
+        data, other_dense, SCALAR_MUL_ADD, alpha=alpha, dense_output=dense_output,
+        buffer=buffer, distribution=distribution,
+    )
+
+
+def _raw_result(data, other, operation, alpha, beta, alpha_is_one):
+    """Same arithmetic on an uncompressed (RAW layout) left operand, in PyTorch."""
+    left = data.data.reshape(data.shape)
+    if operation.name != "scalar_mul_add":
+        return operation.torch_fn(left, other)
+    if alpha_is_one:
+        if beta is None:
+            return (left.float() + other.float()).to(torch.bfloat16)
+        return torch.addcmul(left.float(), other.float(), beta).to(torch.bfloat16)
+    if beta is None:
+        return operation.torch_fn(left, other, alpha)
+    return torch.addcmul(other.float() * beta, left.float(), alpha).to(torch.bfloat16)
+
+
+def pointwise_compressed_dense(
+    data: CompressedTensor, other: Tensor, operation: PointwiseOp, *,
+    alpha: Tensor | None = None, beta: Tensor | None = None, alpha_is_one: bool = False,
+    dense_output: bool = True, buffer: TensorBuffer | None = None,
+    distribution: Distribution | None = None,
+) -> Tensor | CompressedTensor:
+    """``compA + B``, ``compA * B`` or ``alpha * compA + beta * B`` elementwise."""
+    if tuple(other.shape) != data.shape:
+        raise ValueError(f"{operation.name} expects tensors with the same shape")
+    result_distribution = distribution or data.distribution
+    if operation.name == "scalar_mul_add" and alpha is None:
+        raise ValueError("scalar_mul_add requires an alpha argument")
+    if (data.layout == StorageLayout.COMPRESSED and not dense_output
+            and geometry(result_distribution) != data.codec_geometry):
+        raise ValueError("matrix compressed output must preserve the input stream geometry")
+
+    if data.layout == StorageLayout.RAW:
+        result = _raw_result(data, other, operation, alpha, beta, alpha_is_one)
+        return result if dense_output else compress_dense(result, result_distribution, buffer)
+
+    values, auxiliary = _launch_pointwise_compressed_dense(
+        data, other, operation, dense_output, alpha=alpha, beta=beta, alpha_is_one=alpha_is_one)
+    if dense_output:
+        return values.reshape(data.shape)
+    return compress_components(
+        auxiliary, values, data.size, result_distribution, buffer, data.shape,
+        precomputed=True, logical_numel=data.logical_numel,
+    )

@@ -1,0 +1,196 @@
+// Device-resident first-fit allocator for the shared overflow arena, and the
+// per-tensor scan of block overflow summaries that feeds it.  Every launch is
+// a single CTA; nothing here waits on another kernel, and the one lock wait is
+// bounded (status 7 when it gives up).
+#include "common.cuh"
+#include "lct_b200.h"
+
+namespace lct {
+
+constexpr int kArenaThreads = 256;
+constexpr int kScanThreads = 1024;
+
+__global__ void __launch_bounds__(kArenaThreads)
+arena_reset_kernel(void* storage, int regions, int32_t capacity) {
+  const Arena a = arena_of(storage, regions);
+  for (int i = threadIdx.x; i < regions; i += blockDim.x) {
+    a.starts[i] = 0;
+    a.sizes[i] = i == 0 ? capacity : 0;
+  }
+  if (threadIdx.x == 0) {
+    *a.count = 1;
+    *a.generation = *a.generation + 1;
+    __threadfence();
+    atomicExch(a.lock, 0);
+  }
+}
+
+__global__ void __launch_bounds__(kArenaThreads)
+arena_allocate_kernel(void* storage, const int32_t* requested_bytes, const int32_t* item_count,
+                      int item_bytes, int32_t* descriptor, int regions) {
+  __shared__ int scratch[2];
+  int32_t request = *requested_bytes;
+  if (item_bytes != 0) request += *item_count * item_bytes;
+  arena_allocate(arena_of(storage, regions), regions, request, descriptor, scratch);
+}
+
+// Return a region to the sorted free list, merging with its neighbours.
+__global__ void __launch_bounds__(kArenaThreads)
+arena_free_kernel(void* storage, int32_t* descriptor, int32_t* status_out, int regions) {
+  __shared__ int scratch[2];
+  const Arena a = arena_of(storage, regions);
+  if (!arena_lock(a, scratch)) {
+    if (threadIdx.x == 0) *status_out = kStatusLockTimeout;
+    return;
+  }
+  const int32_t offset = descriptor[0], size = descriptor[1];
+  const bool valid = descriptor[2] == 0 && descriptor[3] == *a.generation && offset >= 0 && size > 0;
+  const int count = *a.count;
+  // Insert position = number of free regions that start below the freed one.
+  if (threadIdx.x == 0) scratch[1] = 0;
+  __syncthreads();
+  int below = 0;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) below += a.starts[i] < offset ? 1 : 0;
+  if (below) atomicAdd(&scratch[1], below);
+  __syncthreads();
+  const int insert = scratch[1];
+  __syncthreads();
+  bool merge_prev = false, merge_next = false;
+  int32_t prev_size = 0, next_size = 0;
+  if (valid) {
+    if (insert > 0) {
+      prev_size = a.sizes[insert - 1];
+      merge_prev = a.starts[insert - 1] + prev_size == offset;
+    }
+    if (insert < count) {
+      next_size = a.sizes[insert];
+      merge_next = offset + size == a.starts[insert];
+    }
+  }
+  __syncthreads();
+  int status = valid ? 0 : 4;
+  if (valid && merge_prev && merge_next) {
+    if (threadIdx.x == 0) a.sizes[insert - 1] = prev_size + size + next_size;
+    for (int base = insert; base + 1 < count; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      const bool move = i + 1 < count;
+      int32_t ns = 0, nz = 0;
+      if (move) { ns = a.starts[i + 1]; nz = a.sizes[i + 1]; }
+      __syncthreads();
+      if (move) { a.starts[i] = ns; a.sizes[i] = nz; }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) *a.count = count - 1;
+  } else if (valid && merge_prev) {
+    if (threadIdx.x == 0) a.sizes[insert - 1] = prev_size + size;
+  } else if (valid && merge_next) {
+    if (threadIdx.x == 0) { a.starts[insert] = offset; a.sizes[insert] = next_size + size; }
+  } else if (valid) {
+    if (count >= regions) {
+      status = 3;
+    } else {
+      // Open a slot: shift right from the top down, chunk by chunk.
+      for (int top = count; top > insert; top -= blockDim.x) {
+        const int i = top - 1 - (int)threadIdx.x;  // source index, moves to i + 1
+        const bool move = i >= insert;
+        int32_t ps = 0, pz = 0;
+        if (move) { ps = a.starts[i]; pz = a.sizes[i]; }
+        __syncthreads();
+        if (move) { a.starts[i + 1] = ps; a.sizes[i + 1] = pz; }
+        __syncthreads();
+      }
+      if (threadIdx.x == 0) {
+        a.starts[insert] = offset;
+        a.sizes[insert] = size;
+        *a.count = count + 1;
+      }
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (status == 0) descriptor[2] = 5;
+    *status_out = status;
+  }
+  arena_unlock(a);
+}
+
+// Exclusive scans of the per-block overflow counts and tail bytes, totals, and
+// (for a shared arena) the reservation of this tensor's overflow region.
+__global__ void __launch_bounds__(kScanThreads)
+scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, void* arena_storage,
+                     int64_t blocks, int regions) {
+  __shared__ int scratch[33];
+  __shared__ int alloc_scratch[2];
+  int running_count = 0, running_bytes = 0;
+  for (int64_t base = 0; base < blocks; base += blockDim.x) {
+    const int64_t i = base + threadIdx.x;
+    const int c = i < blocks ? summaries[i] : 0;
+    const int t = i < blocks ? summaries[blocks + i] : 0;
+    int total_c, total_t;
+    const int pc = block_exclusive_scan(c, scratch, &total_c);
+    const int pt = block_exclusive_scan(t, scratch, &total_t);
+    if (i < blocks) {
+      summaries[2 * blocks + i] = running_count + pc;
+      summaries[3 * blocks + i] = running_bytes + pt;
+    }
+    running_count += total_c;
+    running_bytes += total_t;
+  }
+  if (threadIdx.x == 0) {
+    counts[0] = running_count;
+    counts[1] = running_bytes;
+    counts[2] = 0;
+    counts[3] = 0;
+  }
+  if (arena_storage != nullptr) {
+    // Two metadata bytes per overflowing stream (lane, start) ahead of the tails.
+    arena_allocate(arena_of(arena_storage, regions), regions, running_bytes + 2 * running_count,
+                   descriptor, alloc_scratch);
+  }
+}
+
+}  // namespace lct
+
+extern "C" {
+
+static bool power_of_two(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+int lct_buffer_reset(void* storage, int max_free_regions, int32_t capacity_bytes, void* stream) {
+  if (storage == nullptr) return LCT_E_NULL_POINTER;
+  if (!power_of_two(max_free_regions) || capacity_bytes < 0) return LCT_E_BAD_ARGUMENT;
+  lct::arena_reset_kernel<<<1, lct::kArenaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      storage, max_free_regions, capacity_bytes);
+  return (int)cudaGetLastError();
+}
+
+int lct_buffer_allocate(void* storage, const int32_t* requested_bytes, const int32_t* item_count,
+                        int item_bytes, int32_t* descriptor, int max_free_regions, void* stream) {
+  if (storage == nullptr || requested_bytes == nullptr || descriptor == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (item_bytes != 0 && item_count == nullptr) return LCT_E_NULL_POINTER;
+  if (!power_of_two(max_free_regions) || item_bytes < 0) return LCT_E_BAD_ARGUMENT;
+  lct::arena_allocate_kernel<<<1, lct::kArenaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      storage, requested_bytes, item_count, item_bytes, descriptor, max_free_regions);
+  return (int)cudaGetLastError();
+}
+
+int lct_buffer_free(void* storage, int32_t* descriptor, int32_t* status, int max_free_regions,
+                    void* stream) {
+  if (storage == nullptr || descriptor == nullptr || status == nullptr) return LCT_E_NULL_POINTER;
+  if (!power_of_two(max_free_regions)) return LCT_E_BAD_ARGUMENT;
+  lct::arena_free_kernel<<<1, lct::kArenaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      storage, descriptor, status, max_free_regions);
+  return (int)cudaGetLastError();
+}
+
+int lct_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
+                      void* arena_storage, int64_t blocks, int max_free_regions, void* stream) {
+  if (summaries == nullptr || counts == nullptr) return LCT_E_NULL_POINTER;
+  if (arena_storage != nullptr && descriptor == nullptr) return LCT_E_NULL_POINTER;
+  if (blocks < 0) return LCT_E_BAD_ARGUMENT;
+  if (arena_storage != nullptr && !power_of_two(max_free_regions)) return LCT_E_BAD_ARGUMENT;
+  lct::scan_allocate_kernel<<<1, lct::kScanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      summaries, counts, descriptor, arena_storage, blocks, max_free_regions);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

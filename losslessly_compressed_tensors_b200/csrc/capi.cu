@@ -1,0 +1,24 @@
+// Library identity and error text.
+#include <cuda_runtime.h>
+
+#include "lct_b200.h"
+
+extern "C" {
+
+const char* lct_version(void) { return "lct-b200 0.1.0 sm_100a"; }
+
+const char* lct_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case LCT_E_BAD_GEOMETRY: return "unsupported stream geometry";
+    case LCT_E_NULL_POINTER: return "required pointer is null";
+    case LCT_E_ALIGNMENT: return "buffer is not aligned as required";
+    case LCT_E_BAD_ARGUMENT: return "argument out of range";
+    case LCT_E_TOO_LARGE: return "tensor has too many blocks for one launch";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown lct error";
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+// Shared device helpers of the sm_100a codec kernels.
+//
+// Data layout recap.  A block is `steps` rows of 256 lanes.  Lane l at global
+// row n holds logical element n*256 + (l ^ (n & 254)); rows 2k and 2k+1 share
+// one XOR mask, and the mask is even, so lanes 2p/2p+1 stay adjacent.  Inside
+// every kernel a block is processed in tiles of 32 rows that pass through a
+// shared-memory tile of exponent bytes kept in COLUMN (logical) order:
+//
+//     tile[pair p][column c] = e(row 2p, c) | e(row 2p+1, c) << 8      (uint16)
+//
+// One side of each kernel works lane-wise (a thread owns a lane and walks its
+// bit stream, touching tile[p][lane ^ mask]); the other side works row-wise
+// (a thread owns 8 adjacent columns of a row pair, so global loads and stores
+// are 128-bit and a warp covers one full 512-byte row).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lct {
+
+constexpr int kLanes = 256;
+constexpr int kThreads = 256;           // one thread per lane
+constexpr int kTilePairs = 16;          // row pairs per shared-memory tile (32 rows)
+constexpr int kTileRows = 2 * kTilePairs;
+constexpr int kPairBits = 12;           // stream bits indexing the two-symbol table
+constexpr int kPairEntries = 1 << kPairBits;
+constexpr int kFirstMask = 1023;        // the codebook's first-level table covers 10 bits
+
+// Two-symbol table entry: byte0 = first symbol, byte1 = second symbol,
+// byte2 = bits consumed by the symbols present, byte3 = length of the first
+// symbol | flags.  kSlow marks every entry that is not two directly coded
+// symbols (the sign bit, so one signed compare finds it).
+constexpr uint32_t kSlow = 0x80000000u;
+constexpr uint32_t kEscape = 0x40000000u;
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  return __byte_perm(a, b, selector);
+}
+
+// Selectors that reorder the four byte pairs of an 8-byte group by XOR-ing the
+// pair index with q (q = (row & 6) >> 1).  The same permutation maps lane
+// order to column order and back.
+__device__ __forceinline__ uint32_t pair_selector_low(uint32_t q) { return 0x3210u ^ (q * 0x2222u); }
+__device__ __forceinline__ uint32_t pair_selector_high(uint32_t q) { return 0x7654u ^ (q * 0x2222u); }
+
+// [s0, e0, s1, e1] bytes (side, exponent of two neighbours) -> two BF16 bit patterns.
+__device__ __forceinline__ uint32_t join_bf16x2(uint32_t x) {
+  return ((x >> 1) & 0x7F807F80u) | (x & 0x007F007Fu) | ((x << 8) & 0x80008000u);
+}
+
+// Two BF16 bit patterns -> exponent bytes in bytes 0 and 2 / side bytes in bytes 0 and 2.
+__device__ __forceinline__ uint32_t exponents_of(uint32_t w) { return w >> 7; }
+__device__ __forceinline__ uint32_t sides_of(uint32_t w) {
+  return (w & 0x007F007Fu) | ((w >> 8) & 0x00800080u);
+}
+
+// Table index (0 = exact zero, else centred exponent delta) -> raw exponent byte.
+__device__ __forceinline__ uint32_t index_to_exponent_byte(uint32_t index, int center) {
+  const uint32_t zero_delta = (uint32_t)(-127 - center) & 255u;
+  if (index == 0) return 0;
+  return (index - (index <= zero_delta ? 1u : 0u) + (uint32_t)(center + 127)) & 255u;
+}
+
+// Number of leading steps of `lane` in block `block` that hold real elements.
+__device__ __forceinline__ int valid_steps_of(int64_t block, int lane, int steps, int block_symbols,
+                                              int64_t logical_numel) {
+  const int64_t in_block = logical_numel - block * (int64_t)block_symbols;
+  if (in_block >= block_symbols) return steps;
+  if (in_block <= 0) return 0;
+  const int full_rows = (int)(in_block >> 8);
+  const int rem = (int)(in_block & 255);
+  const int mask = (int)((block * steps + full_rows) & 254);
+  return full_rows + ((rem > 0 && ((lane ^ mask) < rem)) ? 1 : 0);
+}
+
+// Block-wide exclusive prefix sum of one int per thread (blockDim.x <= 1024).
+// `scratch` needs 33 ints.  Returns the exclusive prefix; *total gets the sum.
+__device__ __forceinline__ int block_exclusive_scan(int value, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inclusive = value;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int up = __shfl_up_sync(0xFFFFFFFFu, inclusive, d);
+    if (lane >= d) inclusive += up;
+  }
+  if (lane == 31) scratch[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = (blockDim.x + 31) >> 5;
+    int w = lane < warps ? scratch[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int up = __shfl_up_sync(0xFFFFFFFFu, winc, d);
+      if (lane >= d) winc += up;
+    }
+    scratch[lane] = winc - w;
+    if (lane == 31) scratch[32] = winc;
+  }
+  __syncthreads();
+  const int result = scratch[warp] + inclusive - value;
+  *total = scratch[32];
+  __syncthreads();
+  return result;
+}
+
+// ---- shared overflow arena ------------------------------------------------
+// int32 free_starts[R] | free_sizes[R] | free_count | lock | generation
+struct Arena {
+  volatile int32_t* starts;
+  volatile int32_t* sizes;
+  volatile int32_t* count;
+  int32_t* lock;
+  volatile int32_t* generation;
+};
+
+__device__ __forceinline__ Arena arena_of(void* storage, int regions) {
+  int32_t* m = reinterpret_cast<int32_t*>(storage);
+  return Arena{m, m + regions, m + 2 * regions, m + 2 * regions + 1, m + 2 * regions + 2};
+}
+
+constexpr int kLockSpins = 200000;  // bounded wait: ~0.1 s worst case, then status 7
+constexpr int kStatusLockTimeout = 7;
+
+// Thread 0 of the CTA takes the arena lock; all threads learn the outcome.
+__device__ __forceinline__ bool arena_lock(const Arena& a, int* shared_flag) {
+  if (threadIdx.x == 0) {
+    int spins = 0;
+    bool got = false;
+    while (spins++ < kLockSpins) {
+      if (atomicCAS(a.lock, 0, 1) == 0) { got = true; break; }
+      __nanosleep(256);
+    }
+    __threadfence();
+    *shared_flag = got ? 1 : 0;
+  }
+  __syncthreads();
+  const bool ok = *shared_flag != 0;
+  __syncthreads();
+  return ok;
+}
+
+__device__ __forceinline__ void arena_unlock(const Arena& a) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicExch(a.lock, 0);
+  }
+}
+
+// First-fit reservation by a whole CTA (same results as the reference's
+// single-program allocator: lowest-index region that fits; exact fit removes
+// the region, otherwise it shrinks from the front).  `scratch` needs 2 ints.
+__device__ inline void arena_allocate(const Arena& a, int regions, int32_t request,
+                                      int32_t* descriptor, int* scratch) {
+  const int32_t generation = *a.generation;
+  if (!arena_lock(a, scratch)) {
+    if (threadIdx.x == 0) {
+      descriptor[0] = -1; descriptor[1] = 0; descriptor[2] = kStatusLockTimeout;
+      descriptor[3] = generation;
+    }
+    return;
+  }
+  const int32_t size = (request + 15) / 16 * 16;
+  const int count = *a.count;
+  if (threadIdx.x == 0) scratch[1] = regions;
+  __syncthreads();
+  for (int i = threadIdx.x; i < count; i += blockDim.x)
+    if (a.sizes[i] >= size) atomicMin(&scratch[1], i);
+  __syncthreads();
+  const int slot = scratch[1];
+  const bool success = request > 0 && slot < count;
+  int32_t start = 0, region = 0;
+  if (success) { start = a.starts[slot]; region = a.sizes[slot]; }
+  __syncthreads();
+  if (success && region == size) {
+    // Remove the region: shift the list left, chunk by chunk, reads before writes.
+    for (int base = slot; base + 1 < count; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      int32_t ns = 0, nz = 0;
+      const bool move = i + 1 < count;
+      if (move) { ns = a.starts[i + 1]; nz = a.sizes[i + 1]; }
+      __syncthreads();
+      if (move) { a.starts[i] = ns; a.sizes[i] = nz; }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) *a.count = count - 1;
+  } else if (success && threadIdx.x == 0) {
+    a.starts[slot] = start + size;
+    a.sizes[slot] = region - size;
+  }
+  if (threadIdx.x == 0) {
+    descriptor[0] = success ? start : -1;
+    descriptor[1] = success ? size : 0;
+    descriptor[2] = request <= 0 ? 2 : (success ? 0 : 1);
+    descriptor[3] = *a.generation;
+  }
+  arena_unlock(a);
+}
+
+}  // namespace lct

@@ -1,0 +1,162 @@
+// Codebook preparation kernels: exponent-center sampling, per-tensor shifted
+// tables, and the per-codebook two-symbol lookup table.
+#include "common.cuh"
+#include "lct_b200.h"
+
+namespace lct {
+
+constexpr int kCenterSamples = 4096;
+constexpr int kTableThreads = 1024;
+
+// Shifted tables for a center: encode indexed by raw exponent byte, decode
+// storing the unbiased exponent above the code length.
+__device__ __forceinline__ void write_shifted_tables(const int32_t* __restrict__ base_encode,
+                                                     const int32_t* __restrict__ base_decode,
+                                                     int center, int32_t* shifted_encode,
+                                                     int32_t* shifted_decode) {
+  const int zero_delta = (-127 - center) & 255;
+  if (shifted_encode != nullptr) {
+    for (int raw = threadIdx.x; raw < 256; raw += blockDim.x) {
+      const int exponent = raw - 127;
+      const int delta = (exponent - center) & 255;
+      const int index = exponent == -127 ? 0 : delta + (delta < zero_delta ? 1 : 0);
+      shifted_encode[raw] = base_encode[index];
+    }
+  }
+  if (shifted_decode != nullptr) {
+    for (int i = threadIdx.x; i <= kFirstMask; i += blockDim.x) {
+      const int32_t packed = base_decode[i];
+      const int length = packed & 255;
+      const int symbol = (packed >> 8) & 255;
+      int delta = symbol == 0 ? 0 : symbol - (symbol <= zero_delta ? 1 : 0);
+      if (delta >= 128) delta -= 256;
+      const int exponent = symbol == 0 ? -127 : delta + center;
+      shifted_decode[i] = length == 0 ? 0 : (int32_t)((uint32_t)length | ((uint32_t)exponent << 8));
+    }
+  }
+}
+
+// One CTA.  Every thread takes up to four of the <= 4096 jittered sample
+// positions; the mean exponent of the samples with exponent >= -120, rounded
+// half away from zero, is the center.
+template <bool kPrecomputed>
+__global__ void __launch_bounds__(kTableThreads)
+center_and_tables_kernel(const void* __restrict__ src, int64_t n,
+                         const int32_t* __restrict__ base_encode,
+                         const int32_t* __restrict__ base_decode, int32_t* center_out,
+                         int32_t* shifted_encode, int32_t* shifted_decode) {
+  __shared__ int s_sum[32], s_kept[32], s_center;
+  const int64_t samples = n < kCenterSamples ? n : kCenterSamples;
+  int sum = 0, kept = 0;
+  for (int64_t idx = threadIdx.x; idx < samples; idx += blockDim.x) {
+    const uint32_t hashed = (uint32_t)idx * 0x9E3779B9u;
+    const int64_t start = idx * n / samples;
+    const int64_t end = (idx + 1) * n / samples;
+    const uint64_t jitter = ((uint64_t)hashed * (uint64_t)(end - start)) >> 32;
+    const int64_t pos = start + (int64_t)jitter;
+    int exponent;
+    if (kPrecomputed) {
+      exponent = (int)static_cast<const uint8_t*>(src)[pos] - 127;
+    } else {
+      exponent = (((int)static_cast<const uint16_t*>(src)[pos] >> 7) & 0xFF) - 127;
+    }
+    if (exponent >= -120) { sum += exponent; ++kept; }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    sum += __shfl_down_sync(0xFFFFFFFFu, sum, d);
+    kept += __shfl_down_sync(0xFFFFFFFFu, kept, d);
+  }
+  if ((threadIdx.x & 31) == 0) { s_sum[threadIdx.x >> 5] = sum; s_kept[threadIdx.x >> 5] = kept; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int total = 0, count = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { total += s_sum[w]; count += s_kept[w]; }
+    const int safe = count > 0 ? count : 1;
+    int center = total >= 0 ? (total + safe / 2) / safe : -((-total + safe / 2) / safe);
+    if (count == 0) center = 0;
+    center = min(max(center, -128), 127);
+    s_center = center;
+    *center_out = center;
+  }
+  __syncthreads();
+  write_shifted_tables(base_encode, base_decode, s_center, shifted_encode, shifted_decode);
+}
+
+__global__ void __launch_bounds__(kTableThreads)
+shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __restrict__ base_decode,
+                    const int32_t* __restrict__ center, int32_t* shifted_encode,
+                    int32_t* shifted_decode) {
+  write_shifted_tables(base_encode, base_decode, *center, shifted_encode, shifted_decode);
+}
+
+// Two symbols per lookup over 12 stream bits, in table-index space (so it is
+// valid for every center).  The second symbol is present only when both codes
+// are direct and fit in the 12 bits together.
+__global__ void __launch_bounds__(kTableThreads)
+pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pair_table) {
+  for (int i = threadIdx.x; i < kPairEntries; i += blockDim.x) {
+    const int32_t first = decode[i & kFirstMask];
+    uint32_t entry;
+    if (first == 0) {
+      entry = kSlow | kEscape;
+    } else {
+      const uint32_t len0 = (uint32_t)first & 255u;
+      const uint32_t idx0 = ((uint32_t)first >> 8) & 255u;
+      entry = idx0 | (len0 << 24);
+      const int32_t second = decode[(i >> len0) & kFirstMask];
+      const uint32_t len1 = (uint32_t)second & 255u;
+      if (second != 0 && len0 + len1 <= (uint32_t)kPairBits) {
+        entry |= (((uint32_t)second >> 8) & 255u) << 8 | (len0 + len1) << 16;
+      } else {
+        entry |= kSlow | (len0 << 16);
+      }
+    }
+    pair_table[i] = entry;
+  }
+}
+
+}  // namespace lct
+
+extern "C" {
+
+int lct_build_pair_table(const int32_t* decode_table, int rare_length, uint32_t* pair_table,
+                         void* stream) {
+  if (decode_table == nullptr || pair_table == nullptr) return LCT_E_NULL_POINTER;
+  if (rare_length < 0 || rare_length > 8) return LCT_E_BAD_ARGUMENT;
+  lct::pair_table_kernel<<<1, lct::kTableThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      decode_table, pair_table);
+  return (int)cudaGetLastError();
+}
+
+int lct_center_and_tables(const void* src, int64_t logical_numel, int precomputed,
+                          const int32_t* encode_table, const int32_t* decode_table,
+                          int32_t* center, int32_t* shifted_encode, int32_t* shifted_decode,
+                          void* stream) {
+  if (encode_table == nullptr || decode_table == nullptr || center == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (logical_numel < 0) return LCT_E_BAD_ARGUMENT;
+  if (logical_numel > 0 && src == nullptr) return LCT_E_NULL_POINTER;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (precomputed)
+    lct::center_and_tables_kernel<true><<<1, lct::kTableThreads, 0, s>>>(
+        src, logical_numel, encode_table, decode_table, center, shifted_encode, shifted_decode);
+  else
+    lct::center_and_tables_kernel<false><<<1, lct::kTableThreads, 0, s>>>(
+        src, logical_numel, encode_table, decode_table, center, shifted_encode, shifted_decode);
+  return (int)cudaGetLastError();
+}
+
+int lct_shift_tables(const int32_t* encode_table, const int32_t* decode_table,
+                     const int32_t* center, int32_t* shifted_encode, int32_t* shifted_decode,
+                     void* stream) {
+  if (center == nullptr) return LCT_E_NULL_POINTER;
+  if ((shifted_encode != nullptr && encode_table == nullptr) ||
+      (shifted_decode != nullptr && decode_table == nullptr))
+    return LCT_E_NULL_POINTER;
+  lct::shift_tables_kernel<<<1, lct::kTableThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      encode_table, decode_table, center, shifted_encode, shifted_decode);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,275 @@
+"""One Python wrapper per launch of the CUDA library.
+
+The function names and argument meaning follow the reference's launch layer
+(``LCT/kernels/dispatch.py:16-361``), which is what its host pipelines call;
+here each wrapper forwards raw device pointers, sizes and the current CUDA
+stream to the C ABI declared in ``include/lct_b200.h``.  Differences from the
+reference's layer, all invisible to the pipelines' results:
+
+* overflow rows of the fused operations are handled inside ``pointwise_dense``
+  and ``dual_scale_add`` (no separate fix-up launch, no per-stream maps);
+* the decoders use a two-symbol lookup table per codebook, cached per device
+  by ``pair_table_for``;
+* every launch goes to ``torch.cuda.current_stream`` of the tensors' device.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import config
+from ..compression.huffman_tables import FIRST_BITS, get_distribution_tables
+from . import _lib
+from ._lib import Operand, Overflow
+from .backends import FallbackStorage
+
+OP_ADD, OP_MULTIPLY, OP_SCALAR_MUL_ADD = 0, 1, 2
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    if tensor is None or tensor.numel() == 0:
+        return None
+    return tensor.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(tensor: torch.Tensor) -> torch.device:
+    if tensor.device.type != "cuda":
+        raise ValueError(f"LCT kernel dispatch requires a CUDA device, got {tensor.device}")
+    config.check()
+    return tensor.device
+
+
+class _on:
+    """Make ``device`` current for a launch when it is not already."""
+
+    def __init__(self, device: torch.device):
+        self.guard = None
+        if device.index is not None and device.index != torch.cuda.current_device():
+            self.guard = torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+# ---------------------------------------------------------------------------
+# Table preparation
+# ---------------------------------------------------------------------------
+
+_pair_tables: dict = {}
+
+
+def pair_table_for(distribution, device: torch.device) -> torch.Tensor:
+    """Two-symbol decode table (uint32[4096] stored as int32) of a codebook on ``device``."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    key = (distribution.family, distribution.param, distribution.mean, distribution.zero_prob, device)
+    table = _pair_tables.get(key)
+    if table is None:
+        _, decode_table, rare_length = get_distribution_tables(distribution, device)
+        table = torch.empty(4096, dtype=torch.int32, device=device)
+        with _on(device):
+            _lib.check(_lib.load().lct_build_pair_table(
+                decode_table.data_ptr(), rare_length, table.data_ptr(), _stream(device)),
+                "lct_build_pair_table")
+        _pair_tables[key] = table
+    return table
+
+
+def shift_encoding_table(encode_table, center, shifted_encode, decode_table, shifted_decode=None):
+    """Tables for a known center (device int32 scalar)."""
+    device = _require_cuda(encode_table)
+    if shifted_decode is None:
+        shifted_decode = torch.empty_like(decode_table)
+    with _on(device):
+        _lib.check(_lib.load().lct_shift_tables(
+            encode_table.data_ptr(), decode_table.data_ptr(), center.data_ptr(),
+            shifted_encode.data_ptr(), shifted_decode.data_ptr(), _stream(device)),
+            "lct_shift_tables")
+
+
+def estimate_and_shift_encoding_table(source, center, size, encode_table, shifted_encode,
+                                      decode_table, shifted_decode, sample_size, precomputed):
+    """Sample the center of ``source`` and build both shifted tables in one launch.
+
+    ``sample_size`` is implied (min(size, 4096)) and only checked.
+    """
+    device = _require_cuda(source)
+    if sample_size != min(size, 4096):
+        raise ValueError("the center is always estimated from min(size, 4096) samples")
+    if shifted_decode is None:
+        shifted_decode = torch.empty_like(decode_table)
+    with _on(device):
+        _lib.check(_lib.load().lct_center_and_tables(
+            _ptr(source), size, int(precomputed), encode_table.data_ptr(), decode_table.data_ptr(),
+            center.data_ptr(), shifted_encode.data_ptr(), shifted_decode.data_ptr(),
+            _stream(device)), "lct_center_and_tables")
+
+
+def shift_decoding_table(decode_table, center):
+    """Return a center-shifted copy of ``decode_table``."""
+    device = _require_cuda(decode_table)
+    shifted = torch.empty(1 << FIRST_BITS, dtype=torch.int32, device=device)
+    with _on(device):
+        _lib.check(_lib.load().lct_shift_tables(
+            None, decode_table.data_ptr(), center.data_ptr(), None, shifted.data_ptr(),
+            _stream(device)), "lct_shift_tables")
+    return shifted
+
+
+# ---------------------------------------------------------------------------
+# Encode pipeline
+# ---------------------------------------------------------------------------
+
+def encode_kernel(source, side, encoded, encode_table, extra_starts, summaries, size, streams, *,
+                  precomputed, logical_numel, block_symbols, lanes, steps, fixed_words,
+                  write_summary=True):
+    """Field split + Huffman encode; always writes the per-block overflow summaries."""
+    device = _require_cuda(source)
+    if lanes != 256 or streams != size // block_symbols * lanes:
+        raise ValueError("inconsistent stream geometry")
+    with _on(device):
+        _lib.check(_lib.load().lct_encode(
+            _ptr(source), _ptr(side), encoded.data_ptr(), encode_table.data_ptr(),
+            extra_starts.data_ptr(), summaries.data_ptr(), size, logical_numel, block_symbols,
+            steps, fixed_words, int(precomputed), _stream(device)), "lct_encode")
+
+
+def prefix_allocate(summaries, counts, descriptor, buffer, blocks, buffered, max_free_regions):
+    """Scan the block summaries and, when ``buffered``, reserve the shared arena region."""
+    device = _require_cuda(summaries)
+    storage = buffer._storage.data_ptr() if buffered else None
+    with _on(device):
+        _lib.check(_lib.load().lct_scan_allocate(
+            summaries.data_ptr(), counts.data_ptr(), descriptor.data_ptr() if buffered else None,
+            storage, blocks, max_free_regions, _stream(device)), "lct_scan_allocate")
+
+
+def compact_extra(source, storage: FallbackStorage, final_counts, n_blocks, n_elements, *,
+                  precomputed, buffered, logical_numel, block_symbols, lanes, steps,
+                  extra_starts, summaries, n_streams, build_meta=True):
+    """Write overflow entries, raw exponent tails and the per-block metadata."""
+    device = _require_cuda(source)
+    if not build_meta:
+        raise ValueError("only the summaries path (build_meta=True) exists")
+    with _on(device):
+        _lib.check(_lib.load().lct_compact_tails(
+            _ptr(source), _ptr(storage.lanes), _ptr(storage.starts), _ptr(storage.tail),
+            storage.descriptor.data_ptr() if buffered else None, final_counts.data_ptr(),
+            storage.blocks.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(),
+            n_elements, logical_numel, block_symbols, steps, int(precomputed), _stream(device)),
+            "lct_compact_tails")
+
+
+# ---------------------------------------------------------------------------
+# Decode and fused operations
+# ---------------------------------------------------------------------------
+
+def fallback_tail_args(storage: FallbackStorage | None) -> Overflow:
+    """The overflow view the decoders take (``struct lct_overflow``)."""
+    view = Overflow()
+    if storage is None:
+        view.mode = 0
+        return view
+    view.lanes = _ptr(storage.lanes)
+    view.starts = _ptr(storage.starts)
+    view.tail = _ptr(storage.tail)
+    view.count = _ptr(storage.count)
+    view.blocks = _ptr(storage.blocks)
+    view.base = int(storage.base)
+    if storage.buffered:
+        view.descriptor = storage.descriptor.data_ptr()
+        view.mode = 2
+    else:
+        view.mode = 1
+    return view
+
+
+def make_operand(encoded, side, shifted_decode, center, pair_table, overflow: Overflow) -> Operand:
+    operand = Operand()
+    operand.encoded = encoded.data_ptr()
+    operand.side = side.data_ptr()
+    operand.shifted_decode = shifted_decode.data_ptr() if shifted_decode is not None else None
+    operand.center = center.data_ptr()
+    operand.pair_table = pair_table.data_ptr()
+    operand.overflow = overflow
+    return operand
+
+
+def decode_kernel(operand: Operand, output, size, *, logical_numel, block_symbols, lanes, steps,
+                  fixed_words, rare_length):
+    """Decode into ``output`` (int16[logical_numel]); overflow tails restored in the same launch."""
+    device = _require_cuda(output)
+    with _on(device):
+        _lib.check(_lib.load().lct_decode(
+            ctypes.byref(operand), output.data_ptr(), size, logical_numel, block_symbols, steps,
+            fixed_words, rare_length, _stream(device)), "lct_decode")
+
+
+def pointwise_dense(operand: Operand, other, output, auxiliary, n_elements, alpha, beta, *,
+                    op, alpha_is_one, beta_is_one, compressed_output, rare_length, logical_numel,
+                    block_symbols, lanes, steps, fixed_words):
+    """Decode one compressed operand, apply ``op`` against dense ``other``, emit dense BF16
+    or (side bytes, exponent bytes) for re-encoding."""
+    device = _require_cuda(output)
+    with _on(device):
+        _lib.check(_lib.load().lct_pointwise(
+            ctypes.byref(operand), other.data_ptr(), output.data_ptr(),
+            auxiliary.data_ptr() if compressed_output else None,
+            alpha.data_ptr() if alpha is not None else None,
+            beta.data_ptr() if beta is not None else None,
+            op, int(alpha_is_one), int(beta_is_one), int(compressed_output), n_elements,
+            logical_numel, block_symbols, steps, fixed_words, rare_length, _stream(device)),
+            "lct_pointwise")
+
+
+def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements, *,
+                   compressed_output, rare_length, logical_numel, block_symbols, lanes, steps,
+                   fixed_words):
+    """``alpha * compA + compB`` in one launch."""
+    device = _require_cuda(output)
+    with _on(device):
+        _lib.check(_lib.load().lct_dual_scale_add(
+            ctypes.byref(a), ctypes.byref(b), output.data_ptr(),
+            auxiliary.data_ptr() if compressed_output else None, alpha.data_ptr(),
+            int(compressed_output), n_elements, logical_numel, block_symbols, steps, fixed_words,
+            rare_length, _stream(device)), "lct_dual_scale_add")
+
+
+# ---------------------------------------------------------------------------
+# Shared arena
+# ---------------------------------------------------------------------------
+
+def buffer_reset(storage, max_free_regions, capacity_bytes):
+    device = _require_cuda(storage)
+    with _on(device):
+        _lib.check(_lib.load().lct_buffer_reset(
+            storage.data_ptr(), max_free_regions, capacity_bytes, _stream(device)),
+            "lct_buffer_reset")
+
+
+def buffer_allocate(storage, requested_bytes, item_count, item_bytes, descriptor, max_free_regions):
+    device = _require_cuda(storage)
+    with _on(device):
+        _lib.check(_lib.load().lct_buffer_allocate(
+            storage.data_ptr(), requested_bytes.data_ptr(),
+            item_count.data_ptr() if item_count is not None else None, item_bytes,
+            descriptor.data_ptr(), max_free_regions, _stream(device)), "lct_buffer_allocate")
+
+
+def buffer_free(storage, descriptor, status, max_free_regions):
+    device = _require_cuda(storage)
+    with _on(device):
+        _lib.check(_lib.load().lct_buffer_free(
+            storage.data_ptr(), descriptor.data_ptr(), status.data_ptr(), max_free_regions,
+            _stream(device)), "lct_buffer_free")

@@ -1,0 +1,181 @@
+"""Device-resident first-fit arena shared by the overflow tails of many tensors.
+
+API and memory layout of the reference's ``TensorBuffer`` (``LCT/tensor_buffer.py:13-201``):
+one uint8 tensor holding ``free_starts[R] | free_sizes[R] | free_count | lock |
+generation | pad | payload[capacity]``; requests and results stay on the device as
+``[offset, aligned_size, status, generation]`` descriptors, so allocating and
+freeing never synchronise the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .kernels import dispatch
+
+_ALIGNMENT = 16
+
+
+@dataclass(frozen=True)
+class Allocation:
+    """A device ``[offset, aligned_size, status, generation]`` descriptor and its arena."""
+
+    descriptor: torch.Tensor
+    owner: object
+
+    @property
+    def offset(self) -> torch.Tensor:
+        return self.descriptor[0]
+
+    @property
+    def size(self) -> torch.Tensor:
+        return self.descriptor[1]
+
+    @property
+    def status(self) -> torch.Tensor:
+        return self.descriptor[2]
+
+    @property
+    def generation(self) -> torch.Tensor:
+        return self.descriptor[3]
+
+
+@torch.library.custom_op("lct::tensor_buffer_free", mutates_args=("storage", "descriptor"))
+def tensor_buffer_free(storage: torch.Tensor, descriptor: torch.Tensor,
+                       max_free_regions: int) -> torch.Tensor:
+    """Opaque to ``torch.compile`` like the reference's op (``LCT/kernels/tensor_buffer_ops.py:5-20``)."""
+    status = torch.empty(1, dtype=torch.int32, device=storage.device)
+    dispatch.buffer_free(storage, descriptor, status, max_free_regions)
+    return status
+
+
+@tensor_buffer_free.register_fake
+def _tensor_buffer_free_fake(storage, descriptor, max_free_regions):
+    return torch.empty(1, dtype=torch.int32, device=storage.device)
+
+
+class TensorBuffer:
+    """First-fit allocator living in device memory.
+
+    ``max_free_regions`` bounds the free list (a power of two).  Callers hand the
+    payload tensor (``data``) and the device descriptors straight to kernels.
+    """
+
+    def __init__(self, capacity_bytes: int, *, max_free_regions: int = 256,
+                 device: torch.device | str | None = None) -> None:
+        if capacity_bytes > torch.iinfo(torch.int32).max:
+            raise ValueError("capacity_bytes must fit in int32")
+        if max_free_regions <= 0 or max_free_regions & (max_free_regions - 1):
+            raise ValueError("max_free_regions must be a positive power of two")
+        self.capacity_bytes = int(capacity_bytes)
+        self.max_free_regions = int(max_free_regions)
+        regions = self.max_free_regions
+        self._metadata_bytes = self._align(8 * regions + 12)
+        self._storage = torch.zeros(self._metadata_bytes + self.capacity_bytes, dtype=torch.uint8,
+                                    device=torch.device(device or "cuda"))
+        self.device = self._storage.device
+        words = self._storage[: 8 * regions + 12].view(torch.int32)
+        self._free_starts = words[:regions]
+        self._free_sizes = words[regions: 2 * regions]
+        self._free_count = words[2 * regions: 2 * regions + 1]
+        self._lock = words[2 * regions + 1: 2 * regions + 2]
+        self._generation = words[2 * regions + 2: 2 * regions + 3]
+        self._data = self._storage[self._metadata_bytes:]
+        self.reset()
+
+    @staticmethod
+    def _align(nbytes: int) -> int:
+        return -(-nbytes // _ALIGNMENT) * _ALIGNMENT
+
+    @property
+    def data(self) -> torch.Tensor:
+        """The payload bytes descriptors index into."""
+        return self._data
+
+    def _request(self, value: torch.Tensor) -> torch.Tensor:
+        value = value.reshape(-1)[:1]
+        if value.dtype != torch.int32 or value.device != self.device:
+            value = value.to(device=self.device, dtype=torch.int32)
+        return value
+
+    def allocate(self, nbytes: torch.Tensor) -> Allocation:
+        """Reserve ``nbytes`` (a one-element device integer tensor) without a host sync."""
+        descriptor = torch.empty(4, dtype=torch.int32, device=self.device)
+        dispatch.buffer_allocate(self._storage, self._request(nbytes), None, 0, descriptor,
+                                 self.max_free_regions)
+        return Allocation(descriptor, self)
+
+    def allocate_with_items(self, payload_bytes: torch.Tensor, item_count: torch.Tensor,
+                            item_bytes: int) -> Allocation:
+        """Reserve ``payload_bytes + item_count * item_bytes``, both read on the device."""
+        if item_bytes <= 0:
+            raise ValueError("item_bytes must be positive")
+        descriptor = torch.empty(4, dtype=torch.int32, device=self.device)
+        dispatch.buffer_allocate(self._storage, self._request(payload_bytes),
+                                 self._request(item_count), int(item_bytes), descriptor,
+                                 self.max_free_regions)
+        return Allocation(descriptor, self)
+
+    def free(self, allocation: Allocation) -> torch.Tensor:
+        """Return a region; the result is a device status word (0 ok, 3 list full, 4 stale/invalid)."""
+        if allocation.owner is not self:
+            raise ValueError("allocation belongs to a different allocator")
+        if allocation.descriptor.device != self.device:
+            raise ValueError("allocation must be on the allocator device")
+        return tensor_buffer_free(self._storage, allocation.descriptor, self.max_free_regions)
+
+    def reset(self) -> None:
+        """Forget every allocation; outstanding descriptors become stale (generation bump)."""
+        dispatch.buffer_reset(self._storage, self.max_free_regions, self.capacity_bytes)
+
+
+def _free_regions_snapshot(buffer: TensorBuffer) -> list[tuple[int, int]]:
+    """Synchronise and return the free list as ``(start, size)`` pairs."""
+    regions = buffer.max_free_regions
+    words = buffer._storage[: buffer._metadata_bytes].view(torch.int32).cpu().tolist()
+    count = words[2 * regions]
+    if not 0 <= count <= regions:
+        raise RuntimeError(f"corrupt free-list count: {count}")
+    return [(words[i], words[regions + i]) for i in range(count)]
+
+
+def verify_buffer(buffer: TensorBuffer) -> None:
+    """Synchronise and check the free list: sorted, in range, non-empty, coalesced."""
+    end_of_previous = 0
+    free_bytes = 0
+    for start, size in _free_regions_snapshot(buffer):
+        if size <= 0 or start < end_of_previous or start + size > buffer.capacity_bytes:
+            raise RuntimeError(f"invalid free region: [{start}, {start + size})")
+        if start == end_of_previous and end_of_previous != 0:
+            raise RuntimeError("adjacent free regions were not coalesced")
+        end_of_previous = start + size
+        free_bytes += size
+    if free_bytes > buffer.capacity_bytes:
+        raise RuntimeError("free regions exceed payload capacity")
+
+
+def visualize_buffer(buffer: TensorBuffer | None, width: int = 80) -> str:
+    """Synchronise and draw the payload as ``#`` (used) and ``.`` (free) cells."""
+    if buffer is None:
+        return ""
+    if width < 8:
+        raise ValueError("width must be at least 8")
+    capacity = buffer.capacity_bytes
+    free = _free_regions_snapshot(buffer)
+    used = capacity - sum(size for _, size in free)
+    cells = ["#"] * width
+    for start, size in free:
+        first = start * width // capacity
+        last = ((start + size) * width + capacity - 1) // capacity
+        for cell in range(first, min(width, max(first + 1, last))):
+            cells[cell] = "."
+    spans = [f"[{start}, {start + size})" for start, size in free]
+    if len(spans) > 8:
+        spans = spans[:4] + ["..."] + spans[-4:]
+    return "\n".join((
+        f"payload: {used}/{capacity} B used ({used / capacity:.1%}); {len(free)} free region(s)",
+        f"0 [{''.join(cells)}] {capacity}",
+        "# used  . free",
+        f"free: {', '.join(spans) or 'none'}",
+    ))
