@@ -1,0 +1,348 @@
+"""Benchmark of the BF16 lossless codec hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): BASELINE configuration 2 - an 8192 x 8192 BF16 weight-like tensor, i.i.d.
+Laplace(0, 0.02) from a fixed seed with 1e-4 of the entries multiplied by 100,
+``Distribution(LAPLACE, param=0.02)``, CLEAN layout, overflow tails in a shared ``TensorBuffer``.
+One step = one ``compress`` + one ``decompress`` of that tensor.  With N > 1 every rank runs the
+same step on its own tensor (independent tensors partitioned across GPUs: weak scaling, no
+data-path collective), and the value is the aggregate over ranks against the slowest rank's time.
+
+Reported value: GB/s of BF16 data through the codec = (2N bytes encoded + 2N bytes decoded) /
+(encode time + decode time), device time from CUDA events with the inputs already in HBM and the
+L2 flushed before each timed phase.  ``e2e`` is the same figure through the public API with host
+buffers: pinned-host -> device copy of the input, compress, decompress, device -> pinned-host copy
+of the decoded tensor, all inside the timed region.
+
+``--impl reference`` times the CPU implementation of the same path: the C restatement of the
+reference's kernels (the oracle), on all host threads, on the same tensor.  The reference itself
+is a Python/Triton project with no CPU build; its interpreter mode needs the reference checkout,
+which does not exist on the benchmark machine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _path in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")):
+    if _path not in sys.path:
+        sys.path.insert(0, _path)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+ROWS = COLS = 8192
+METRIC = "codec_bf16_gbps_per_gpu"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+L2_FLUSH_BYTES = 512 << 20
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None until a capture of that kernel has been taken.
+NCU_TRAFFIC_BYTES = {"lct_encode": None, "lct_decode": None}
+
+
+def make_workload(seed: int) -> torch.Tensor:
+    """Configuration-2 tensor, generated on the CPU so every machine sees the same bits."""
+    n = ROWS * COLS
+    g = torch.Generator().manual_seed(seed)
+    u = torch.rand(n, generator=g) - 0.5
+    values = -0.02 * torch.sign(u) * torch.log1p(-2.0 * u.abs())
+    del u
+    outliers = torch.rand(n, generator=g) < 1e-4
+    values[outliers] *= 100.0
+    return values.to(torch.bfloat16).reshape(ROWS, COLS)
+
+
+def peak_hbm_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.process = None
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def finish(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        out, _ = self.process.communicate(timeout=10)
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def distributed_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    elif n_gpus > 1:
+        raise SystemExit("launch N > 1 with torch.distributed.run (one process per GPU)")
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def cpu_leg(bits: np.ndarray, threads: int, budget_s: float, max_steps: int):
+    """Time the CPU restatement on the whole workload; returns (GB/s, steps, threads used)."""
+    from helpers import oracle_compress
+    from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
+    from oracle import lct_oracle as oracle
+
+    oracle.build()
+    used = oracle.set_threads(threads)
+    dist = Distribution(DistType.LAPLACE, param=0.02)
+    arena = oracle.new_arena(64 << 20)
+    elapsed, steps = 0.0, 0
+    while steps < max_steps and (steps == 0 or elapsed < budget_s):
+        t0 = time.perf_counter()
+        c = oracle_compress(oracle, bits, dist, arena)
+        y = oracle.decompress(c)
+        elapsed += time.perf_counter() - t0
+        oracle.buf_free(arena, c["descriptor"])
+        steps += 1
+    assert np.array_equal(y, bits)
+    return 2 * bits.nbytes * steps / elapsed / 1e9, steps, used, elapsed / steps * 1e3
+
+
+def run_reference(args, rank: int):
+    """CPU arm: rank 0 alone works; one JSON line."""
+    if rank != 0:
+        return
+    bits = make_workload(1).view(torch.int16).numpy().reshape(-1)
+    cores = os.cpu_count() or 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_leg(bits, cores, 0.0, 1)
+    value, steps, used, ms = cpu_leg(bits, cores, 1e9, args.steps)
+    sample = f"full workload ({ROWS}x{COLS} BF16), {steps} step(s) of compress+decompress"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "config2: 8192x8192 BF16 Laplace(0,0.02)+1e-4 outliers x100, "
+                               "LAPLACE/CLEAN, shared arena", "where": "host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args, rank: int, world: int, local: int):
+    from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
+    from losslessly_compressed_tensors_b200.kernels import dispatch
+    from losslessly_compressed_tensors_b200.operations import compress, decompress
+    from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
+
+    dist_cfg = Distribution(DistType.LAPLACE, param=0.02)
+    host_x = make_workload(1 + rank).pin_memory()
+    x = host_x.cuda(non_blocking=True)
+    buffer = TensorBuffer(64 << 20)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    n = x.numel()
+    bf16_bytes = 2 * n
+
+    # Correctness of what is about to be timed, and the byte counts for the roofline.
+    c = compress(x, dist_cfg, buffer)
+    y = decompress(c)
+    assert torch.equal(y.view(torch.int16), x.view(torch.int16)), "round trip is not bit-exact"
+    memory = c.memory_size()
+    tails = int(c.fallback_used.item()) + 2 * int(c.fallback_count.item())
+    algorithmic = bf16_bytes + c.sign_mantissa.numel() + (c.data.numel() - 4) * 4 + tails
+    c.free()
+    del y
+
+    def event():
+        return torch.cuda.Event(enable_timing=True)
+
+    def one_step(timed):
+        flush.zero_()
+        e0, e1, e2, e3 = event(), event(), event(), event()
+        e0.record()
+        c = compress(x, dist_cfg, buffer)
+        e1.record()
+        flush.zero_()
+        e2.record()
+        y = decompress(c)
+        e3.record()
+        c.free()
+        if timed is not None:
+            timed.append((e0, e1, e2, e3))
+        return y
+
+    for _ in range(args.warmup):
+        one_step(None)
+    barrier(world)
+    sampler = ClockSampler(local) if rank == 0 else None
+    spans = []
+    with dispatch.LaunchTrace(timed=("lct_encode", "lct_decode")) as trace:
+        wall0 = time.perf_counter()
+        for _ in range(args.steps):
+            one_step(spans)
+        barrier(world)
+        wall = time.perf_counter() - wall0
+    clocks = sampler.finish() if sampler else None
+    enc_ms = [a.elapsed_time(b) for a, b, _, _ in spans]
+    dec_ms = [c_.elapsed_time(d) for _, _, c_, d in spans]
+    step_ms = (sum(enc_ms) + sum(dec_ms)) / args.steps
+    step_ms = max_over_ranks(step_ms, world)
+    value = world * 2 * bf16_bytes / (step_ms * 1e-3) / 1e9
+    launches = trace.count
+    kernel_ms = {name: statistics.mean(trace.milliseconds(name)) for name in trace.timed}
+
+    # End to end: host buffers in, host buffers out, copies inside the timed region.
+    host_out = torch.empty_like(host_x).pin_memory()
+    dev_in = torch.empty_like(x)
+
+    def e2e_step():
+        dev_in.copy_(host_x, non_blocking=True)
+        c = compress(dev_in, dist_cfg, buffer)
+        y = decompress(c)
+        host_out.copy_(y, non_blocking=True)
+        c.free()
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    barrier(world)
+    e2e_steps = max(3, min(args.steps, 10))
+    s, t = event(), event()
+    s.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(s.elapsed_time(t) / e2e_steps, world)
+    assert torch.equal(host_out.view(torch.int16), host_x.view(torch.int16))
+    verify_buffer(buffer)
+    e2e_value = world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        return
+    peak, peak_kind = peak_hbm_gbs()
+    kernels = {}
+    for name, ms in kernel_ms.items():
+        achieved = algorithmic / (ms * 1e-3) / 1e9
+        kernels[name] = {"ms": ms, "achieved": achieved, "frac": achieved / peak,
+                         "bf16_gbps": bf16_bytes / (ms * 1e-3) / 1e9}
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    roofline = {
+        "kernel": dominant, "bound": "hbm", "achieved": kernels[dominant]["achieved"], "peak": peak,
+        "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s",
+        "frac": kernels[dominant]["frac"], "traffic": NCU_TRAFFIC_BYTES[dominant],
+        "algorithmic_bytes": algorithmic,
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "config2: 8192x8192 BF16 Laplace(0,0.02)+1e-4 outliers x100, "
+                               "LAPLACE/CLEAN, shared arena; step = compress + decompress",
+                   "l2": f"flushed ({L2_FLUSH_BYTES >> 20} MiB write) before each timed phase",
+                   "parallelism": f"{world} independent tensor(s), one per GPU"},
+        "encode_ms": statistics.mean(enc_ms), "decode_ms": statistics.mean(dec_ms),
+        "encode_gbps": bf16_bytes / statistics.mean(enc_ms) / 1e6,
+        "decode_gbps": bf16_bytes / statistics.mean(dec_ms) / 1e6,
+        "compression_ratio": bf16_bytes / memory, "memory_size": memory,
+        "wall_ms_per_step": wall / args.steps * 1e3,
+        "roofline": roofline, "kernels": kernels,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu:
+        bits = host_x.view(torch.int16).numpy().reshape(-1)
+        cpu_value, cpu_steps, used, _ = cpu_leg(bits, 1, 15.0, 8)
+        line["cpu_baseline"] = {
+            "value": cpu_value, "unit": UNIT, "cores": used, "kind": "port",
+            "sample": f"full workload, {cpu_steps} step(s) of compress+decompress, "
+                      f"single-threaded C restatement of the reference kernels"}
+    print(json.dumps(line))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")))
+        return
+    args.warmup = max(args.warmup, 3)
+    rank, world, local = distributed_setup(args.gpus)
+    try:
+        run_ours(args, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -33,10 +33,6 @@ def _ptr(tensor: torch.Tensor | None) -> int | None:
     return tensor.data_ptr()
 
 
-def _stream(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
-
-
 def _require_cuda(tensor: torch.Tensor) -> torch.device:
     if tensor.device.type != "cuda":
         raise ValueError(f"LCT kernel dispatch requires a CUDA device, got {tensor.device}")
@@ -61,6 +57,51 @@ class _on:
             self.guard.__exit__(*exc)
 
 
+class LaunchTrace:
+    """Counts library launches and, for the entry points named in ``timed``, brackets each
+    launch with CUDA events on the launching stream (used by the benchmark's roofline)."""
+
+    def __init__(self, timed=()):
+        self.timed = set(timed)
+        self.count = 0
+        self.events: dict[str, list] = {name: [] for name in self.timed}
+
+    def __enter__(self):
+        global _trace
+        self._previous, _trace = _trace, self
+        return self
+
+    def __exit__(self, *exc):
+        global _trace
+        _trace = self._previous
+
+    def milliseconds(self, name: str) -> list[float]:
+        """Durations of the timed launches of ``name`` (call after synchronising)."""
+        return [start.elapsed_time(end) for start, end in self.events[name]]
+
+
+_trace: LaunchTrace | None = None
+
+
+def _call(name: str, device: torch.device, *args) -> None:
+    """Launch entry point ``name`` on the current stream of ``device``."""
+    function = getattr(_lib.load(), name)
+    trace = _trace
+    with _on(device):
+        stream = torch.cuda.current_stream(device)
+        if trace is not None:
+            trace.count += 1
+            if name in trace.timed:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record(stream)
+                code = function(*args, stream.cuda_stream)
+                end.record(stream)
+                trace.events[name].append((start, end))
+                _lib.check(code, name)
+                return
+        _lib.check(function(*args, stream.cuda_stream), name)
+
+
 # ---------------------------------------------------------------------------
 # Table preparation
 # ---------------------------------------------------------------------------
@@ -78,10 +119,9 @@ def pair_table_for(distribution, device: torch.device) -> torch.Tensor:
     if table is None:
         _, decode_table, rare_length = get_distribution_tables(distribution, device)
         table = torch.empty(4096, dtype=torch.int32, device=device)
-        with _on(device):
-            _lib.check(_lib.load().lct_build_pair_table(
-                decode_table.data_ptr(), rare_length, table.data_ptr(), _stream(device)),
-                "lct_build_pair_table")
+        _call(
+            "lct_build_pair_table", device,
+            decode_table.data_ptr(), rare_length, table.data_ptr())
         _pair_tables[key] = table
     return table
 
@@ -91,11 +131,10 @@ def shift_encoding_table(encode_table, center, shifted_encode, decode_table, shi
     device = _require_cuda(encode_table)
     if shifted_decode is None:
         shifted_decode = torch.empty_like(decode_table)
-    with _on(device):
-        _lib.check(_lib.load().lct_shift_tables(
-            encode_table.data_ptr(), decode_table.data_ptr(), center.data_ptr(),
-            shifted_encode.data_ptr(), shifted_decode.data_ptr(), _stream(device)),
-            "lct_shift_tables")
+    _call(
+        "lct_shift_tables", device,
+        encode_table.data_ptr(), decode_table.data_ptr(), center.data_ptr(),
+        shifted_encode.data_ptr(), shifted_decode.data_ptr())
 
 
 def estimate_and_shift_encoding_table(source, center, size, encode_table, shifted_encode,
@@ -109,21 +148,19 @@ def estimate_and_shift_encoding_table(source, center, size, encode_table, shifte
         raise ValueError("the center is always estimated from min(size, 4096) samples")
     if shifted_decode is None:
         shifted_decode = torch.empty_like(decode_table)
-    with _on(device):
-        _lib.check(_lib.load().lct_center_and_tables(
-            _ptr(source), size, int(precomputed), encode_table.data_ptr(), decode_table.data_ptr(),
-            center.data_ptr(), shifted_encode.data_ptr(), shifted_decode.data_ptr(),
-            _stream(device)), "lct_center_and_tables")
+    _call(
+        "lct_center_and_tables", device,
+        _ptr(source), size, int(precomputed), encode_table.data_ptr(), decode_table.data_ptr(),
+        center.data_ptr(), shifted_encode.data_ptr(), shifted_decode.data_ptr())
 
 
 def shift_decoding_table(decode_table, center):
     """Return a center-shifted copy of ``decode_table``."""
     device = _require_cuda(decode_table)
     shifted = torch.empty(1 << FIRST_BITS, dtype=torch.int32, device=device)
-    with _on(device):
-        _lib.check(_lib.load().lct_shift_tables(
-            None, decode_table.data_ptr(), center.data_ptr(), None, shifted.data_ptr(),
-            _stream(device)), "lct_shift_tables")
+    _call(
+        "lct_shift_tables", device,
+        None, decode_table.data_ptr(), center.data_ptr(), None, shifted.data_ptr())
     return shifted
 
 
@@ -138,21 +175,21 @@ def encode_kernel(source, side, encoded, encode_table, extra_starts, summaries, 
     device = _require_cuda(source)
     if lanes != 256 or streams != size // block_symbols * lanes:
         raise ValueError("inconsistent stream geometry")
-    with _on(device):
-        _lib.check(_lib.load().lct_encode(
-            _ptr(source), _ptr(side), encoded.data_ptr(), encode_table.data_ptr(),
-            extra_starts.data_ptr(), summaries.data_ptr(), size, logical_numel, block_symbols,
-            steps, fixed_words, int(precomputed), _stream(device)), "lct_encode")
+    _call(
+        "lct_encode", device,
+        _ptr(source), _ptr(side), encoded.data_ptr(), encode_table.data_ptr(),
+        extra_starts.data_ptr(), summaries.data_ptr(), size, logical_numel, block_symbols,
+        steps, fixed_words, int(precomputed))
 
 
 def prefix_allocate(summaries, counts, descriptor, buffer, blocks, buffered, max_free_regions):
     """Scan the block summaries and, when ``buffered``, reserve the shared arena region."""
     device = _require_cuda(summaries)
     storage = buffer._storage.data_ptr() if buffered else None
-    with _on(device):
-        _lib.check(_lib.load().lct_scan_allocate(
-            summaries.data_ptr(), counts.data_ptr(), descriptor.data_ptr() if buffered else None,
-            storage, blocks, max_free_regions, _stream(device)), "lct_scan_allocate")
+    _call(
+        "lct_scan_allocate", device,
+        summaries.data_ptr(), counts.data_ptr(), descriptor.data_ptr() if buffered else None,
+        storage, blocks, max_free_regions)
 
 
 def compact_extra(source, storage: FallbackStorage, final_counts, n_blocks, n_elements, *,
@@ -162,13 +199,12 @@ def compact_extra(source, storage: FallbackStorage, final_counts, n_blocks, n_el
     device = _require_cuda(source)
     if not build_meta:
         raise ValueError("only the summaries path (build_meta=True) exists")
-    with _on(device):
-        _lib.check(_lib.load().lct_compact_tails(
-            _ptr(source), _ptr(storage.lanes), _ptr(storage.starts), _ptr(storage.tail),
-            storage.descriptor.data_ptr() if buffered else None, final_counts.data_ptr(),
-            storage.blocks.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(),
-            n_elements, logical_numel, block_symbols, steps, int(precomputed), _stream(device)),
-            "lct_compact_tails")
+    _call(
+        "lct_compact_tails", device,
+        _ptr(source), _ptr(storage.lanes), _ptr(storage.starts), _ptr(storage.tail),
+        storage.descriptor.data_ptr() if buffered else None, final_counts.data_ptr(),
+        storage.blocks.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(),
+        n_elements, logical_numel, block_symbols, steps, int(precomputed))
 
 
 # ---------------------------------------------------------------------------
@@ -210,10 +246,10 @@ def decode_kernel(operand: Operand, output, size, *, logical_numel, block_symbol
                   fixed_words, rare_length):
     """Decode into ``output`` (int16[logical_numel]); overflow tails restored in the same launch."""
     device = _require_cuda(output)
-    with _on(device):
-        _lib.check(_lib.load().lct_decode(
-            ctypes.byref(operand), output.data_ptr(), size, logical_numel, block_symbols, steps,
-            fixed_words, rare_length, _stream(device)), "lct_decode")
+    _call(
+        "lct_decode", device,
+        ctypes.byref(operand), output.data_ptr(), size, logical_numel, block_symbols, steps,
+        fixed_words, rare_length)
 
 
 def pointwise_dense(operand: Operand, other, output, auxiliary, n_elements, alpha, beta, *,
@@ -222,15 +258,14 @@ def pointwise_dense(operand: Operand, other, output, auxiliary, n_elements, alph
     """Decode one compressed operand, apply ``op`` against dense ``other``, emit dense BF16
     or (side bytes, exponent bytes) for re-encoding."""
     device = _require_cuda(output)
-    with _on(device):
-        _lib.check(_lib.load().lct_pointwise(
-            ctypes.byref(operand), other.data_ptr(), output.data_ptr(),
-            auxiliary.data_ptr() if compressed_output else None,
-            alpha.data_ptr() if alpha is not None else None,
-            beta.data_ptr() if beta is not None else None,
-            op, int(alpha_is_one), int(beta_is_one), int(compressed_output), n_elements,
-            logical_numel, block_symbols, steps, fixed_words, rare_length, _stream(device)),
-            "lct_pointwise")
+    _call(
+        "lct_pointwise", device,
+        ctypes.byref(operand), other.data_ptr(), output.data_ptr(),
+        auxiliary.data_ptr() if compressed_output else None,
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        op, int(alpha_is_one), int(beta_is_one), int(compressed_output), n_elements,
+        logical_numel, block_symbols, steps, fixed_words, rare_length)
 
 
 def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements, *,
@@ -238,12 +273,12 @@ def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements,
                    fixed_words):
     """``alpha * compA + compB`` in one launch."""
     device = _require_cuda(output)
-    with _on(device):
-        _lib.check(_lib.load().lct_dual_scale_add(
-            ctypes.byref(a), ctypes.byref(b), output.data_ptr(),
-            auxiliary.data_ptr() if compressed_output else None, alpha.data_ptr(),
-            int(compressed_output), n_elements, logical_numel, block_symbols, steps, fixed_words,
-            rare_length, _stream(device)), "lct_dual_scale_add")
+    _call(
+        "lct_dual_scale_add", device,
+        ctypes.byref(a), ctypes.byref(b), output.data_ptr(),
+        auxiliary.data_ptr() if compressed_output else None, alpha.data_ptr(),
+        int(compressed_output), n_elements, logical_numel, block_symbols, steps, fixed_words,
+        rare_length)
 
 
 # ---------------------------------------------------------------------------
@@ -252,24 +287,22 @@ def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements,
 
 def buffer_reset(storage, max_free_regions, capacity_bytes):
     device = _require_cuda(storage)
-    with _on(device):
-        _lib.check(_lib.load().lct_buffer_reset(
-            storage.data_ptr(), max_free_regions, capacity_bytes, _stream(device)),
-            "lct_buffer_reset")
+    _call(
+        "lct_buffer_reset", device,
+        storage.data_ptr(), max_free_regions, capacity_bytes)
 
 
 def buffer_allocate(storage, requested_bytes, item_count, item_bytes, descriptor, max_free_regions):
     device = _require_cuda(storage)
-    with _on(device):
-        _lib.check(_lib.load().lct_buffer_allocate(
-            storage.data_ptr(), requested_bytes.data_ptr(),
-            item_count.data_ptr() if item_count is not None else None, item_bytes,
-            descriptor.data_ptr(), max_free_regions, _stream(device)), "lct_buffer_allocate")
+    _call(
+        "lct_buffer_allocate", device,
+        storage.data_ptr(), requested_bytes.data_ptr(),
+        item_count.data_ptr() if item_count is not None else None, item_bytes,
+        descriptor.data_ptr(), max_free_regions)
 
 
 def buffer_free(storage, descriptor, status, max_free_regions):
     device = _require_cuda(storage)
-    with _on(device):
-        _lib.check(_lib.load().lct_buffer_free(
-            storage.data_ptr(), descriptor.data_ptr(), status.data_ptr(), max_free_regions,
-            _stream(device)), "lct_buffer_free")
+    _call(
+        "lct_buffer_free", device,
+        storage.data_ptr(), descriptor.data_ptr(), status.data_ptr(), max_free_regions)

@@ -11,14 +11,29 @@
  * Each function names the reference source it follows (paths are relative to
  * the reference project's root).
  *
- * Build: gcc -O2 -fPIC -shared -ffp-contract=off -o liblct_oracle.so lct_oracle.c -lm
+ * Build: gcc -O2 -fopenmp -fPIC -shared -ffp-contract=off -o liblct_oracle.so lct_oracle.c -lm
  */
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define LANES 256
+
+/* Blocks are independent, so the block loops below run in parallel when built
+ * with OpenMP; results do not depend on the thread count. */
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 #define FIRST_MASK 1023
 
 /* ------------------------------------------------------------------------ */
@@ -100,6 +115,7 @@ void orc_encode(const void *src, int precomputed, int64_t logical_numel, int64_t
                 uint8_t *extra_starts, int32_t *summaries) {
   int64_t blocks = (size + block_symbols - 1) / block_symbols;
   int64_t streams = blocks * LANES;
+#pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < blocks; ++b) {
     int count = 0, total = 0;
     for (int lane = 0; lane < LANES; ++lane) {
@@ -191,6 +207,7 @@ void orc_compact(const void *src, int precomputed, int64_t logical_numel, int64_
                  uint8_t *starts, int64_t start_off, uint8_t *tail, int64_t tail_off,
                  int32_t *blocks_out) {
   int64_t blocks = (size + block_symbols - 1) / block_symbols;
+#pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < blocks; ++b) {
     int32_t count = summaries[b];
     int32_t first = summaries[2 * blocks + b];
@@ -312,8 +329,9 @@ void orc_decode(const int32_t *encoded, const uint8_t *side, const int32_t *shif
                 int64_t start_off, const uint8_t *tail, int64_t tail_off, int16_t *out) {
   int64_t blocks = (size + block_symbols - 1) / block_symbols;
   int64_t streams = blocks * LANES;
-  block_overflow map;
+#pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < blocks; ++b) {
+    block_overflow map;
     map_block(&map, steps, blocks_meta, blocks, b, lanes, lane_off, starts, start_off);
     for (int lane = 0; lane < LANES; ++lane) {
       lane_reader r;
@@ -411,8 +429,9 @@ void orc_pointwise(const int32_t *encoded, const uint8_t *side, const int32_t *s
                    int beta_is_one, uint16_t *dense_out, uint8_t *side_out, uint8_t *exp_out) {
   int64_t blocks = (size + block_symbols - 1) / block_symbols;
   int64_t streams = blocks * LANES;
-  block_overflow map;
+#pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < blocks; ++b) {
+    block_overflow map;
     map_block(&map, steps, blocks_meta, blocks, b, lanes, lane_off, starts, start_off);
     for (int lane = 0; lane < LANES; ++lane) {
       lane_reader r;
@@ -456,8 +475,9 @@ void orc_dual(const int32_t *a_encoded, const uint8_t *a_side, const int32_t *a_
               int fw, float alpha, uint16_t *dense_out, uint8_t *side_out, uint8_t *exp_out) {
   int64_t blocks = (size + block_symbols - 1) / block_symbols;
   int64_t streams = blocks * LANES;
-  block_overflow ma, mb;
+#pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < blocks; ++b) {
+    block_overflow ma, mb;
     map_block(&ma, steps, a_meta, blocks, b, a_lanes, a_lane_off, a_starts, a_start_off);
     map_block(&mb, steps, b_meta, blocks, b, b_lanes, b_lane_off, b_starts, b_start_off);
     for (int lane = 0; lane < LANES; ++lane) {

@@ -29,7 +29,8 @@ def build(force: bool = False) -> str:
     if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
         os.makedirs(os.path.dirname(_SO), exist_ok=True)
         subprocess.check_call(
-            ["gcc", "-O2", "-fPIC", "-std=c11", "-ffp-contract=off", "-shared", "-o", _SO, src, "-lm"]
+            ["gcc", "-O2", "-fopenmp", "-fPIC", "-std=c11", "-ffp-contract=off", "-shared", "-o", _SO,
+             src, "-lm"]
         )
     return _SO
 
@@ -43,7 +44,13 @@ def lib() -> ctypes.CDLL:
         _lib = ctypes.CDLL(build())
         _lib.orc_estimate_center.restype = ctypes.c_int
         _lib.orc_buf_free.restype = ctypes.c_int
+        _lib.orc_set_threads.restype = ctypes.c_int
     return _lib
+
+
+def set_threads(n: int) -> int:
+    """Use ``n`` host threads for the block loops (0 = leave as is); returns the count in use."""
+    return int(lib().orc_set_threads(ctypes.c_int(n)))
 
 
 def _p(array):

@@ -1,0 +1,76 @@
+"""The C-ABI library: it loads without a GPU, exports every symbol the header declares,
+and rejects bad arguments before touching the device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from losslessly_compressed_tensors_b200.kernels import _lib
+
+
+@pytest.fixture(scope="module")
+def library():
+    from losslessly_compressed_tensors_b200 import build
+
+    build.build()
+    return _lib.load()
+
+
+def test_every_declared_symbol_is_exported(library):
+    header = open(os.path.join(ROOT, "include", "lct_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(lct_[a-z_]+)\s*\(", header))
+    assert len(declared) >= 14
+    assert declared == set(_lib.EXPORTS)
+    for name in declared:
+        assert getattr(library, name) is not None, name
+
+
+def test_identity_and_error_text(library):
+    assert library.lct_version().decode().startswith("lct-b200 ")
+    assert b"sm_100a" in library.lct_version()
+    assert library.lct_error_string(0) == b"success"
+    for code in (-1, -2, -3, -4, -5):
+        assert library.lct_error_string(code) not in (b"", b"unknown lct error")
+
+
+def test_argument_validation_needs_no_device(library):
+    fake = ctypes.c_void_p(0x1000)  # never dereferenced: validation fails first
+    # geometry that is not a supported layout
+    assert library.lct_encode(fake, fake, fake, fake, fake, fake, 65536, 65536, 65536, 100, 25, 0,
+                              None) == -1
+    # size not a whole number of blocks
+    assert library.lct_encode(fake, fake, fake, fake, fake, fake, 1000, 1000, 65536, 256, 25, 0,
+                              None) == -4
+    # null pointers
+    assert library.lct_encode(None, fake, fake, fake, fake, fake, 65536, 65536, 65536, 256, 25, 0,
+                              None) == -2
+    assert library.lct_scan_allocate(None, fake, None, None, 1, 256, None) == -2
+    # misaligned payload
+    odd = ctypes.c_void_p(0x1004)
+    assert library.lct_encode(fake, fake, odd, fake, fake, fake, 65536, 65536, 65536, 256, 25, 0,
+                              None) == -3
+    operand = _lib.Operand()
+    assert library.lct_decode(ctypes.byref(operand), fake, 65536, 65536, 65536, 256, 25, 8,
+                              None) == -2
+    assert library.lct_buffer_reset(fake, 3, 1024, None) == -4  # regions not a power of two
+    assert library.lct_buffer_free(fake, None, fake, 256, None) == -2
+
+
+def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_library", None)
+    monkeypatch.setattr(_lib, "LIBRARY_PATH", str(tmp_path / "absent.so"))
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib.load()
+
+
+def test_cpu_tensors_are_rejected():
+    """No CPU path: the host API refuses anything that is not on a CUDA device."""
+    import torch
+    from losslessly_compressed_tensors_b200.kernels import dispatch
+
+    with pytest.raises(ValueError, match="CUDA device"):
+        dispatch.shift_decoding_table(torch.zeros(1024, dtype=torch.int32),
+                                      torch.zeros(1, dtype=torch.int32))
