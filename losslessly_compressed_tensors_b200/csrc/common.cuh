@@ -2,16 +2,20 @@
 //
 // Data layout recap.  A block is `steps` rows of 256 lanes.  Lane l at global
 // row n holds logical element n*256 + (l ^ (n & 254)); rows 2k and 2k+1 share
-// one XOR mask, and the mask is even, so lanes 2p/2p+1 stay adjacent.  Inside
-// every kernel a block is processed in tiles of 32 rows that pass through a
-// shared-memory tile of exponent bytes kept in COLUMN (logical) order:
+// one XOR mask, and the mask is even, so lanes 2p/2p+1 stay adjacent.  The
+// mask's bits 5..7 move a warp's 32 lanes to another aligned group of 32
+// columns and its bits 1..4 permute them inside that group, so in every row
+// one warp's lanes cover exactly one 64-byte segment of the BF16 row.  That
+// makes the whole pipeline warp-private: a warp (32 lanes of a block) passes
+// its data through its own shared-memory tile, 32 rows at a time, kept in
+// COLUMN (logical) order:
 //
-//     tile[pair p][column c] = e(row 2p, c) | e(row 2p+1, c) << 8      (uint16)
+//     tile[pair p][column c in the warp's group] = e(row 2p, c) | e(row 2p+1, c) << 8
 //
 // One side of each kernel works lane-wise (a thread owns a lane and walks its
 // bit stream, touching tile[p][lane ^ mask]); the other side works row-wise
-// (a thread owns 8 adjacent columns of a row pair, so global loads and stores
-// are 128-bit and a warp covers one full 512-byte row).
+// (a thread owns 8 adjacent columns of a row pair: 128-bit global accesses,
+// four threads per 64-byte segment).  Only __syncwarp() separates the two.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -22,7 +26,8 @@ namespace lct {
 
 constexpr int kLanes = 256;
 constexpr int kThreads = 256;           // one thread per lane
-constexpr int kTilePairs = 16;          // row pairs per shared-memory tile (32 rows)
+constexpr int kWarps = kThreads / 32;
+constexpr int kTilePairs = 16;          // row pairs per warp tile (32 rows)
 constexpr int kTileRows = 2 * kTilePairs;
 constexpr int kPairBits = 12;           // stream bits indexing the two-symbol table
 constexpr int kPairEntries = 1 << kPairBits;
@@ -45,15 +50,21 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t select
 __device__ __forceinline__ uint32_t pair_selector_low(uint32_t q) { return 0x3210u ^ (q * 0x2222u); }
 __device__ __forceinline__ uint32_t pair_selector_high(uint32_t q) { return 0x7654u ^ (q * 0x2222u); }
 
-// [s0, e0, s1, e1] bytes (side, exponent of two neighbours) -> two BF16 bit patterns.
-__device__ __forceinline__ uint32_t join_bf16x2(uint32_t x) {
-  return ((x >> 1) & 0x7F807F80u) | (x & 0x007F007Fu) | ((x << 8) & 0x80008000u);
+// Four exponent bytes + four side bytes (same columns) -> the low bytes and the
+// high bytes of the four BF16 values: low = mantissa | exponent bit 0 << 7,
+// high = sign | exponent >> 1.
+__device__ __forceinline__ uint32_t bf16_low_bytes(uint32_t e4, uint32_t s4) {
+  return (s4 & 0x7F7F7F7Fu) | ((e4 << 7) & 0x80808080u);
 }
-
-// Two BF16 bit patterns -> exponent bytes in bytes 0 and 2 / side bytes in bytes 0 and 2.
-__device__ __forceinline__ uint32_t exponents_of(uint32_t w) { return w >> 7; }
-__device__ __forceinline__ uint32_t sides_of(uint32_t w) {
-  return (w & 0x007F007Fu) | ((w >> 8) & 0x00800080u);
+__device__ __forceinline__ uint32_t bf16_high_bytes(uint32_t e4, uint32_t s4) {
+  return (s4 & 0x80808080u) | ((e4 >> 1) & 0x7F7F7F7Fu);
+}
+// ... and back: low/high bytes of four BF16 values -> exponent bytes, side bytes.
+__device__ __forceinline__ uint32_t exponent_bytes(uint32_t low4, uint32_t high4) {
+  return ((low4 >> 7) & 0x01010101u) | ((high4 << 1) & 0xFEFEFEFEu);
+}
+__device__ __forceinline__ uint32_t side_bytes(uint32_t low4, uint32_t high4) {
+  return (low4 & 0x7F7F7F7Fu) | (high4 & 0x80808080u);
 }
 
 // Table index (0 = exact zero, else centred exponent delta) -> raw exponent byte.

@@ -1,13 +1,23 @@
 // Table-driven decoder and the fused decode -> pointwise operation kernels.
 //
-// One CTA (256 threads) per codec block.  Per 32-row tile:
-//   lane phase  - thread = lane: walks its bit stream two symbols per lookup
-//                 (12-bit two-symbol table in shared memory, remapped to this
-//                 tensor's center at CTA start) and drops the exponent bytes
-//                 into the column-ordered shared tile;
-//   row phase   - thread = 8 columns of a row pair: 128-bit read of the tile,
-//                 64-bit reads of the side bytes, byte permutes to rebuild the
-//                 BF16 words, optional arithmetic, 128-bit streaming stores.
+// One CTA (256 threads) per codec block; after a short block-wide prologue
+// every warp runs on its own (see common.cuh: a warp's 32 lanes own one
+// 64-byte segment of every row).
+//
+// Prologue: the block's payload tile (fixed_words rows of 256 words) is copied
+// into shared memory with cp.async while the codebook's two-symbol table is
+// remapped to this tensor's center and the block's overflow map is expanded.
+//
+// Per 32-row tile, per warp:
+//   lane phase - thread = lane: reads the two payload words under its absolute
+//                bit position from shared memory, funnel-shifts, looks 12 bits
+//                up in the two-symbol table, advances.  No per-lane refill
+//                branch; the only divergent path is the rare "not two direct
+//                symbols" entry, decoded one symbol at a time;
+//   row phase  - thread = 8 columns of a row pair: 128-bit read of the tile,
+//                64-bit side-byte loads (issued before the lane phase), four
+//                bytes at a time rebuilt into BF16 low/high bytes, optional
+//                arithmetic, 128-bit streaming stores.
 // Overflow lanes switch from the bit stream to their raw tail bytes at their
 // recorded start step, inside the same launch.
 #include "common.cuh"
@@ -41,124 +51,116 @@ struct Shape {
   int rare_length;
 };
 
+// Fixed part of one operand's shared memory; the payload image
+// (fixed_words + 1 rows of 256 words, last row zero) follows it.
 struct __align__(16) DecodeShared {
   uint32_t table[kPairEntries];
-  uint16_t tile[kTilePairs * kLanes];
+  uint16_t tile[kWarps][kTilePairs * 32];
   uint8_t index_to_byte[256];
   uint16_t overflow_start[kLanes];
   int32_t overflow_offset[kLanes];
-  int scan[33];
+  int scan[36];
 };
 
-// Per-lane read position in the fixed payload: a 64-bit window plus one
-// prefetched word, so the dependent lookup chain never waits on HBM.
-struct LaneReader {
-  const uint32_t* next_ptr;  // word index word + 2 of this stream
-  int64_t stride;            // words between consecutive words of one stream
-  uint32_t lo, hi, next;
-  int shift, word, fixed_words;
+static size_t operand_shared_bytes(int fixed_words) {
+  return sizeof(DecodeShared) + (size_t)(fixed_words + 1) * kLanes * 4;
+}
 
-  __device__ __forceinline__ void open(const uint32_t* encoded, int64_t streams, int64_t stream,
-                                       int fw) {
-    const uint32_t* p = encoded + stream;
-    stride = streams;
-    fixed_words = fw;
-    lo = __ldcs(p);
-    hi = __ldcs(p + streams);
-    next = fw > 2 ? __ldcs(p + 2 * streams) : 0u;
-    next_ptr = p + 3 * streams;
-    shift = 0;
-    word = 0;
-  }
-  __device__ __forceinline__ void advance(int bits) {
-    shift += bits;
-    if (shift >= 32) {
-      shift -= 32;
-      lo = hi;
-      hi = next;
-      ++word;
-      next = (word + 2 < fixed_words) ? __ldcs(next_ptr) : 0u;
-      next_ptr += stride;
-    }
+__device__ __forceinline__ void cp_async_16(void* shared_dst, const void* global_src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(shared_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(global_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+// Absolute bit position of one lane in the shared payload image.
+struct BitReader {
+  const uint32_t* column;  // &payload[lane]
+  int pos;
+  int last_word;           // fixed_words - 1: reads never leave the image
+
+  __device__ __forceinline__ uint32_t peek(int at) const {
+    const uint32_t* p = column + min(at >> 5, last_word) * kLanes;
+    return __funnelshift_r(p[0], p[kLanes], at);  // shift amount is taken modulo 32
   }
 };
 
-// Decode one symbol at bit offset 0 of `bits` (>= 16 valid bits).
-__device__ __forceinline__ void one_symbol(uint32_t bits, const DecodeShared& sh, int rare_length,
-                                           uint32_t* exponent_byte, int* length) {
+// Decode one symbol at bit position `at`.
+__device__ __forceinline__ uint32_t one_symbol(const BitReader& r, int at, const DecodeShared& sh,
+                                               int rare_length, int* length) {
+  const uint32_t bits = r.peek(at);
   const uint32_t entry = sh.table[bits & (kPairEntries - 1)];
   if (entry & kEscape) {
-    *exponent_byte = sh.index_to_byte[(bits >> rare_length) & 255u];
     *length = rare_length + 8;
-  } else {
-    *exponent_byte = entry & 255u;
-    *length = (int)((entry >> 24) & 15u);
+    return sh.index_to_byte[(bits >> rare_length) & 255u];
   }
+  *length = (int)((entry >> 24) & 15u);
+  return entry & 255u;
 }
 
 // Pair whose table entry is not "two direct symbols": decode them one by one.
-__device__ __noinline__ uint32_t slow_pair(uint32_t lo, uint32_t hi, int shift,
-                                           const DecodeShared& sh, int rare_length, int* consumed) {
-  const uint64_t window = (((uint64_t)hi << 32) | lo) >> shift;
-  uint32_t e0, e1;
+// Returns the pair in table-entry form (bytes: first, second, bits consumed).
+__device__ __forceinline__ uint32_t slow_pair(const BitReader& r, const DecodeShared& sh,
+                                              int rare_length) {
   int l0, l1;
-  one_symbol((uint32_t)window, sh, rare_length, &e0, &l0);
-  one_symbol((uint32_t)(window >> l0), sh, rare_length, &e1, &l1);
-  *consumed = l0 + l1;
-  return e0 | (e1 << 8);
+  const uint32_t e0 = one_symbol(r, r.pos, sh, rare_length, &l0);
+  const uint32_t e1 = one_symbol(r, r.pos + l0, sh, rare_length, &l1);
+  return e0 | (e1 << 8) | ((uint32_t)(l0 + l1) << 16);
 }
 
 // Lane phase for one tile.  `coded` = number of leading steps of this lane that
 // are in the bit stream (its overflow start or its valid length, whichever is
 // first); steps from `tail_from` on come from the raw tail.
-__device__ __forceinline__ void decode_tile_rows(LaneReader& r, DecodeShared& sh, uint16_t* tile,
-                                                 int lane, int64_t row0, int step0, int coded,
-                                                 int tail_from, const uint8_t* tail_bytes,
-                                                 int rare_length) {
-  if (step0 + kTileRows <= coded) {
-#pragma unroll 4
+__device__ __forceinline__ void decode_tile_rows(BitReader& r, const DecodeShared& sh,
+                                                 uint16_t* tile, int lane32, int64_t row0,
+                                                 int step0, int coded, int tail_from,
+                                                 const uint8_t* tail_bytes, int rare_length) {
+  const int row_bits = (int)(row0 + step0);
+  if (__all_sync(0xFFFFFFFFu, step0 + kTileRows <= coded)) {
+#pragma unroll
     for (int p = 0; p < kTilePairs; ++p) {
-      const int mask = (int)((row0 + step0 + 2 * p) & 254);
-      const uint32_t bits = __funnelshift_r(r.lo, r.hi, r.shift);
-      uint32_t entry = sh.table[bits & (kPairEntries - 1)];
-      int consumed;
-      if ((int32_t)entry < 0) {
-        entry = slow_pair(r.lo, r.hi, r.shift, sh, rare_length, &consumed);
-      } else {
-        consumed = (int)prmt(entry, 0, 0x4442);
-      }
-      tile[p * kLanes + (lane ^ mask)] = (uint16_t)entry;
-      r.advance(consumed);
+      const int column = lane32 ^ ((row_bits + 2 * p) & 30);
+      uint32_t entry = sh.table[r.peek(r.pos) & (kPairEntries - 1)];
+      if ((int32_t)entry < 0) entry = slow_pair(r, sh, rare_length);
+      r.pos += (int)prmt(entry, 0, 0x4442);
+      tile[p * 32 + column] = (uint16_t)entry;
     }
     return;
   }
   for (int p = 0; p < kTilePairs; ++p) {
     const int step = step0 + 2 * p;
-    const int mask = (int)((row0 + step) & 254);
+    const int column = lane32 ^ ((row_bits + 2 * p) & 30);
     uint32_t pair = 0;
     if (step + 2 <= coded) {
-      int consumed;
-      pair = slow_pair(r.lo, r.hi, r.shift, sh, rare_length, &consumed);
-      r.advance(consumed);
+      pair = sh.table[r.peek(r.pos) & (kPairEntries - 1)];
+      if ((int32_t)pair < 0) pair = slow_pair(r, sh, rare_length);
+      r.pos += (int)prmt(pair, 0, 0x4442);
     } else if (step >= tail_from) {
       const uint32_t t0 = tail_bytes[step - tail_from], t1 = tail_bytes[step + 1 - tail_from];
       pair = ((t0 + 127u) & 255u) | (((t1 + 127u) & 255u) << 8);
     } else if (step + 1 == coded) {
-      const uint64_t window = (((uint64_t)r.hi << 32) | r.lo) >> r.shift;
-      uint32_t e0;
       int l0;
-      one_symbol((uint32_t)window, sh, rare_length, &e0, &l0);
-      r.advance(l0);
-      pair = e0;
+      pair = one_symbol(r, r.pos, sh, rare_length, &l0);
+      r.pos += l0;
     }
-    tile[p * kLanes + (lane ^ mask)] = (uint16_t)pair;
+    tile[p * 32 + column] = (uint16_t)pair;
   }
 }
 
-// CTA prologue: center-specific symbol table and this block's overflow map.
-__device__ __forceinline__ void prepare_block(DecodeShared& sh, const OperandView& a,
-                                              const Shape& g, int64_t block) {
+// CTA prologue: stage the payload, build the center-specific symbol table and
+// this block's overflow map.  Ends with a block barrier.
+__device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payload,
+                                              const OperandView& a, const Shape& g, int64_t block) {
   const int tid = threadIdx.x;
+  // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
+  const uint32_t* rows = a.encoded + block * kLanes;
+  for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
+    const int w = i >> 6, c = (i & 63) * 4;
+    cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
+  }
+  payload[g.fixed_words * kLanes + tid] = 0u;
+
   const int center = *a.center;
   sh.index_to_byte[tid] = (uint8_t)index_to_exponent_byte((uint32_t)tid, center);
   sh.overflow_start[tid] = (uint16_t)g.steps;
@@ -205,6 +207,7 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, const OperandVie
       }
     }
   }
+  cp_async_wait_all();
   __syncthreads();
 }
 
@@ -213,23 +216,41 @@ __device__ __forceinline__ const uint8_t* tail_origin(const OperandView& a) {
   return a.tail + a.base;
 }
 
-// Rebuild the 8 BF16 values (4 words, column order) of one row from the tile
-// words and that row's side bytes.  `second_row` picks the high exponent byte.
+// Where one row-phase unit (row pair p of the tile, 8-column subgroup j4 of the
+// warp's 32 columns) lives in the tensor.
+struct UnitPlace {
+  int64_t logical;   // element offset of the top row's first column
+  int64_t storage;   // byte offset of the top row's first lane in the side bytes
+  uint32_t q;        // pair permutation between lane order and column order
+};
+
+__device__ __forceinline__ UnitPlace place_unit(int warp, int p, int j4, int64_t row0, int step0,
+                                                int64_t block_base) {
+  const int step = step0 + 2 * p;
+  const int64_t row = row0 + step;
+  const int mask = (int)(row & 254);
+  UnitPlace u;
+  u.logical = row * kLanes + 32 * (warp ^ (mask >> 5)) + 8 * j4;
+  u.storage = block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (mask & 0x18));
+  u.q = (uint32_t)(mask >> 1) & 3u;
+  return u;
+}
+
+// Rebuild the 8 BF16 values (4 words, column order) of one row from the unit's
+// tile words and that row's side bytes (lane order).
 __device__ __forceinline__ void join_row(const uint4& tile_words, uint2 side_lane_order, uint32_t q,
                                          bool second_row, uint32_t out[4]) {
-  const uint32_t p0 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_low(q));
-  const uint32_t p1 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_high(q));
-  if (!second_row) {
-    out[0] = join_bf16x2(prmt(tile_words.x, p0, 0x2504));
-    out[1] = join_bf16x2(prmt(tile_words.y, p0, 0x2706));
-    out[2] = join_bf16x2(prmt(tile_words.z, p1, 0x2504));
-    out[3] = join_bf16x2(prmt(tile_words.w, p1, 0x2706));
-  } else {
-    out[0] = join_bf16x2(prmt(tile_words.x, p0, 0x3514));
-    out[1] = join_bf16x2(prmt(tile_words.y, p0, 0x3716));
-    out[2] = join_bf16x2(prmt(tile_words.z, p1, 0x3514));
-    out[3] = join_bf16x2(prmt(tile_words.w, p1, 0x3716));
-  }
+  const uint32_t pick = second_row ? 0x7531u : 0x6420u;
+  const uint32_t e03 = prmt(tile_words.x, tile_words.y, pick);
+  const uint32_t e47 = prmt(tile_words.z, tile_words.w, pick);
+  const uint32_t s03 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_low(q));
+  const uint32_t s47 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_high(q));
+  const uint32_t l03 = bf16_low_bytes(e03, s03), h03 = bf16_high_bytes(e03, s03);
+  const uint32_t l47 = bf16_low_bytes(e47, s47), h47 = bf16_high_bytes(e47, s47);
+  out[0] = prmt(l03, h03, 0x5140);
+  out[1] = prmt(l03, h03, 0x7362);
+  out[2] = prmt(l47, h47, 0x5140);
+  out[3] = prmt(l47, h47, 0x7362);
 }
 
 // ---------------------------------------------------------------------------
@@ -240,48 +261,43 @@ __global__ void __launch_bounds__(kThreads)
 decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
+  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(DecodeShared));
   const int64_t block = blockIdx.x;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
-  prepare_block(sh, a, g, block);
+  const int64_t block_base = block * (int64_t)g.block_symbols;
+  prepare_block(sh, payload, a, g, block);
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  LaneReader reader;
-  reader.open(a.encoded, g.streams, block * kLanes + tid, g.fixed_words);
-  const bool full_block = (block + 1) * (int64_t)g.block_symbols <= g.logical_numel;
-  const uint8_t* side_block = a.side + block * (int64_t)g.block_symbols;
+  BitReader reader{payload + tid, 0, g.fixed_words - 1};
+  const bool full_block = block_base + g.block_symbols <= g.logical_numel;
+  uint16_t* tile = sh.tile[warp];
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    // Side bytes of the two row-phase units of this thread, fetched early.
+    // Side bytes of this thread's two row-phase units, requested before the lane phase.
+    UnitPlace place[2];
     uint2 side_regs[2][2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (tid >> 5) + 8 * u;
-      const int j = tid & 31;
-      const int step = step0 + 2 * p;
-      const int mask = (int)((row0 + step) & 254);
-      const int lane_group = (8 * j) ^ (mask & 0xF8);
-      const uint8_t* s = side_block + (int64_t)step * kLanes + lane_group;
+      place[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base);
+      const uint8_t* s = a.side + place[u].storage;
       side_regs[u][0] = __ldcs(reinterpret_cast<const uint2*>(s));
       side_regs[u][1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
     }
-    decode_tile_rows(reader, sh, sh.tile, tid, row0, step0, coded, tail_from, tail_bytes,
+    decode_tile_rows(reader, sh, tile, lane32, row0, step0, coded, tail_from, tail_bytes,
                      g.rare_length);
-    __syncthreads();
+    __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (tid >> 5) + 8 * u;
-      const int j = tid & 31;
-      const int64_t row = row0 + step0 + 2 * p;
-      const uint32_t q = (uint32_t)(row >> 1) & 3u;
-      const uint4 words = *reinterpret_cast<const uint4*>(&sh.tile[p * kLanes + 8 * j]);
+      const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
+      const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
       uint32_t top[4], bottom[4];
-      join_row(words, side_regs[u][0], q, false, top);
-      join_row(words, side_regs[u][1], q, true, bottom);
-      const int64_t at = row * kLanes + 8 * j;
+      join_row(words, side_regs[u][0], place[u].q, false, top);
+      join_row(words, side_regs[u][1], place[u].q, true, bottom);
+      const int64_t at = place[u].logical;
       if (full_block || at + kLanes + 8 <= g.logical_numel) {
         __stcs(reinterpret_cast<uint4*>(out + at), make_uint4(top[0], top[1], top[2], top[3]));
         __stcs(reinterpret_cast<uint4*>(out + at + kLanes),
@@ -296,7 +312,7 @@ decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
         }
       }
     }
-    __syncthreads();
+    __syncwarp();
   }
 }
 
@@ -380,19 +396,19 @@ __device__ __forceinline__ void store_row(uint32_t r[4], bool compressed, void* 
     for (int i = 0; i < 8; ++i)
       if (at + i >= numel) r[i >> 1] &= (i & 1) ? 0x0000FFFFu : 0xFFFF0000u;
   }
-  const uint32_t e01 = prmt(exponents_of(r[0]), exponents_of(r[1]), 0x6420);
-  const uint32_t e23 = prmt(exponents_of(r[2]), exponents_of(r[3]), 0x6420);
-  const uint32_t c01 = prmt(sides_of(r[0]), sides_of(r[1]), 0x6420);
-  const uint32_t c23 = prmt(sides_of(r[2]), sides_of(r[3]), 0x6420);
+  const uint32_t l03 = prmt(r[0], r[1], 0x6420), h03 = prmt(r[0], r[1], 0x7531);
+  const uint32_t l47 = prmt(r[2], r[3], 0x6420), h47 = prmt(r[2], r[3], 0x7531);
+  const uint32_t e03 = exponent_bytes(l03, h03), e47 = exponent_bytes(l47, h47);
+  const uint32_t c03 = side_bytes(l03, h03), c47 = side_bytes(l47, h47);
   const uint2 side_lane_order =
-      make_uint2(prmt(c01, c23, pair_selector_low(q)), prmt(c01, c23, pair_selector_high(q)));
+      make_uint2(prmt(c03, c47, pair_selector_low(q)), prmt(c03, c47, pair_selector_high(q)));
   *reinterpret_cast<uint2*>(static_cast<uint8_t*>(output) + storage_at) = side_lane_order;
   if (at + 8 <= numel) {
-    *reinterpret_cast<uint2*>(auxiliary + at) = make_uint2(e01, e23);
+    *reinterpret_cast<uint2*>(auxiliary + at) = make_uint2(e03, e47);
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      if (at + i < numel) auxiliary[at + i] = (uint8_t)((i < 4 ? e01 : e23) >> (8 * (i & 3)));
+      if (at + i < numel) auxiliary[at + i] = (uint8_t)((i < 4 ? e03 : e47) >> (8 * (i & 3)));
   }
 }
 
@@ -400,15 +416,19 @@ template <bool kDual>
 __global__ void __launch_bounds__(kThreads)
 pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restrict__ other,
                  bool other_vector_ok, void* output, uint8_t* auxiliary, OpSpec spec,
-                 bool compressed) {
+                 bool compressed, uint32_t operand_bytes) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
-  DecodeShared& sh_b = *reinterpret_cast<DecodeShared*>(smem_raw + (kDual ? sizeof(DecodeShared) : 0));
+  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(DecodeShared));
+  unsigned char* second = smem_raw + (kDual ? operand_bytes : 0u);
+  DecodeShared& sh_b = *reinterpret_cast<DecodeShared*>(second);
+  uint32_t* payload_b = reinterpret_cast<uint32_t*>(second + sizeof(DecodeShared));
   const int64_t block = blockIdx.x;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
-  prepare_block(sh, a, g, block);
-  if (kDual) prepare_block(sh_b, b, g, block);
+  const int64_t block_base = block * (int64_t)g.block_symbols;
+  prepare_block(sh, payload, a, g, block);
+  if (kDual) prepare_block(sh_b, payload_b, b, g, block);
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
@@ -416,48 +436,42 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
   const int a_tail_from = sh.overflow_start[tid];
   const int a_coded = min(valid, a_tail_from);
   const uint8_t* a_tail = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  LaneReader reader_a, reader_b;
-  reader_a.open(a.encoded, g.streams, block * kLanes + tid, g.fixed_words);
+  BitReader reader_a{payload + tid, 0, g.fixed_words - 1};
+  BitReader reader_b{payload_b + tid, 0, g.fixed_words - 1};
   int b_tail_from = g.steps, b_coded = 0;
   const uint8_t* b_tail = nullptr;
   if (kDual) {
     b_tail_from = sh_b.overflow_start[tid];
     b_coded = min(valid, b_tail_from);
     b_tail = b.mode ? tail_origin(b) + sh_b.overflow_offset[tid] : nullptr;
-    reader_b.open(b.encoded, g.streams, block * kLanes + tid, g.fixed_words);
   }
-  const int64_t block_base = block * (int64_t)g.block_symbols;
+  uint16_t* tile = sh.tile[warp];
+  uint16_t* tile_b = sh_b.tile[warp];
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader_a, sh, sh.tile, tid, row0, step0, a_coded, a_tail_from, a_tail,
+    decode_tile_rows(reader_a, sh, tile, lane32, row0, step0, a_coded, a_tail_from, a_tail,
                      g.rare_length);
     if (kDual)
-      decode_tile_rows(reader_b, sh_b, sh_b.tile, tid, row0, step0, b_coded, b_tail_from, b_tail,
+      decode_tile_rows(reader_b, sh_b, tile_b, lane32, row0, step0, b_coded, b_tail_from, b_tail,
                        g.rare_length);
-    __syncthreads();
+    __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (tid >> 5) + 8 * u;
-      const int j = tid & 31;
-      const int step = step0 + 2 * p;
-      const int64_t row = row0 + step;
-      const int mask = (int)(row & 254);
-      const uint32_t q = (uint32_t)(mask >> 1) & 3u;
-      const int lane_group = (8 * j) ^ (mask & 0xF8);
-      const int64_t storage_at = block_base + (int64_t)step * kLanes + lane_group;
-      const int64_t at = row * kLanes + 8 * j;
-      const uint4 words = *reinterpret_cast<const uint4*>(&sh.tile[p * kLanes + 8 * j]);
+      const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
+      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base);
+      const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
       uint4 words_b = make_uint4(0, 0, 0, 0);
-      if (kDual) words_b = *reinterpret_cast<const uint4*>(&sh_b.tile[p * kLanes + 8 * j]);
+      if (kDual) words_b = *reinterpret_cast<const uint4*>(&tile_b[p * 32 + 8 * j4]);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int64_t s_at = storage_at + half * kLanes;
-        const int64_t l_at = at + half * kLanes;
+        const int64_t s_at = place.storage + half * kLanes;
+        const int64_t l_at = place.logical + half * kLanes;
         uint32_t left[4], right[4], result[4];
-        join_row(words, __ldcs(reinterpret_cast<const uint2*>(a.side + s_at)), q, half == 1, left);
+        join_row(words, __ldcs(reinterpret_cast<const uint2*>(a.side + s_at)), place.q, half == 1,
+                 left);
         if (kDual) {
-          join_row(words_b, __ldcs(reinterpret_cast<const uint2*>(b.side + s_at)), q, half == 1,
-                   right);
+          join_row(words_b, __ldcs(reinterpret_cast<const uint2*>(b.side + s_at)), place.q,
+                   half == 1, right);
         } else {
           load_dense8(other, l_at, g.logical_numel, other_vector_ok, right);
         }
@@ -465,10 +479,10 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
         for (int k = 0; k < 4; ++k)
           result[k] = apply_op(left[k], right[k], spec.op, spec.alpha_is_one != 0,
                                spec.beta_is_one != 0, alpha, beta);
-        store_row(result, compressed, output, auxiliary, l_at, g.logical_numel, s_at, q);
+        store_row(result, compressed, output, auxiliary, l_at, g.logical_numel, s_at, place.q);
       }
     }
-    __syncthreads();
+    __syncwarp();
   }
 }
 
@@ -503,7 +517,8 @@ static int view_of(const lct_operand* in, OperandView* v) {
   if (in == nullptr || in->encoded == nullptr || in->side == nullptr || in->center == nullptr ||
       in->pair_table == nullptr)
     return LCT_E_NULL_POINTER;
-  if (!aligned16(in->side) || !aligned16(in->pair_table)) return LCT_E_ALIGNMENT;
+  if (!aligned16(in->side) || !aligned16(in->pair_table) || !aligned16(in->encoded))
+    return LCT_E_ALIGNMENT;
   const lct_overflow& o = in->overflow;
   if (o.mode < 0 || o.mode > 2) return LCT_E_BAD_ARGUMENT;
   if (o.mode != 0 && (o.blocks == nullptr || o.tail == nullptr || o.lanes == nullptr ||
@@ -543,7 +558,7 @@ int lct_decode(const lct_operand* a, int16_t* out, int64_t size, int64_t logical
   if ((rc = lct::view_of(a, &va)) != 0) return rc;
   if (out == nullptr) return LCT_E_NULL_POINTER;
   if (!lct::aligned16(out)) return LCT_E_ALIGNMENT;
-  const size_t shared = sizeof(lct::DecodeShared);
+  const size_t shared = lct::operand_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::decode_kernel, shared)) != 0) return rc;
   lct::decode_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared,
                        static_cast<cudaStream_t>(stream)>>>(va, g, reinterpret_cast<uint16_t*>(out));
@@ -572,12 +587,12 @@ int lct_pointwise(const lct_operand* a, const void* other, void* output, uint8_t
     return LCT_E_ALIGNMENT;
   if ((reinterpret_cast<uintptr_t>(other) & 1u) != 0) return LCT_E_ALIGNMENT;
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
-  const size_t shared = sizeof(lct::DecodeShared);
+  const size_t shared = lct::operand_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::pointwise_kernel<false>, shared)) != 0) return rc;
   lct::pointwise_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, shared,
                                  static_cast<cudaStream_t>(stream)>>>(
       va, va, g, static_cast<const uint16_t*>(other), lct::aligned16(other), output, auxiliary,
-      spec, compressed_output != 0);
+      spec, compressed_output != 0, (uint32_t)shared);
   return (int)cudaGetLastError();
 }
 
@@ -597,11 +612,11 @@ int lct_dual_scale_add(const lct_operand* a, const lct_operand* b, void* output,
     return LCT_E_ALIGNMENT;
   // fma(a, alpha, b): the scaled operation with beta == 1.
   const lct::OpSpec spec{alpha, nullptr, LCT_OP_SCALAR_MUL_ADD, 0, 1};
-  const size_t shared = 2 * sizeof(lct::DecodeShared);
-  if ((rc = lct::opt_in_shared(lct::pointwise_kernel<true>, shared)) != 0) return rc;
-  lct::pointwise_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, shared,
+  const size_t one = lct::operand_shared_bytes(fixed_words);
+  if ((rc = lct::opt_in_shared(lct::pointwise_kernel<true>, 2 * one)) != 0) return rc;
+  lct::pointwise_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, 2 * one,
                                 static_cast<cudaStream_t>(stream)>>>(
-      va, vb, g, nullptr, false, output, auxiliary, spec, compressed_output != 0);
+      va, vb, g, nullptr, false, output, auxiliary, spec, compressed_output != 0, (uint32_t)one);
   return (int)cudaGetLastError();
 }
 

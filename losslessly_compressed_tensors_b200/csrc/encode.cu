@@ -1,16 +1,19 @@
 // Field split + fixed-budget Huffman encoder, and the overflow tail compaction.
 //
-// One CTA (256 threads) per codec block.  Per 32-row tile:
+// One CTA (256 threads) per codec block; between the prologue and the epilogue
+// every warp runs on its own (see common.cuh: a warp's 32 lanes own one
+// 64-byte segment of every row).  Per 32-row tile, per warp:
 //   row phase  - thread = 8 columns of a row pair: 128-bit loads of the BF16
-//                source, exponent bytes into the column-ordered shared tile,
-//                side bytes permuted to lane order and stored 64 bits at a time;
-//   lane phase - thread = lane: reads its exponent pair from the tile, looks
-//                both codes up in the shared encode table, appends them to a
-//                64-bit accumulator and drops finished 32-bit words into a
-//                shared image of the block's payload.
+//                source (requested one tile ahead), four values at a time
+//                split into exponent bytes -> column-ordered shared tile and
+//                side bytes -> lane order, stored 64 bits at a time;
+//   lane phase - thread = lane: reads its exponent pair from the tile, fetches
+//                both (code, length) entries from the shared encode table,
+//                appends them at its absolute bit position and drops finished
+//                32-bit words into a shared image of the block's payload.
 // At the end the payload image (zero where nothing was written, so the output
-// is deterministic) is copied out with coalesced stores, and the block's
-// overflow summary is reduced.
+// is deterministic) is copied out with coalesced 128-bit stores, and the
+// block's overflow summary is reduced.
 #include "common.cuh"
 #include "lct_b200.h"
 
@@ -26,18 +29,97 @@ struct EncodeShape {
   int fixed_words;
 };
 
-// Dynamic shared memory: encode table | tile | scan scratch | payload image.
+// Fixed part of the dynamic shared memory; the payload image follows it.
 struct __align__(16) EncodeSharedHead {
-  uint32_t table[256];
-  uint16_t tile[kTilePairs * kLanes];
-  int scan[33];
-  int pad[3];
+  uint2 table[256];                        // x = code bits (LSB first), y = code length
+  uint16_t tile[kWarps][kTilePairs * 32];
+  int scan[36];
+};
+
+// Source values of one row-phase unit: 8 columns of two consecutive rows.
+struct UnitSource {
+  uint4 top, bottom;  // BF16 bits; for precomputed exponent bytes only .x/.y are used
 };
 
 __device__ __forceinline__ uint32_t load_pair_guarded(const uint16_t* src, int64_t at, int64_t numel) {
   const uint32_t a = at < numel ? src[at] : 0u;
   const uint32_t b = at + 1 < numel ? src[at + 1] : 0u;
   return a | (b << 16);
+}
+
+template <bool kPrecomputed>
+__device__ __forceinline__ UnitSource load_unit(const void* src, int64_t at, int64_t numel,
+                                                bool vector_ok, bool full_block) {
+  UnitSource u;
+  u.top = make_uint4(0, 0, 0, 0);
+  u.bottom = make_uint4(0, 0, 0, 0);
+  if (kPrecomputed) {
+    const uint8_t* bytes = static_cast<const uint8_t*>(src);
+    if (vector_ok && (full_block || at + kLanes + 8 <= numel)) {
+      const uint2 t = __ldcs(reinterpret_cast<const uint2*>(bytes + at));
+      const uint2 b = __ldcs(reinterpret_cast<const uint2*>(bytes + at + kLanes));
+      u.top.x = t.x; u.top.y = t.y; u.bottom.x = b.x; u.bottom.y = b.y;
+    } else {
+      uint32_t* top = &u.top.x;
+      uint32_t* bottom = &u.bottom.x;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (at + i < numel) top[i >> 2] |= (uint32_t)bytes[at + i] << (8 * (i & 3));
+        if (at + kLanes + i < numel) bottom[i >> 2] |= (uint32_t)bytes[at + kLanes + i] << (8 * (i & 3));
+      }
+    }
+  } else {
+    const uint16_t* bits = static_cast<const uint16_t*>(src);
+    if (vector_ok && (full_block || at + kLanes + 8 <= numel)) {
+      u.top = __ldcs(reinterpret_cast<const uint4*>(bits + at));
+      u.bottom = __ldcs(reinterpret_cast<const uint4*>(bits + at + kLanes));
+    } else {
+      uint32_t* top = &u.top.x;
+      uint32_t* bottom = &u.bottom.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        top[k] = load_pair_guarded(bits, at + 2 * k, numel);
+        bottom[k] = load_pair_guarded(bits, at + kLanes + 2 * k, numel);
+      }
+    }
+  }
+  return u;
+}
+
+// Lane phase of one tile.  Returns false once the lane has overflowed.
+template <bool kCheckValid>
+__device__ __forceinline__ bool encode_tile_rows(const EncodeSharedHead& sh, const uint8_t* tile_bytes,
+                                                 uint32_t* payload_column, int lane32, int row_bits,
+                                                 int step0, int valid, int budget_bits, int& pos,
+                                                 uint32_t& lo, int& extra_start) {
+#pragma unroll 8
+  for (int p = 0; p < kTilePairs; ++p) {
+    const int column = lane32 ^ ((row_bits + 2 * p) & 30);
+    const uint8_t* e = tile_bytes + 2 * (p * 32 + column);
+    uint2 c0 = sh.table[e[0]];
+    uint2 c1 = sh.table[e[1]];
+    if (kCheckValid) {  // padding carries no bits
+      if (step0 + 2 * p >= valid) c0 = make_uint2(0u, 0u);
+      if (step0 + 2 * p + 1 >= valid) c1 = make_uint2(0u, 0u);
+    }
+    const uint32_t code = c0.x | (c1.x << c0.y);
+    const int length = (int)(c0.y + c1.y);
+    const int shift = pos & 31;
+    const int next = pos + length;
+    if (next > budget_bits) {
+      // First pair that does not fit: freeze the current word and stop.
+      extra_start = step0 + 2 * p;
+      if (pos < budget_bits) payload_column[(pos >> 5) * kLanes] = lo;
+      return false;
+    }
+    lo |= code << shift;
+    if (shift + length >= 32) {
+      payload_column[(pos >> 5) * kLanes] = lo;
+      lo = __funnelshift_l(code, 0u, shift);  // the bits that did not fit; 0 when shift == 0
+    }
+    pos = next;
+  }
+  return true;
 }
 
 template <bool kPrecomputed>
@@ -50,122 +132,98 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(EncodeSharedHead));
 
   const int64_t block = blockIdx.x;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
 
-  sh.table[tid] = (uint32_t)shifted_encode[tid];
+  {
+    const uint32_t packed = (uint32_t)shifted_encode[tid];
+    sh.table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
+  }
   for (int w = 0; w < g.fixed_words; ++w) payload[w * kLanes + tid] = 0u;
   if (block == 0 && tid < 4) encoded[g.streams * g.fixed_words + tid] = 0u;  // trailing pad words
+  __syncthreads();
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int budget_bits = g.fixed_words * 32;
-  uint64_t acc = 0;
-  int shift = 0, word = 0;
+  uint16_t* tile = sh.tile[warp];
+  const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
+  uint32_t* payload_column = payload + tid;
+  uint32_t lo = 0;
+  int pos = 0;
   int extra_start = -1;  // first overflowing step, -1 = none
+  bool open = true;
+
+  // This thread's two row-phase units: row pair p, 8-column subgroup j4.
+  const int j4 = lane32 & 3;
+  const int unit_p[2] = {lane32 >> 2, (lane32 >> 2) + 8};
+  auto logical_of = [&](int step) {
+    const int64_t row = row0 + step;
+    const int mask = (int)(row & 254);
+    return row * kLanes + 32 * (warp ^ (mask >> 5)) + 8 * j4;
+  };
+  UnitSource source[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u)
+    source[u] = load_unit<kPrecomputed>(src, logical_of(2 * unit_p[u]), g.logical_numel,
+                                        src_vector_ok, full_block);
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    __syncthreads();  // table/payload ready; previous tile fully consumed
     // ---- row phase ----
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (tid >> 5) + 8 * u;
-      const int j = tid & 31;
+      const int p = unit_p[u];
       const int step = step0 + 2 * p;
-      const int64_t row = row0 + step;
-      const int64_t at = row * kLanes + 8 * j;
-      uint32_t tile_words[4];
+      uint32_t e_top03, e_top47, e_bot03, e_bot47;
       if (kPrecomputed) {
-        const uint8_t* bytes = static_cast<const uint8_t*>(src);
-        uint32_t top[2], bottom[2];
-        if (src_vector_ok && at + kLanes + 8 <= g.logical_numel) {
-          const uint2 t = __ldcs(reinterpret_cast<const uint2*>(bytes + at));
-          const uint2 b = __ldcs(reinterpret_cast<const uint2*>(bytes + at + kLanes));
-          top[0] = t.x; top[1] = t.y; bottom[0] = b.x; bottom[1] = b.y;
-        } else {
-          top[0] = top[1] = bottom[0] = bottom[1] = 0u;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (at + i < g.logical_numel) top[i >> 2] |= (uint32_t)bytes[at + i] << (8 * (i & 3));
-            if (at + kLanes + i < g.logical_numel)
-              bottom[i >> 2] |= (uint32_t)bytes[at + kLanes + i] << (8 * (i & 3));
-          }
-        }
-        tile_words[0] = prmt(top[0], bottom[0], 0x5140);
-        tile_words[1] = prmt(top[0], bottom[0], 0x7362);
-        tile_words[2] = prmt(top[1], bottom[1], 0x5140);
-        tile_words[3] = prmt(top[1], bottom[1], 0x7362);
+        e_top03 = source[u].top.x; e_top47 = source[u].top.y;
+        e_bot03 = source[u].bottom.x; e_bot47 = source[u].bottom.y;
       } else {
-        const uint16_t* bits = static_cast<const uint16_t*>(src);
-        uint32_t top[4], bottom[4];
-        if (src_vector_ok && (full_block || at + kLanes + 8 <= g.logical_numel)) {
-          const uint4 t = __ldcs(reinterpret_cast<const uint4*>(bits + at));
-          const uint4 b = __ldcs(reinterpret_cast<const uint4*>(bits + at + kLanes));
-          top[0] = t.x; top[1] = t.y; top[2] = t.z; top[3] = t.w;
-          bottom[0] = b.x; bottom[1] = b.y; bottom[2] = b.z; bottom[3] = b.w;
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            top[k] = load_pair_guarded(bits, at + 2 * k, g.logical_numel);
-            bottom[k] = load_pair_guarded(bits, at + kLanes + 2 * k, g.logical_numel);
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tile_words[k] = prmt(exponents_of(top[k]), exponents_of(bottom[k]), 0x6240);
+        const uint4 t = source[u].top, b = source[u].bottom;
+        const uint32_t tl03 = prmt(t.x, t.y, 0x6420), th03 = prmt(t.x, t.y, 0x7531);
+        const uint32_t tl47 = prmt(t.z, t.w, 0x6420), th47 = prmt(t.z, t.w, 0x7531);
+        const uint32_t bl03 = prmt(b.x, b.y, 0x6420), bh03 = prmt(b.x, b.y, 0x7531);
+        const uint32_t bl47 = prmt(b.z, b.w, 0x6420), bh47 = prmt(b.z, b.w, 0x7531);
+        e_top03 = exponent_bytes(tl03, th03); e_top47 = exponent_bytes(tl47, th47);
+        e_bot03 = exponent_bytes(bl03, bh03); e_bot47 = exponent_bytes(bl47, bh47);
         // Side bytes: column order -> lane order, one 8-byte store per row.
-        const int mask = (int)(row & 254);
-        const uint32_t q = (uint32_t)(mask >> 1) & 3u;
-        const int lane_group = (8 * j) ^ (mask & 0xF8);
-        uint8_t* s = side + block_base + (int64_t)step * kLanes + lane_group;
-        const uint32_t t01 = prmt(sides_of(top[0]), sides_of(top[1]), 0x6420);
-        const uint32_t t23 = prmt(sides_of(top[2]), sides_of(top[3]), 0x6420);
-        const uint32_t b01 = prmt(sides_of(bottom[0]), sides_of(bottom[1]), 0x6420);
-        const uint32_t b23 = prmt(sides_of(bottom[2]), sides_of(bottom[3]), 0x6420);
-        __stcs(reinterpret_cast<uint2*>(s),
-               make_uint2(prmt(t01, t23, pair_selector_low(q)), prmt(t01, t23, pair_selector_high(q))));
-        __stcs(reinterpret_cast<uint2*>(s + kLanes),
-               make_uint2(prmt(b01, b23, pair_selector_low(q)), prmt(b01, b23, pair_selector_high(q))));
-      }
-      *reinterpret_cast<uint4*>(&sh.tile[p * kLanes + 8 * j]) =
-          make_uint4(tile_words[0], tile_words[1], tile_words[2], tile_words[3]);
-    }
-    __syncthreads();
-    // ---- lane phase ----
-    if (extra_start < 0) {
-#pragma unroll 4
-      for (int p = 0; p < kTilePairs; ++p) {
-        const int step = step0 + 2 * p;
         const int mask = (int)((row0 + step) & 254);
-        const uint32_t pair = sh.tile[p * kLanes + (tid ^ mask)];
-        uint32_t c0 = sh.table[pair & 255u];
-        uint32_t c1 = sh.table[pair >> 8];
-        if (step >= valid) c0 = 0u;          // padding carries no bits
-        if (step + 1 >= valid) c1 = 0u;
-        const int length0 = (int)(c0 >> 20);
-        const int length = (int)((c0 + c1) >> 20);  // codes are < 2^16: no carry into bit 20
-        const uint32_t code = (c0 & 0xFFFFFu) | ((c1 & 0xFFFFFu) << length0);
-        if (word * 32 + shift + length > budget_bits) {
-          // First pair that does not fit: freeze the current word and stop.
-          extra_start = step;
-          if (word < g.fixed_words) payload[word * kLanes + tid] = (uint32_t)acc;
-          word = g.fixed_words;
-          break;
-        }
-        acc |= (uint64_t)code << shift;
-        shift += length;
-        if (shift >= 32) {
-          payload[word * kLanes + tid] = (uint32_t)acc;
-          acc >>= 32;
-          shift -= 32;
-          ++word;
-        }
+        const uint32_t q = (uint32_t)(mask >> 1) & 3u;
+        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (mask & 0x18));
+        const uint32_t ts03 = side_bytes(tl03, th03), ts47 = side_bytes(tl47, th47);
+        const uint32_t bs03 = side_bytes(bl03, bh03), bs47 = side_bytes(bl47, bh47);
+        __stcs(reinterpret_cast<uint2*>(s),
+               make_uint2(prmt(ts03, ts47, pair_selector_low(q)), prmt(ts03, ts47, pair_selector_high(q))));
+        __stcs(reinterpret_cast<uint2*>(s + kLanes),
+               make_uint2(prmt(bs03, bs47, pair_selector_low(q)), prmt(bs03, bs47, pair_selector_high(q))));
       }
+      // tile word for columns (2k, 2k+1): [e_top(2k), e_bot(2k), e_top(2k+1), e_bot(2k+1)]
+      *reinterpret_cast<uint4*>(&tile[p * 32 + 8 * j4]) =
+          make_uint4(prmt(e_top03, e_bot03, 0x5140), prmt(e_top03, e_bot03, 0x7362),
+                     prmt(e_top47, e_bot47, 0x5140), prmt(e_top47, e_bot47, 0x7362));
     }
+    __syncwarp();
+    // Request the next tile's source now; it arrives while the lanes encode.
+    if (step0 + kTileRows < g.steps) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        source[u] = load_unit<kPrecomputed>(src, logical_of(step0 + kTileRows + 2 * unit_p[u]),
+                                            g.logical_numel, src_vector_ok, full_block);
+    }
+    // ---- lane phase ----
+    if (open) {
+      const int row_bits = (int)(row0 + step0);
+      if (full_block)
+        open = encode_tile_rows<false>(sh, tile_bytes, payload_column, lane32, row_bits, step0,
+                                       valid, budget_bits, pos, lo, extra_start);
+      else
+        open = encode_tile_rows<true>(sh, tile_bytes, payload_column, lane32, row_bits, step0,
+                                      valid, budget_bits, pos, lo, extra_start);
+    }
+    __syncwarp();
   }
-  if (extra_start < 0 && word < g.fixed_words && shift != 0)
-    payload[word * kLanes + tid] = (uint32_t)acc;
+  if (open && (pos & 31) != 0) payload_column[(pos >> 5) * kLanes] = lo;
   extra_starts[block * kLanes + tid] = extra_start < 0 ? (uint8_t)255 : (uint8_t)extra_start;
 
   // Block summary: overflowing lanes and their tail bytes.
@@ -176,12 +234,11 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
     bad += __shfl_down_sync(0xFFFFFFFFu, bad, d);
     bytes += __shfl_down_sync(0xFFFFFFFFu, bytes, d);
   }
-  __syncthreads();
-  if ((tid & 31) == 0) { sh.scan[tid >> 5] = bad; sh.scan[8 + (tid >> 5)] = bytes; }
+  if (lane32 == 0) { sh.scan[warp] = bad; sh.scan[8 + warp] = bytes; }
   __syncthreads();  // also publishes every lane's payload words
   if (tid == 0) {
     int total_bad = 0, total_bytes = 0;
-    for (int w = 0; w < kThreads / 32; ++w) { total_bad += sh.scan[w]; total_bytes += sh.scan[8 + w]; }
+    for (int w = 0; w < kWarps; ++w) { total_bad += sh.scan[w]; total_bytes += sh.scan[8 + w]; }
     summaries[block] = total_bad;
     summaries[g.n_blocks + block] = total_bytes;
   }
