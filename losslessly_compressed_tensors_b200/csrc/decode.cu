@@ -51,8 +51,11 @@ struct Shape {
   int rare_length;
 };
 
-// Fixed part of one operand's shared memory; the payload image
-// (fixed_words + 1 rows of 256 words, last row zero) follows it.
+// Shared memory of a CTA: the payload image(s) first (fixed_words + 2 rows of
+// 256 words each, the last two zero), then one DecodeShared per operand.  A
+// lane's refill pointer is clamped to the image once per tile; inside a tile a
+// corrupt stream can run at most 16 rows past it, which still lands in the
+// tables below (garbage in, garbage out, but never an out-of-range access).
 struct __align__(16) DecodeShared {
   uint32_t table[kPairEntries];
   uint16_t tile[kWarps][kTilePairs * 32];
@@ -62,8 +65,11 @@ struct __align__(16) DecodeShared {
   int scan[36];
 };
 
+static size_t payload_image_bytes(int fixed_words) {
+  return (size_t)(fixed_words + 2) * kLanes * 4;
+}
 static size_t operand_shared_bytes(int fixed_words) {
-  return sizeof(DecodeShared) + (size_t)(fixed_words + 1) * kLanes * 4;
+  return sizeof(DecodeShared) + payload_image_bytes(fixed_words);
 }
 
 __device__ __forceinline__ void cp_async_16(void* shared_dst, const void* global_src) {
@@ -74,23 +80,45 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
-// Absolute bit position of one lane in the shared payload image.
+// Read position of one lane: a 96-bit register window over the shared payload
+// image (the word under the position and the two after it) plus the bit
+// offset inside the first word.  Lookups take their bits from registers; the
+// only shared-memory access is the refill of the third word, which is not on
+// the lookup's dependency chain.
 struct BitReader {
-  const uint32_t* column;  // &payload[lane]
-  int pos;
-  int last_word;           // fixed_words - 1: reads never leave the image
+  const uint32_t* next_row;  // image word that enters the window at the next refill
+  uint32_t cur, n1, n2;
+  int shift;                 // 0..31 between pairs
 
-  __device__ __forceinline__ uint32_t peek(int at) const {
-    const uint32_t* p = column + min(at >> 5, last_word) * kLanes;
-    return __funnelshift_r(p[0], p[kLanes], at);  // shift amount is taken modulo 32
+  __device__ __forceinline__ void open(const uint32_t* column) {
+    cur = column[0];
+    n1 = column[kLanes];
+    n2 = column[2 * kLanes];
+    next_row = column + 3 * kLanes;
+    shift = 0;
+  }
+  // 32 stream bits starting `extra` bits after the position (shift + extra < 64).
+  __device__ __forceinline__ uint32_t peek(int extra) const {
+    const int s = shift + extra;
+    const bool far = s >= 32;
+    return __funnelshift_r(far ? n1 : cur, far ? n2 : n1, s);  // amount is taken modulo 32
+  }
+  __device__ __forceinline__ uint32_t peek0() const { return __funnelshift_r(cur, n1, shift); }
+  __device__ __forceinline__ void advance(int bits) {  // bits <= 32
+    shift += bits;
+    if (shift >= 32) {
+      shift -= 32;
+      cur = n1;
+      n1 = n2;
+      n2 = *next_row;
+      next_row += kLanes;
+    }
   }
 };
 
-// Decode one symbol at bit position `at`.
-__device__ __forceinline__ uint32_t one_symbol(const BitReader& r, int at, const DecodeShared& sh,
-                                               int rare_length, int* length) {
-  const uint32_t bits = r.peek(at);
-  const uint32_t entry = sh.table[bits & (kPairEntries - 1)];
+// One symbol from a table entry and the stream bits it was looked up with.
+__device__ __forceinline__ uint32_t symbol_of(uint32_t entry, uint32_t bits, const DecodeShared& sh,
+                                              int rare_length, int* length) {
   if (entry & kEscape) {
     *length = rare_length + 8;
     return sh.index_to_byte[(bits >> rare_length) & 255u];
@@ -99,13 +127,15 @@ __device__ __forceinline__ uint32_t one_symbol(const BitReader& r, int at, const
   return entry & 255u;
 }
 
-// Pair whose table entry is not "two direct symbols": decode them one by one.
+// Pair whose table entry is not "two direct symbols": take the first symbol
+// from the entry already in hand, look the second one up on its own.
 // Returns the pair in table-entry form (bytes: first, second, bits consumed).
-__device__ __forceinline__ uint32_t slow_pair(const BitReader& r, const DecodeShared& sh,
-                                              int rare_length) {
+__device__ __forceinline__ uint32_t slow_pair(const BitReader& r, uint32_t entry, uint32_t bits,
+                                              const DecodeShared& sh, int rare_length) {
   int l0, l1;
-  const uint32_t e0 = one_symbol(r, r.pos, sh, rare_length, &l0);
-  const uint32_t e1 = one_symbol(r, r.pos + l0, sh, rare_length, &l1);
+  const uint32_t e0 = symbol_of(entry, bits, sh, rare_length, &l0);
+  const uint32_t bits1 = r.peek(l0);
+  const uint32_t e1 = symbol_of(sh.table[table_slot(bits1)], bits1, sh, rare_length, &l1);
   return e0 | (e1 << 8) | ((uint32_t)(l0 + l1) << 16);
 }
 
@@ -113,38 +143,42 @@ __device__ __forceinline__ uint32_t slow_pair(const BitReader& r, const DecodeSh
 // are in the bit stream (its overflow start or its valid length, whichever is
 // first); steps from `tail_from` on come from the raw tail.
 __device__ __forceinline__ void decode_tile_rows(BitReader& r, const DecodeShared& sh,
-                                                 uint16_t* tile, int lane32, int64_t row0,
-                                                 int step0, int coded, int tail_from,
-                                                 const uint8_t* tail_bytes, int rare_length) {
-  const int row_bits = (int)(row0 + step0);
+                                                 uint16_t* tile, int lane32, int step0, int coded,
+                                                 int tail_from, const uint8_t* tail_bytes,
+                                                 int rare_length, const uint32_t* last_row) {
+  // A well-formed stream never refills past the image's second zero row; a
+  // corrupt one is pulled back here, once per tile (at most 16 refills each).
+  if (r.next_row > last_row) r.next_row = last_row;
+  // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
   if (__all_sync(0xFFFFFFFFu, step0 + kTileRows <= coded)) {
 #pragma unroll
     for (int p = 0; p < kTilePairs; ++p) {
-      const int column = lane32 ^ ((row_bits + 2 * p) & 30);
-      uint32_t entry = sh.table[r.peek(r.pos) & (kPairEntries - 1)];
-      if ((int32_t)entry < 0) entry = slow_pair(r, sh, rare_length);
-      r.pos += (int)prmt(entry, 0, 0x4442);
-      tile[p * 32 + column] = (uint16_t)entry;
+      const uint32_t bits = r.peek0();
+      uint32_t entry = sh.table[table_slot(bits)];
+      if ((int32_t)entry < 0) entry = slow_pair(r, entry, bits, sh, rare_length);
+      tile[p * 32 + (lane32 ^ (2 * p))] = (uint16_t)entry;
+      r.advance((int)prmt(entry, 0, 0x4442));
     }
     return;
   }
   for (int p = 0; p < kTilePairs; ++p) {
     const int step = step0 + 2 * p;
-    const int column = lane32 ^ ((row_bits + 2 * p) & 30);
     uint32_t pair = 0;
     if (step + 2 <= coded) {
-      pair = sh.table[r.peek(r.pos) & (kPairEntries - 1)];
-      if ((int32_t)pair < 0) pair = slow_pair(r, sh, rare_length);
-      r.pos += (int)prmt(pair, 0, 0x4442);
+      const uint32_t bits = r.peek0();
+      pair = sh.table[table_slot(bits)];
+      if ((int32_t)pair < 0) pair = slow_pair(r, pair, bits, sh, rare_length);
+      r.advance((int)prmt(pair, 0, 0x4442));
     } else if (step >= tail_from) {
       const uint32_t t0 = tail_bytes[step - tail_from], t1 = tail_bytes[step + 1 - tail_from];
       pair = ((t0 + 127u) & 255u) | (((t1 + 127u) & 255u) << 8);
     } else if (step + 1 == coded) {
       int l0;
-      pair = one_symbol(r, r.pos, sh, rare_length, &l0);
-      r.pos += l0;
+      const uint32_t bits = r.peek0();
+      pair = symbol_of(sh.table[table_slot(bits)], bits, sh, rare_length, &l0);
+      r.advance(l0);
     }
-    tile[p * 32 + column] = (uint16_t)pair;
+    tile[p * 32 + (lane32 ^ (2 * p))] = (uint16_t)pair;
   }
 }
 
@@ -160,6 +194,7 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
     cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
   }
   payload[g.fixed_words * kLanes + tid] = 0u;
+  payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
 
   const int center = *a.center;
   sh.index_to_byte[tid] = (uint8_t)index_to_exponent_byte((uint32_t)tid, center);
@@ -169,7 +204,7 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
   const uint4* source = reinterpret_cast<const uint4*>(a.pair_table);
   uint4* target = reinterpret_cast<uint4*>(sh.table);
   for (int i = tid; i < kPairEntries / 4; i += kThreads) {
-    uint4 e = __ldg(source + i);
+    uint4 e = __ldg(source + i);  // already in slot (bit-reversed) order
     uint32_t* w = &e.x;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -226,13 +261,13 @@ struct UnitPlace {
 
 __device__ __forceinline__ UnitPlace place_unit(int warp, int p, int j4, int64_t row0, int step0,
                                                 int64_t block_base) {
-  const int step = step0 + 2 * p;
-  const int64_t row = row0 + step;
-  const int mask = (int)(row & 254);
+  // All 32 rows of a tile share mask bits 5..7; bits 1..4 of pair p are 2p.
+  const int64_t tile_row = row0 + step0;
+  const int group = warp ^ ((int)(tile_row >> 5) & 7);
   UnitPlace u;
-  u.logical = row * kLanes + 32 * (warp ^ (mask >> 5)) + 8 * j4;
-  u.storage = block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (mask & 0x18));
-  u.q = (uint32_t)(mask >> 1) & 3u;
+  u.logical = (tile_row + 2 * p) * kLanes + 32 * group + 8 * j4;
+  u.storage = block_base + (int64_t)(step0 + 2 * p) * kLanes + 32 * warp + ((8 * j4) ^ ((2 * p) & 0x18));
+  u.q = (uint32_t)p & 3u;
   return u;
 }
 
@@ -260,8 +295,8 @@ __device__ __forceinline__ void join_row(const uint4& tile_words, uint2 side_lan
 __global__ void __launch_bounds__(kThreads)
 decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(DecodeShared));
+  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
+  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
   const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
@@ -272,7 +307,9 @@ decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  BitReader reader{payload + tid, 0, g.fixed_words - 1};
+  BitReader reader;
+  reader.open(payload + tid);
+  const uint32_t* last_row = payload + tid + (g.fixed_words + 2) * kLanes;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
   uint16_t* tile = sh.tile[warp];
 
@@ -287,8 +324,8 @@ decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
       side_regs[u][0] = __ldcs(reinterpret_cast<const uint2*>(s));
       side_regs[u][1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
     }
-    decode_tile_rows(reader, sh, tile, lane32, row0, step0, coded, tail_from, tail_bytes,
-                     g.rare_length);
+    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
+                     last_row);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -416,13 +453,14 @@ template <bool kDual>
 __global__ void __launch_bounds__(kThreads)
 pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restrict__ other,
                  bool other_vector_ok, void* output, uint8_t* auxiliary, OpSpec spec,
-                 bool compressed, uint32_t operand_bytes) {
+                 bool compressed) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(DecodeShared));
-  unsigned char* second = smem_raw + (kDual ? operand_bytes : 0u);
-  DecodeShared& sh_b = *reinterpret_cast<DecodeShared*>(second);
-  uint32_t* payload_b = reinterpret_cast<uint32_t*>(second + sizeof(DecodeShared));
+  const size_t image = (size_t)(g.fixed_words + 2) * kLanes * 4;
+  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
+  uint32_t* payload_b = reinterpret_cast<uint32_t*>(smem_raw + (kDual ? image : 0));
+  unsigned char* tables = smem_raw + (kDual ? 2 : 1) * image;
+  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(tables);
+  DecodeShared& sh_b = *reinterpret_cast<DecodeShared*>(tables + (kDual ? sizeof(DecodeShared) : 0));
   const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
@@ -436,8 +474,11 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
   const int a_tail_from = sh.overflow_start[tid];
   const int a_coded = min(valid, a_tail_from);
   const uint8_t* a_tail = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  BitReader reader_a{payload + tid, 0, g.fixed_words - 1};
-  BitReader reader_b{payload_b + tid, 0, g.fixed_words - 1};
+  BitReader reader_a, reader_b;
+  reader_a.open(payload + tid);
+  reader_b.open(payload_b + tid);
+  const uint32_t* last_row_a = payload + tid + (g.fixed_words + 2) * kLanes;
+  const uint32_t* last_row_b = payload_b + tid + (g.fixed_words + 2) * kLanes;
   int b_tail_from = g.steps, b_coded = 0;
   const uint8_t* b_tail = nullptr;
   if (kDual) {
@@ -449,11 +490,11 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
   uint16_t* tile_b = sh_b.tile[warp];
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader_a, sh, tile, lane32, row0, step0, a_coded, a_tail_from, a_tail,
-                     g.rare_length);
+    decode_tile_rows(reader_a, sh, tile, lane32, step0, a_coded, a_tail_from, a_tail,
+                     g.rare_length, last_row_a);
     if (kDual)
-      decode_tile_rows(reader_b, sh_b, tile_b, lane32, row0, step0, b_coded, b_tail_from, b_tail,
-                       g.rare_length);
+      decode_tile_rows(reader_b, sh_b, tile_b, lane32, step0, b_coded, b_tail_from, b_tail,
+                       g.rare_length, last_row_b);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -592,7 +633,7 @@ int lct_pointwise(const lct_operand* a, const void* other, void* output, uint8_t
   lct::pointwise_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, shared,
                                  static_cast<cudaStream_t>(stream)>>>(
       va, va, g, static_cast<const uint16_t*>(other), lct::aligned16(other), output, auxiliary,
-      spec, compressed_output != 0, (uint32_t)shared);
+      spec, compressed_output != 0);
   return (int)cudaGetLastError();
 }
 
@@ -616,7 +657,7 @@ int lct_dual_scale_add(const lct_operand* a, const lct_operand* b, void* output,
   if ((rc = lct::opt_in_shared(lct::pointwise_kernel<true>, 2 * one)) != 0) return rc;
   lct::pointwise_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, 2 * one,
                                 static_cast<cudaStream_t>(stream)>>>(
-      va, vb, g, nullptr, false, output, auxiliary, spec, compressed_output != 0, (uint32_t)one);
+      va, vb, g, nullptr, false, output, auxiliary, spec, compressed_output != 0);
   return (int)cudaGetLastError();
 }
 

@@ -89,13 +89,13 @@ __device__ __forceinline__ UnitSource load_unit(const void* src, int64_t at, int
 // Lane phase of one tile.  Returns false once the lane has overflowed.
 template <bool kCheckValid>
 __device__ __forceinline__ bool encode_tile_rows(const EncodeSharedHead& sh, const uint8_t* tile_bytes,
-                                                 uint32_t* payload_column, int lane32, int row_bits,
+                                                 uint32_t* payload_column, int lane32,
                                                  int step0, int valid, int budget_bits, int& pos,
                                                  uint32_t& lo, int& extra_start) {
-#pragma unroll 8
+#pragma unroll
   for (int p = 0; p < kTilePairs; ++p) {
-    const int column = lane32 ^ ((row_bits + 2 * p) & 30);
-    const uint8_t* e = tile_bytes + 2 * (p * 32 + column);
+    // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
+    const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ (2 * p)));
     uint2 c0 = sh.table[e[0]];
     uint2 c1 = sh.table[e[1]];
     if (kCheckValid) {  // padding carries no bits
@@ -123,7 +123,7 @@ __device__ __forceinline__ bool encode_tile_rows(const EncodeSharedHead& sh, con
 }
 
 template <bool kPrecomputed>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
               uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
               uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
@@ -160,8 +160,7 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
   const int unit_p[2] = {lane32 >> 2, (lane32 >> 2) + 8};
   auto logical_of = [&](int step) {
     const int64_t row = row0 + step;
-    const int mask = (int)(row & 254);
-    return row * kLanes + 32 * (warp ^ (mask >> 5)) + 8 * j4;
+    return row * kLanes + 32 * (warp ^ ((int)(row >> 5) & 7)) + 8 * j4;
   };
   UnitSource source[2];
 #pragma unroll
@@ -188,9 +187,9 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
         e_top03 = exponent_bytes(tl03, th03); e_top47 = exponent_bytes(tl47, th47);
         e_bot03 = exponent_bytes(bl03, bh03); e_bot47 = exponent_bytes(bl47, bh47);
         // Side bytes: column order -> lane order, one 8-byte store per row.
-        const int mask = (int)((row0 + step) & 254);
-        const uint32_t q = (uint32_t)(mask >> 1) & 3u;
-        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (mask & 0x18));
+        // mask bits 1..4 of this row pair are 2p (tiles start on multiples of 32 rows).
+        const uint32_t q = (uint32_t)p & 3u;
+        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ ((2 * p) & 0x18));
         const uint32_t ts03 = side_bytes(tl03, th03), ts47 = side_bytes(tl47, th47);
         const uint32_t bs03 = side_bytes(bl03, bh03), bs47 = side_bytes(bl47, bh47);
         __stcs(reinterpret_cast<uint2*>(s),
@@ -213,13 +212,12 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
     }
     // ---- lane phase ----
     if (open) {
-      const int row_bits = (int)(row0 + step0);
       if (full_block)
-        open = encode_tile_rows<false>(sh, tile_bytes, payload_column, lane32, row_bits, step0,
-                                       valid, budget_bits, pos, lo, extra_start);
+        open = encode_tile_rows<false>(sh, tile_bytes, payload_column, lane32, step0, valid,
+                                       budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(sh, tile_bytes, payload_column, lane32, row_bits, step0,
-                                      valid, budget_bits, pos, lo, extra_start);
+        open = encode_tile_rows<true>(sh, tile_bytes, payload_column, lane32, step0, valid,
+                                      budget_bits, pos, lo, extra_start);
     }
     __syncwarp();
   }

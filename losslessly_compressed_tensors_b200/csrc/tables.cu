@@ -92,10 +92,12 @@ shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __re
 
 // Two symbols per lookup over 12 stream bits, in table-index space (so it is
 // valid for every center).  The second symbol is present only when both codes
-// are direct and fit in the 12 bits together.
+// are direct and fit in the 12 bits together.  The entry for stream window i
+// is stored at table_slot(i) (common.cuh).
 __global__ void __launch_bounds__(kTableThreads)
 pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pair_table) {
-  for (int i = threadIdx.x; i < kPairEntries; i += blockDim.x) {
+  for (int slot = threadIdx.x; slot < kPairEntries; slot += blockDim.x) {
+    const int i = (int)table_window((uint32_t)slot);
     const int32_t first = decode[i & kFirstMask];
     uint32_t entry;
     if (first == 0) {
@@ -112,7 +114,7 @@ pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pai
         entry |= kSlow | (len0 << 16);
       }
     }
-    pair_table[i] = entry;
+    pair_table[slot] = entry;
   }
 }
 

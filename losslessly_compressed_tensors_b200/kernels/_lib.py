@@ -10,7 +10,8 @@ import ctypes
 import os
 
 _PACKAGE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIBRARY_PATH = os.path.join(_PACKAGE, "liblct_b200.so")
+# LCT_B200_LIBRARY points at an alternative build of the same library (e.g. a debug build).
+LIBRARY_PATH = os.environ.get("LCT_B200_LIBRARY") or os.path.join(_PACKAGE, "liblct_b200.so")
 
 _p = ctypes.c_void_p
 _i = ctypes.c_int
