@@ -40,6 +40,7 @@ extern "C" {
 #define LCT_E_ALIGNMENT (-3)     /* a buffer that must be 16-byte aligned is not */
 #define LCT_E_BAD_ARGUMENT (-4)
 #define LCT_E_TOO_LARGE (-5)
+#define LCT_E_SCRATCH_LIMIT (-6) /* tensor too large for the built-in scratch of lct_encode_noalloc */
 
 /* Overflow ("fallback") storage of one compressed tensor, as the decoders see
  * it.  mode 0: the tensor has no overflow streams, the other fields are
@@ -132,6 +133,34 @@ int lct_compact_tails(const void *src, uint8_t *lanes, uint8_t *starts, uint8_t 
                       const uint8_t *extra_starts, const int32_t *summaries, int64_t size,
                       int64_t logical_numel, int block_symbols, int steps, int precomputed,
                       void *stream);
+
+/* lct_encode followed by the summary scan of lct_scan_allocate (no arena), for
+ * callers that cannot allocate device memory: a serving loop that forbids
+ * allocation once it has started, a host whose device memory all belongs to
+ * another pool, a plain C program with no allocator.  The two work buffers lct_encode takes from its caller
+ * (extra_starts, summaries) are replaced by a 272 KiB array inside the library
+ * image, one per GPU that loads the library, held until the process exits.
+ * The caller passes only the source, the outputs side[size] and
+ * encoded[streams*fixed_words + 4], and counts[4], which receives the number of
+ * overflow streams and their tail bytes (counts[2..3] = 0); counts[0] == 0
+ * means side + encoded are the complete compressed form, otherwise finish with
+ * the regular lct_encode / lct_compact_tails sequence.
+ *   - Limit: at most 1024 codec blocks (64 Mi elements in the 65536-element
+ *     layouts, 32 Mi in the 32768-element ones); a larger tensor is rejected
+ *     with LCT_E_SCRATCH_LIMIT before anything is launched.
+ *   - Calls no cudaMalloc/cudaFree nor any allocating routine.  The first
+ *     call on each GPU looks up the array's device address
+ *     (cudaGetSymbolAddress, with that GPU current); make that first call
+ *     outside any stream capture.
+ *   - Every call on a GPU uses the same array.  Nothing in it needs clearing
+ *     between calls (each call rewrites all it reads), but two calls that
+ *     overlap on the GPU, e.g. on different streams, race on it.
+ * Has no counterpart in the reference, whose host code allocates these
+ * buffers with torch.empty on every encode. */
+int lct_encode_noalloc(const void *src, uint8_t *side, int32_t *encoded,
+                       const int32_t *shifted_encode, int32_t *counts, int64_t size,
+                       int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                       int precomputed, void *stream);
 
 /* ---- decode and fused operations ------------------------------------------ */
 

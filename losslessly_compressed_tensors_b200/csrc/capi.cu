@@ -15,6 +15,8 @@ const char* lct_error_string(int code) {
     case LCT_E_ALIGNMENT: return "buffer is not aligned as required";
     case LCT_E_BAD_ARGUMENT: return "argument out of range";
     case LCT_E_TOO_LARGE: return "tensor has too many blocks for one launch";
+    case LCT_E_SCRATCH_LIMIT:
+      return "tensor exceeds the built-in scratch of lct_encode_noalloc (1024 codec blocks)";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -396,3 +396,84 @@ int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Encode without any caller-side scratch: lct_encode_noalloc
+// ---------------------------------------------------------------------------
+//
+// lct_encode needs two work buffers from its caller (one "first overflow step"
+// byte per stream and four ints per block) that exist only to be handed to the
+// summary scan.  Some callers cannot provide them: a serving loop that must
+// not allocate once it has started, a host that gave all device memory to
+// another allocator at start-up, or a C program that links this library and
+// has no allocator at all.  For them the work buffers below live in the
+// library image itself.  The first call on a GPU looks the array's address up
+// and should come before any stream capture.
+
+namespace lct {
+
+// Largest tensor the built-in scratch serves: 1024 codec blocks (64 Mi
+// elements in the 65536-element layouts, 32 Mi in the 32768-element ones).
+constexpr int kNoAllocMaxBlocks = 1024;
+constexpr size_t kNoAllocSummaryBytes = (size_t)kNoAllocMaxBlocks * 4 * sizeof(int32_t);
+constexpr size_t kNoAllocBytes = kNoAllocSummaryBytes + (size_t)kNoAllocMaxBlocks * kLanes;
+
+// 272 KiB per GPU that loads the library, held until the process exits.
+// [0, 16 KiB): block summaries, int32[4 * blocks]; then one byte per stream.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+static unsigned char* g_noalloc_address[kMaxDevices];  // device address of the array, per GPU
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an
+// address a kernel may use; the device address has to be asked for, once per
+// GPU, while that GPU is current.  Returns 0 or a cudaError_t.
+static int noalloc_scratch_address(unsigned char** out) {
+  int device = -1;
+  cudaError_t rc = cudaGetDevice(&device);
+  if (rc != cudaSuccess) return (int)rc;
+  if (device < 0 || device >= kMaxDevices) return LCT_E_BAD_ARGUMENT;
+  unsigned char* known = __atomic_load_n(&g_noalloc_address[device], __ATOMIC_ACQUIRE);
+  if (known == nullptr) {
+    void* address = nullptr;
+    rc = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+    if (rc != cudaSuccess) return (int)rc;
+    if (address == nullptr) return (int)cudaErrorInvalidSymbol;
+    known = static_cast<unsigned char*>(address);
+    // Two threads racing here store the same value.
+    __atomic_store_n(&g_noalloc_address[device], known, __ATOMIC_RELEASE);
+  }
+  *out = known;
+  return 0;
+}
+
+}  // namespace lct
+
+extern "C" {
+
+int lct_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
+                      void* arena_storage, int64_t blocks, int max_free_regions, void* stream);
+
+int lct_encode_noalloc(const void* src, uint8_t* side, int32_t* encoded,
+                       const int32_t* shifted_encode, int32_t* counts, int64_t size,
+                       int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                       int precomputed, void* stream) {
+  if (counts == nullptr) return LCT_E_NULL_POINTER;
+  if (block_symbols <= 0 || size <= 0) return LCT_E_BAD_ARGUMENT;
+  const int64_t blocks = (size + block_symbols - 1) / block_symbols;
+  if (blocks > lct::kNoAllocMaxBlocks) return LCT_E_SCRATCH_LIMIT;
+  unsigned char* scratch = nullptr;
+  int rc = lct::noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  int32_t* summaries = reinterpret_cast<int32_t*>(scratch);
+  uint8_t* extra_starts = scratch + lct::kNoAllocSummaryBytes;
+  // Both kernels overwrite every scratch byte they later read (all streams of
+  // the tensor, all four summary rows), so nothing left by an earlier call is
+  // ever consumed and nothing has to be cleared first.
+  rc = lct_encode(src, side, encoded, shifted_encode, extra_starts, summaries, size, logical_numel,
+                  block_symbols, steps, fixed_words, precomputed, stream);
+  if (rc) return rc;
+  return lct_scan_allocate(summaries, counts, nullptr, nullptr, blocks, 256, stream);
+}
+
+}  // extern "C"

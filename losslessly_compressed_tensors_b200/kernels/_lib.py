@@ -42,6 +42,7 @@ _SIGNATURES = {
     "lct_center_and_tables": [_p, _i64, _i, _p, _p, _p, _p, _p, _p],
     "lct_shift_tables": [_p, _p, _p, _p, _p, _p],
     "lct_encode": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _p],
+    "lct_encode_noalloc": [_p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _p],
     "lct_scan_allocate": [_p, _p, _p, _p, _i64, _i, _p],
     "lct_compact_tails": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _p],
     "lct_decode": [ctypes.POINTER(Operand), _p, _i64, _i64, _i, _i, _i, _i, _p],
