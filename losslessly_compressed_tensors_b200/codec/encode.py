@@ -39,9 +39,14 @@ def encode_components(
     precomputed: bool,
     center: torch.Tensor | None = None,
     logical_numel: int,
+    out=None,
 ) -> CompressedTensor:
     """Encode int16 BF16 bits, or (``precomputed``) uint8 exponent bytes in logical order
-    whose side bytes already sit in ``sign_mantissa``.  ``size`` is the padded element count."""
+    whose side bytes already sit in ``sign_mantissa``.  ``size`` is the padded element count.
+
+    ``out`` (not in the reference): an object with ``take(name, numel, dtype) -> Tensor`` that
+    supplies the storage of the buffered result's persistent tensors (``encoded``, ``counts``,
+    ``blocks``, ``center``, ``decode_table``, ``descriptor``), e.g. slices of a wire buffer."""
     if buffer is not None and buffer.capacity_bytes % 4:
         raise ValueError("TensorBuffer capacity must be divisible by 4")
     device = source_values.device
@@ -54,10 +59,15 @@ def encode_components(
     def scratch(n, dtype):
         return torch.empty(n, dtype=dtype, device=device)
 
+    def kept(name, n, dtype):
+        return scratch(n, dtype) if out is None else out.take(name, n, dtype)
+
+    if out is not None and buffer is None:
+        raise ValueError("placing the result needs a shared buffer (sizes must not depend on the data)")
     shifted_encode = scratch(256, torch.int32)
-    shifted_decode = torch.empty_like(decode_table)
+    shifted_decode = kept("decode_table", decode_table.numel(), torch.int32)
     if center is None:
-        center = scratch(1, torch.int32)
+        center = kept("center", 1, torch.int32)
         dispatch.estimate_and_shift_encoding_table(
             source_values, center, logical_numel, encode_table, shifted_encode,
             decode_table, shifted_decode, min(logical_numel, CENTER_SAMPLE_SIZE), precomputed,
@@ -66,11 +76,11 @@ def encode_components(
         dispatch.shift_encoding_table(encode_table, center, shifted_encode, decode_table,
                                       shifted_decode)
 
-    encoded = scratch(streams * fixed_words + 4, torch.int32)
+    encoded = kept("encoded", streams * fixed_words + 4, torch.int32)
     extra_starts = scratch(streams, torch.uint8)
     summaries = scratch(4 * blocks, torch.int32)
-    counts = scratch(4, torch.int32)
-    blocks_out = scratch(3 * blocks, torch.int32)
+    counts = kept("counts", 4, torch.int32)
+    blocks_out = kept("blocks", 3 * blocks, torch.int32)
     if blocks == 0:
         # Nothing to encode: an empty tensor keeps well-defined (zero) metadata.
         encoded.zero_()
@@ -85,7 +95,7 @@ def encode_components(
 
     buffered = buffer is not None
     if buffered:
-        descriptor = scratch(4, torch.int32)
+        descriptor = kept("descriptor", 4, torch.int32)
         if blocks:
             dispatch.prefix_allocate(summaries, counts, descriptor, buffer, blocks, True,
                                      buffer.max_free_regions)
@@ -130,8 +140,9 @@ def encode_components(
 
 
 def encode(data: torch.Tensor, distribution: Distribution, buffer: TensorBuffer | None = None, *,
-           allow_raw: bool = False) -> CompressedTensor:
-    """Compress a BF16 tensor of any shape through the flattened, block-padded layout."""
+           allow_raw: bool = False, out=None) -> CompressedTensor:
+    """Compress a BF16 tensor of any shape through the flattened, block-padded layout.
+    ``out``: optional placement of the result's tensors, see ``encode_components``."""
     if data.dtype != torch.bfloat16:
         raise TypeError(f"the codec compresses bfloat16 tensors, got {data.dtype}")
     shape = tuple(data.shape)
@@ -146,8 +157,11 @@ def encode(data: torch.Tensor, distribution: Distribution, buffer: TensorBuffer 
         if smallest > logical_numel * data.element_size():
             return CompressedTensor(source, logical_numel, buffer=buffer, distribution=distribution,
                                     shape=shape, layout=StorageLayout.RAW)
-    sign_mantissa = torch.empty(storage_numel, dtype=torch.uint8, device=source.device)
+    if out is None:
+        sign_mantissa = torch.empty(storage_numel, dtype=torch.uint8, device=source.device)
+    else:
+        sign_mantissa = out.take("side", storage_numel, torch.uint8)
     return encode_components(
         source.view(torch.int16), sign_mantissa, storage_numel, distribution, buffer, shape,
-        precomputed=False, logical_numel=logical_numel,
+        precomputed=False, logical_numel=logical_numel, out=out,
     )

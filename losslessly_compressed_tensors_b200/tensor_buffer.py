@@ -63,7 +63,10 @@ class TensorBuffer:
     """
 
     def __init__(self, capacity_bytes: int, *, max_free_regions: int = 256,
-                 device: torch.device | str | None = None) -> None:
+                 device: torch.device | str | None = None,
+                 storage: torch.Tensor | None = None) -> None:
+        """``storage`` (not in the reference): build the arena inside an existing uint8 tensor of
+        ``storage_bytes(capacity_bytes, max_free_regions)`` bytes, e.g. a slice of a wire buffer."""
         if capacity_bytes > torch.iinfo(torch.int32).max:
             raise ValueError("capacity_bytes must fit in int32")
         if max_free_regions <= 0 or max_free_regions & (max_free_regions - 1):
@@ -72,8 +75,17 @@ class TensorBuffer:
         self.max_free_regions = int(max_free_regions)
         regions = self.max_free_regions
         self._metadata_bytes = self._align(8 * regions + 12)
-        self._storage = torch.zeros(self._metadata_bytes + self.capacity_bytes, dtype=torch.uint8,
-                                    device=torch.device(device or "cuda"))
+        if storage is None:
+            self._storage = torch.zeros(self._metadata_bytes + self.capacity_bytes,
+                                        dtype=torch.uint8, device=torch.device(device or "cuda"))
+        else:
+            if (storage.dtype != torch.uint8 or storage.dim() != 1 or not storage.is_contiguous()
+                    or storage.numel() != self._metadata_bytes + self.capacity_bytes
+                    or storage.data_ptr() % _ALIGNMENT):
+                raise ValueError("storage must be a contiguous, 16-byte aligned uint8 tensor of "
+                                 "storage_bytes(capacity_bytes, max_free_regions) bytes")
+            self._storage = storage
+            self._storage[: self._metadata_bytes].zero_()
         self.device = self._storage.device
         words = self._storage[: 8 * regions + 12].view(torch.int32)
         self._free_starts = words[:regions]
@@ -87,6 +99,11 @@ class TensorBuffer:
     @staticmethod
     def _align(nbytes: int) -> int:
         return -(-nbytes // _ALIGNMENT) * _ALIGNMENT
+
+    @classmethod
+    def storage_bytes(cls, capacity_bytes: int, max_free_regions: int = 256) -> int:
+        """Bytes of the backing tensor: allocator words, padding, then the payload."""
+        return cls._align(8 * max_free_regions + 12) + int(capacity_bytes)
 
     @property
     def data(self) -> torch.Tensor:

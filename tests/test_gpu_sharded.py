@@ -1,0 +1,69 @@
+"""GPU side of the sharded weight-set path: ranks are emulated one after the other on one GPU
+(the collective itself is covered by the gloo test and by bench.py on several GPUs)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import oracle_compress
+from gpu_helpers import assert_same_components, bits_of
+from losslessly_compressed_tensors_b200 import sharded
+from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
+from losslessly_compressed_tensors_b200.tensor_buffer import verify_buffer
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [("emb", (2000, 96)), ("w1", (96, 384)), ("b1", (384,)), ("w2", (384, 96)), ("b2", (96,)),
+          ("ln", (96,)), ("odd", (77, 1031))]
+
+
+def _weights():
+    g = torch.Generator().manual_seed(5)
+    out = []
+    for i, (_, shape) in enumerate(SHAPES):
+        scale = 30.0 if i == 6 else 0.02
+        w = torch.randn(shape, generator=g) * scale
+        if i == 6:
+            w = w * torch.exp(torch.randn(shape, generator=g) * 4)   # forces overflow tails
+        out.append(w.to(torch.bfloat16))
+    out[5].fill_(1.0)
+    out[4].zero_()
+    return out
+
+
+@pytest.mark.parametrize("world,row_shard", [(1, None), (3, None), (3, 30000), (8, 50000)])
+def test_encode_gather_decode_round_trip(oracle, world, row_shard):
+    dist = Distribution(DistType.EMPIRICAL)
+    host = _weights()
+    tensors = [w.cuda() for w in host]
+    plan = sharded.make_plan(SHAPES, world, dist, row_shard_elements=row_shard, arena_fraction=0.5)
+    wires = []
+    for rank in range(world):
+        wire, compressed, arena = sharded.encode_rank(plan, rank, tensors)
+        assert wire.numel() == plan.wire_bytes and len(compressed) == len(plan.shards[rank])
+        verify_buffer(arena)
+        # every shard equals the oracle's encoding of that shard, arena offsets included
+        model = oracle.new_arena(plan.arena_capacity, plan.max_free_regions)
+        for shard, c in zip(plan.shards[rank], compressed):
+            bits = bits_of(host[shard.index][shard.row_start:shard.row_stop])
+            assert_same_components(c, oracle_compress(oracle, bits, dist, model), shard.name)
+        wires.append(wire)
+    gathered = torch.cat(wires)          # what all_gather_into_tensor leaves on every rank
+    assert torch.equal(sharded.all_gather_wire(wires[0], plan), wires[0]) if world == 1 else True
+    restored = sharded.decode_all(plan, gathered, [s for _, s in SHAPES])
+    for want, got in zip(host, restored):
+        assert got.shape == want.shape
+        assert np.array_equal(bits_of(got), bits_of(want))
+    shards = sum(len(r) for r in plan.shards)
+    assert len(sharded.views_of(plan, gathered)) == shards
+
+
+def test_wire_buffer_is_reusable():
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 1, dist, arena_fraction=0.5)
+    wire, _, _ = sharded.encode_rank(plan, 0, tensors)
+    first = wire.clone()
+    wire2, _, _ = sharded.encode_rank(plan, 0, tensors, wire=wire)   # second step of a training loop
+    assert wire2 is wire and torch.equal(wire, first)
+    with pytest.raises(ValueError):
+        sharded.encode_rank(plan, 0, tensors, wire=torch.zeros(16, dtype=torch.uint8, device="cuda"))
