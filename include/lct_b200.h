@@ -162,6 +162,35 @@ int lct_encode_noalloc(const void *src, uint8_t *side, int32_t *encoded,
                        int64_t logical_numel, int block_symbols, int steps, int fixed_words,
                        int precomputed, void *stream);
 
+/* Many tensors of ONE codebook and geometry compressed by four launches in
+ * total (centers, encode, scan + arena reservations in job order, tails),
+ * overflow tails in a shared arena.  Equivalent to calling
+ * lct_center_and_tables, lct_encode, lct_scan_allocate and lct_compact_tails
+ * once per job, in job order, and leaves the same bytes everywhere.  `jobs` is
+ * a DEVICE array sorted by first_block.  Work buffers: extra_starts
+ * uint8[256 * total_blocks], summaries int32[4 * total_blocks] (job j uses
+ * the 4 * blocks_j ints from 4 * first_block), shifted_encode int32[256 * n_jobs].
+ * No counterpart in the reference, which encodes one tensor per call. */
+typedef struct lct_encode_job {
+  const void *src;          /* int16 BF16 bits, any alignment */
+  uint8_t *side;            /* uint8[size] */
+  int32_t *encoded;         /* int32[streams*fixed_words + 4] */
+  int32_t *center;          /* int32[1] */
+  int32_t *shifted_decode;  /* int32[1024] */
+  int32_t *counts;          /* int32[4] */
+  int32_t *descriptor;      /* int32[4] */
+  int32_t *blocks_out;      /* int32[3*blocks] */
+  int64_t size;
+  int64_t logical_numel;
+  int64_t first_block;
+} lct_encode_job;
+
+int lct_compress_batch(const lct_encode_job *jobs /* device */, int n_jobs, int64_t total_blocks,
+                       const int32_t *encode_table, const int32_t *decode_table,
+                       void *arena_storage, int max_free_regions, uint8_t *extra_starts,
+                       int32_t *summaries, int32_t *shifted_encode, int block_symbols, int steps,
+                       int fixed_words, void *stream);
+
 /* ---- decode and fused operations ------------------------------------------ */
 
 /* Decode to int16 BF16 bits out[logical_numel], overflow tails substituted in
@@ -170,6 +199,23 @@ int lct_encode_noalloc(const void *src, uint8_t *side, int32_t *encoded,
 int lct_decode(const lct_operand *a /* host pointer */, int16_t *out, int64_t size,
                int64_t logical_numel, int block_symbols, int steps, int fixed_words,
                int rare_length, void *stream);
+
+/* Many compressed tensors of ONE geometry decoded by one launch (weight sets
+ * with many small tensors are launch-bound otherwise).  `jobs` is a DEVICE
+ * array sorted by first_block; job j owns CTAs [first_block, first_block +
+ * size/block_symbols).  Each job's `out` must be 16-byte aligned.  No
+ * counterpart in the reference, which decodes one tensor per launch. */
+typedef struct lct_decode_job {
+  lct_operand operand;
+  int16_t *out;          /* int16[logical_numel] */
+  int64_t size;          /* padded element count */
+  int64_t logical_numel;
+  int64_t first_block;   /* sum of the earlier jobs' block counts */
+} lct_decode_job;
+
+int lct_decode_batch(const lct_decode_job *jobs /* device */, int n_jobs, int64_t total_blocks,
+                     int block_symbols, int steps, int fixed_words, int rare_length,
+                     void *stream);
 
 #define LCT_OP_ADD 0            /* bf16(a + b)            generic/pointwise.py:340-343 */
 #define LCT_OP_MULTIPLY 1       /* bf16(a * b)            generic/pointwise.py:346-349 */

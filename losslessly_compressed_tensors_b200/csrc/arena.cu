@@ -2,6 +2,7 @@
 // per-tensor scan of block overflow summaries that feeds it.  Every launch is
 // a single CTA; nothing here waits on another kernel, and the one lock wait is
 // bounded (status 7 when it gives up).
+#include "batch.cuh"
 #include "common.cuh"
 #include "lct_b200.h"
 
@@ -146,6 +147,71 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
     arena_allocate(arena_of(arena_storage, regions), regions, running_bytes + 2 * running_count,
                    descriptor, alloc_scratch);
   }
+}
+
+// All jobs of a batch.  Phase 1: every warp takes jobs in turn and scans that
+// job's block summaries with shuffles.  Phase 2: the reservations, strictly in
+// job order (so the arena ends up exactly as after one call per job); jobs
+// without overflow get the "empty request" descriptor without touching the lock,
+// which is what the locked path would have written.
+__global__ void __launch_bounds__(kScanThreads)
+scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* summaries,
+                  void* arena_storage, int regions, int block_symbols) {
+  __shared__ int alloc_scratch[2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int j = warp; j < n_jobs; j += warps) {
+    const lct_encode_job& job = jobs[j];
+    const int64_t blocks = job.size / block_symbols;
+    int32_t* rows = summaries + 4 * job.first_block;
+    int running_count = 0, running_bytes = 0;
+    for (int64_t base = 0; base < blocks; base += 32) {
+      const int64_t i = base + lane;
+      const int c = i < blocks ? rows[i] : 0;
+      const int t = i < blocks ? rows[blocks + i] : 0;
+      int ic = c, it = t;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, d), ut = __shfl_up_sync(0xFFFFFFFFu, it, d);
+        if (lane >= d) { ic += uc; it += ut; }
+      }
+      if (i < blocks) {
+        rows[2 * blocks + i] = running_count + ic - c;
+        rows[3 * blocks + i] = running_bytes + it - t;
+      }
+      running_count += __shfl_sync(0xFFFFFFFFu, ic, 31);
+      running_bytes += __shfl_sync(0xFFFFFFFFu, it, 31);
+    }
+    if (lane == 0) {
+      job.counts[0] = running_count;
+      job.counts[1] = running_bytes;
+      job.counts[2] = 0;
+      job.counts[3] = 0;
+    }
+  }
+  __threadfence_block();
+  __syncthreads();
+  const Arena arena = arena_of(arena_storage, regions);
+  for (int j = 0; j < n_jobs; ++j) {
+    const lct_encode_job& job = jobs[j];
+    const int32_t request = job.counts[1] + 2 * job.counts[0];  // uniform across the CTA
+    if (request > 0) {
+      arena_allocate(arena, regions, request, job.descriptor, alloc_scratch);
+      __syncthreads();
+    } else if (threadIdx.x == 0) {
+      job.descriptor[0] = -1;
+      job.descriptor[1] = 0;
+      job.descriptor[2] = 2;
+      job.descriptor[3] = *arena.generation;
+    }
+  }
+}
+
+int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries,
+                      void* arena_storage, int max_free_regions, int block_symbols,
+                      cudaStream_t stream) {
+  scan_batch_kernel<<<1, kScanThreads, 0, stream>>>(jobs, n_jobs, summaries, arena_storage,
+                                                    max_free_regions, block_symbols);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace lct

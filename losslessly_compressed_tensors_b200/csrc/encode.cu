@@ -14,7 +14,9 @@
 // At the end the payload image (zero where nothing was written, so the output
 // is deterministic) is copied out with coalesced 128-bit stores, and the
 // block's overflow summary is reduced.
+#include "batch.cuh"
 #include "common.cuh"
+#include "encode_core.cuh"
 #include "lct_b200.h"
 
 namespace lct {
@@ -86,52 +88,20 @@ __device__ __forceinline__ UnitSource load_unit(const void* src, int64_t at, int
   return u;
 }
 
-// Lane phase of one tile.  Returns false once the lane has overflowed.
-template <bool kCheckValid>
-__device__ __forceinline__ bool encode_tile_rows(const EncodeSharedHead& sh, const uint8_t* tile_bytes,
-                                                 uint32_t* payload_column, int lane32,
-                                                 int step0, int valid, int budget_bits, int& pos,
-                                                 uint32_t& lo, int& extra_start) {
-#pragma unroll
-  for (int p = 0; p < kTilePairs; ++p) {
-    // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
-    const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ (2 * p)));
-    uint2 c0 = sh.table[e[0]];
-    uint2 c1 = sh.table[e[1]];
-    if (kCheckValid) {  // padding carries no bits
-      if (step0 + 2 * p >= valid) c0 = make_uint2(0u, 0u);
-      if (step0 + 2 * p + 1 >= valid) c1 = make_uint2(0u, 0u);
-    }
-    const uint32_t code = c0.x | (c1.x << c0.y);
-    const int length = (int)(c0.y + c1.y);
-    const int shift = pos & 31;
-    const int next = pos + length;
-    if (next > budget_bits) {
-      // First pair that does not fit: freeze the current word and stop.
-      extra_start = step0 + 2 * p;
-      if (pos < budget_bits) payload_column[(pos >> 5) * kLanes] = lo;
-      return false;
-    }
-    lo |= code << shift;
-    if (shift + length >= 32) {
-      payload_column[(pos >> 5) * kLanes] = lo;
-      lo = __funnelshift_l(code, 0u, shift);  // the bits that did not fit; 0 when shift == 0
-    }
-    pos = next;
-  }
-  return true;
-}
-
+// One codec block.  extra_starts and summaries are the tensor's own arrays
+// (summaries holds g.n_blocks entries per row).
 template <bool kPrecomputed>
-__global__ void __launch_bounds__(kThreads, 4)
-encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
-              uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
-              uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
+__device__ __forceinline__ void encode_block(const void* __restrict__ src, bool src_vector_ok,
+                                             uint8_t* __restrict__ side,
+                                             uint32_t* __restrict__ encoded,
+                                             const int32_t* __restrict__ shifted_encode,
+                                             uint8_t* __restrict__ extra_starts,
+                                             int32_t* __restrict__ summaries, const EncodeShape& g,
+                                             int64_t block) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   EncodeSharedHead& sh = *reinterpret_cast<EncodeSharedHead*>(smem_raw);
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(EncodeSharedHead));
 
-  const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
@@ -213,10 +183,10 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
     // ---- lane phase ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(sh, tile_bytes, payload_column, lane32, step0, valid,
+        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, lane32, step0, valid,
                                        budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(sh, tile_bytes, payload_column, lane32, step0, valid,
+        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, lane32, step0, valid,
                                       budget_bits, pos, lo, extra_start);
     }
     __syncwarp();
@@ -249,18 +219,62 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
   }
 }
 
+template <bool kPrecomputed>
+__global__ void __launch_bounds__(kThreads, 4)
+encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
+              uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
+              uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
+  encode_block<kPrecomputed>(src, src_vector_ok, side, encoded, shifted_encode, extra_starts,
+                             summaries, g, blockIdx.x);
+}
+
+// Shape of one job of a batch (all jobs share the geometry in `common`).
+__device__ __forceinline__ EncodeShape shape_of_job(const lct_encode_job& job,
+                                                    const EncodeShape& common) {
+  EncodeShape g = common;
+  g.size = job.size;
+  g.logical_numel = job.logical_numel;
+  g.n_blocks = job.size / common.block_symbols;
+  g.streams = g.n_blocks * kLanes;
+  return g;
+}
+
+__device__ __forceinline__ int find_encode_job(const lct_encode_job* jobs, int n_jobs, int64_t block) {
+  int lo = 0, hi = n_jobs - 1;
+  while (lo < hi) {  // last job with first_block <= block
+    const int mid = (lo + hi + 1) >> 1;
+    if (jobs[mid].first_block <= block) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kThreads, 4)
+encode_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs,
+                    const int32_t* __restrict__ shifted_encode, uint8_t* __restrict__ extra_starts,
+                    int32_t* __restrict__ summaries, EncodeShape common) {
+  const int64_t block = blockIdx.x;
+  const int j = find_encode_job(jobs, n_jobs, block);
+  const lct_encode_job& job = jobs[j];
+  const EncodeShape g = shape_of_job(job, common);
+  const bool vector_ok = (reinterpret_cast<uintptr_t>(job.src) & 15u) == 0;
+  encode_block<false>(job.src, vector_ok, job.side, reinterpret_cast<uint32_t*>(job.encoded),
+                      shifted_encode + 256 * (int64_t)j, extra_starts + job.first_block * kLanes,
+                      summaries + 4 * job.first_block, g, block - job.first_block);
+}
+
 // Compact overflow metadata and raw exponent tails of one block.  Lanes are
 // listed in increasing order; a lane's tail holds exponent - 127 for every
 // row from its overflow start to the end of the block (padding rows read as
 // exponent byte 0).
 template <bool kPrecomputed>
-__global__ void __launch_bounds__(kThreads)
-compact_tails_kernel(const void* __restrict__ src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
-                     const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
-                     const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
-                     EncodeShape g) {
+__device__ __forceinline__ void compact_block(const void* __restrict__ src, uint8_t* lanes,
+                                              uint8_t* starts, uint8_t* tail,
+                                              const int32_t* descriptor, const int32_t* counts,
+                                              int32_t* blocks_out,
+                                              const uint8_t* __restrict__ extra_starts,
+                                              const int32_t* __restrict__ summaries,
+                                              const EncodeShape& g, int64_t block) {
   __shared__ int scan[33];
-  const int64_t block = blockIdx.x;
   const int tid = threadIdx.x;
   const int count = summaries[block];
   const int first = summaries[2 * g.n_blocks + block];
@@ -312,6 +326,28 @@ compact_tails_kernel(const void* __restrict__ src, uint8_t* lanes, uint8_t* star
       dst[row - lane_start] = (uint8_t)(byte - 127);
     }
   }
+}
+
+template <bool kPrecomputed>
+__global__ void __launch_bounds__(kThreads)
+compact_tails_kernel(const void* __restrict__ src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
+                     const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
+                     const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
+                     EncodeShape g) {
+  compact_block<kPrecomputed>(src, lanes, starts, tail, descriptor, counts, blocks_out,
+                              extra_starts, summaries, g, blockIdx.x);
+}
+
+__global__ void __launch_bounds__(kThreads)
+compact_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, uint8_t* arena_payload,
+                     const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
+                     EncodeShape common) {
+  const int64_t block = blockIdx.x;
+  const lct_encode_job& job = jobs[find_encode_job(jobs, n_jobs, block)];
+  const EncodeShape g = shape_of_job(job, common);
+  compact_block<false>(job.src, arena_payload, arena_payload, arena_payload, job.descriptor,
+                       job.counts, job.blocks_out, extra_starts + job.first_block * kLanes,
+                       summaries + 4 * job.first_block, g, block - job.first_block);
 }
 
 static int check_encode_shape(int64_t size, int64_t logical_numel, int block_symbols, int steps,
@@ -392,6 +428,44 @@ int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t*
   else
     lct::compact_tails_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, 0, st>>>(
         src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts, summaries, g);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int lct_compress_batch(const lct_encode_job* jobs, int n_jobs, int64_t total_blocks,
+                       const int32_t* encode_table, const int32_t* decode_table,
+                       void* arena_storage, int max_free_regions, uint8_t* extra_starts,
+                       int32_t* summaries, int32_t* shifted_encode, int block_symbols, int steps,
+                       int fixed_words, void* stream) {
+  if (jobs == nullptr || encode_table == nullptr || decode_table == nullptr ||
+      arena_storage == nullptr || extra_starts == nullptr || summaries == nullptr ||
+      shifted_encode == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (n_jobs <= 0 || total_blocks <= 0 || total_blocks > 0x7FFFFFFFLL) return LCT_E_BAD_ARGUMENT;
+  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
+  lct::EncodeShape g;
+  int rc = lct::check_encode_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words, &g);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((rc = lct::launch_center_batch(jobs, n_jobs, encode_table, decode_table, shifted_encode, st)))
+    return rc;
+  const size_t shared = sizeof(lct::EncodeSharedHead) + (size_t)fixed_words * lct::kLanes * 4;
+  rc = (int)cudaFuncSetAttribute(lct::encode_batch_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+  if (rc) return rc;
+  lct::encode_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, shared, st>>>(
+      jobs, n_jobs, shifted_encode, extra_starts, summaries, g);
+  if ((rc = (int)cudaGetLastError())) return rc;
+  if ((rc = lct::launch_scan_batch(jobs, n_jobs, summaries, arena_storage, max_free_regions,
+                                   block_symbols, st)))
+    return rc;
+  // The arena payload starts after the allocator words, padded to 16 bytes.
+  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
+  lct::compact_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, 0, st>>>(
+      jobs, n_jobs, static_cast<uint8_t*>(arena_storage) + metadata, extra_starts, summaries, g);
   return (int)cudaGetLastError();
 }
 

@@ -1,0 +1,45 @@
+// Lane side of the encoder, shared by the encode kernels and the fused update
+// kernel: append one tile's exponent pairs of a lane to its bit stream.
+#pragma once
+
+#include "common.cuh"
+
+namespace lct {
+
+// Lane phase of one tile.  Returns false once the lane has overflowed.
+template <bool kCheckValid>
+__device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8_t* tile_bytes,
+                                                 uint32_t* payload_column, int lane32,
+                                                 int step0, int valid, int budget_bits, int& pos,
+                                                 uint32_t& lo, int& extra_start) {
+#pragma unroll
+  for (int p = 0; p < kTilePairs; ++p) {
+    // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
+    const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ (2 * p)));
+    uint2 c0 = table[e[0]];
+    uint2 c1 = table[e[1]];
+    if (kCheckValid) {  // padding carries no bits
+      if (step0 + 2 * p >= valid) c0 = make_uint2(0u, 0u);
+      if (step0 + 2 * p + 1 >= valid) c1 = make_uint2(0u, 0u);
+    }
+    const uint32_t code = c0.x | (c1.x << c0.y);
+    const int length = (int)(c0.y + c1.y);
+    const int shift = pos & 31;
+    const int next = pos + length;
+    if (next > budget_bits) {
+      // First pair that does not fit: freeze the current word and stop.
+      extra_start = step0 + 2 * p;
+      if (pos < budget_bits) payload_column[(pos >> 5) * kLanes] = lo;
+      return false;
+    }
+    lo |= code << shift;
+    if (shift + length >= 32) {
+      payload_column[(pos >> 5) * kLanes] = lo;
+      lo = __funnelshift_l(code, 0u, shift);  // the bits that did not fit; 0 when shift == 0
+    }
+    pos = next;
+  }
+  return true;
+}
+
+}  // namespace lct

@@ -1,5 +1,6 @@
 // Codebook preparation kernels: exponent-center sampling, per-tensor shifted
 // tables, and the per-codebook two-symbol lookup table.
+#include "batch.cuh"
 #include "common.cuh"
 #include "lct_b200.h"
 
@@ -40,11 +41,11 @@ __device__ __forceinline__ void write_shifted_tables(const int32_t* __restrict__
 // positions; the mean exponent of the samples with exponent >= -120, rounded
 // half away from zero, is the center.
 template <bool kPrecomputed>
-__global__ void __launch_bounds__(kTableThreads)
-center_and_tables_kernel(const void* __restrict__ src, int64_t n,
-                         const int32_t* __restrict__ base_encode,
-                         const int32_t* __restrict__ base_decode, int32_t* center_out,
-                         int32_t* shifted_encode, int32_t* shifted_decode) {
+__device__ __forceinline__ void center_and_tables(const void* __restrict__ src, int64_t n,
+                                                  const int32_t* __restrict__ base_encode,
+                                                  const int32_t* __restrict__ base_decode,
+                                                  int32_t* center_out, int32_t* shifted_encode,
+                                                  int32_t* shifted_decode) {
   __shared__ int s_sum[32], s_kept[32], s_center;
   const int64_t samples = n < kCenterSamples ? n : kCenterSamples;
   int sum = 0, kept = 0;
@@ -83,6 +84,24 @@ center_and_tables_kernel(const void* __restrict__ src, int64_t n,
   write_shifted_tables(base_encode, base_decode, s_center, shifted_encode, shifted_decode);
 }
 
+template <bool kPrecomputed>
+__global__ void __launch_bounds__(kTableThreads)
+center_and_tables_kernel(const void* __restrict__ src, int64_t n,
+                         const int32_t* __restrict__ base_encode,
+                         const int32_t* __restrict__ base_decode, int32_t* center_out,
+                         int32_t* shifted_encode, int32_t* shifted_decode) {
+  center_and_tables<kPrecomputed>(src, n, base_encode, base_decode, center_out, shifted_encode,
+                                  shifted_decode);
+}
+
+__global__ void __launch_bounds__(kTableThreads)
+center_batch_kernel(const lct_encode_job* __restrict__ jobs, const int32_t* __restrict__ base_encode,
+                    const int32_t* __restrict__ base_decode, int32_t* shifted_encode) {
+  const lct_encode_job& job = jobs[blockIdx.x];
+  center_and_tables<false>(job.src, job.logical_numel, base_encode, base_decode, job.center,
+                           shifted_encode + 256 * (int64_t)blockIdx.x, job.shifted_decode);
+}
+
 __global__ void __launch_bounds__(kTableThreads)
 shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __restrict__ base_decode,
                     const int32_t* __restrict__ center, int32_t* shifted_encode,
@@ -116,6 +135,13 @@ pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pai
     }
     pair_table[slot] = entry;
   }
+}
+
+int launch_center_batch(const lct_encode_job* jobs, int n_jobs, const int32_t* encode_table,
+                        const int32_t* decode_table, int32_t* shifted_encode, cudaStream_t stream) {
+  center_batch_kernel<<<n_jobs, kTableThreads, 0, stream>>>(jobs, encode_table, decode_table,
+                                                            shifted_encode);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace lct

@@ -37,6 +37,21 @@ class Operand(ctypes.Structure):
     ]
 
 
+class DecodeJob(ctypes.Structure):
+    """``struct lct_decode_job``."""
+
+    _fields_ = [("operand", Operand), ("out", _p), ("size", _i64), ("logical_numel", _i64),
+                ("first_block", _i64)]
+
+
+class EncodeJob(ctypes.Structure):
+    """``struct lct_encode_job``."""
+
+    _fields_ = [("src", _p), ("side", _p), ("encoded", _p), ("center", _p), ("shifted_decode", _p),
+                ("counts", _p), ("descriptor", _p), ("blocks_out", _p), ("size", _i64),
+                ("logical_numel", _i64), ("first_block", _i64)]
+
+
 _SIGNATURES = {
     "lct_build_pair_table": [_p, _i, _p, _p],
     "lct_center_and_tables": [_p, _i64, _i, _p, _p, _p, _p, _p, _p],
@@ -46,6 +61,8 @@ _SIGNATURES = {
     "lct_scan_allocate": [_p, _p, _p, _p, _i64, _i, _p],
     "lct_compact_tails": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _p],
     "lct_decode": [ctypes.POINTER(Operand), _p, _i64, _i64, _i, _i, _i, _i, _p],
+    "lct_decode_batch": [_p, _i, _i64, _i, _i, _i, _i, _p],
+    "lct_compress_batch": [_p, _i, _i64, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p],
     "lct_pointwise": [ctypes.POINTER(Operand), _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i64,
                       _i, _i, _i, _i, _p],
     "lct_dual_scale_add": [ctypes.POINTER(Operand), ctypes.POINTER(Operand), _p, _p, _p, _i,

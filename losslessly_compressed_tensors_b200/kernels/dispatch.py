@@ -21,7 +21,7 @@ import torch
 from .. import config
 from ..compression.huffman_tables import FIRST_BITS, get_distribution_tables
 from . import _lib
-from ._lib import Operand, Overflow
+from ._lib import DecodeJob, EncodeJob, Operand, Overflow
 from .backends import FallbackStorage
 
 OP_ADD, OP_MULTIPLY, OP_SCALAR_MUL_ADD = 0, 1, 2
@@ -279,6 +279,97 @@ def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements,
         auxiliary.data_ptr() if compressed_output else None, alpha.data_ptr(),
         int(compressed_output), n_elements, logical_numel, block_symbols, steps, fixed_words,
         rare_length)
+
+
+# ---------------------------------------------------------------------------
+# Many tensors per launch
+# ---------------------------------------------------------------------------
+
+def _to_device(records, device: torch.device) -> torch.Tensor:
+    """A ctypes array of job records as a device byte tensor."""
+    raw = torch.frombuffer(bytearray(bytes(records)), dtype=torch.uint8)
+    return raw.to(device, non_blocking=True)
+
+
+class CompressBatch:
+    """A prepared multi-tensor compression: the device job table and work buffers.  ``run`` may
+    be called any number of times (e.g. once per training step) as long as the tensors the jobs
+    point at stay alive and in place."""
+
+    def __init__(self, jobs: list[dict], encode_table, decode_table, buffer, *, block_symbols,
+                 lanes, steps, fixed_words):
+        self.device = _require_cuda(encode_table)
+        records = (EncodeJob * len(jobs))()
+        first = 0
+        for record, job in zip(records, jobs):
+            record.src = job["src"].data_ptr()
+            record.side = job["side"].data_ptr()
+            record.encoded = job["encoded"].data_ptr()
+            record.center = job["center"].data_ptr()
+            record.shifted_decode = job["decode_table"].data_ptr()
+            record.counts = job["counts"].data_ptr()
+            record.descriptor = job["descriptor"].data_ptr()
+            record.blocks_out = job["blocks"].data_ptr()
+            record.size = job["size"]
+            record.logical_numel = job["logical_numel"]
+            record.first_block = first
+            first += job["size"] // block_symbols
+        self.keep = (jobs, encode_table, decode_table, buffer)
+        self.table = _to_device(records, self.device)
+        self.extra_starts = torch.empty(first * lanes, dtype=torch.uint8, device=self.device)
+        self.summaries = torch.empty(4 * first, dtype=torch.int32, device=self.device)
+        self.shifted_encode = torch.empty(256 * len(jobs), dtype=torch.int32, device=self.device)
+        self.args = (
+            self.table.data_ptr(), len(jobs), first, encode_table.data_ptr(),
+            decode_table.data_ptr(), buffer._storage.data_ptr(), buffer.max_free_regions,
+            self.extra_starts.data_ptr(), self.summaries.data_ptr(),
+            self.shifted_encode.data_ptr(), block_symbols, steps, fixed_words)
+
+    def run(self) -> None:
+        _call("lct_compress_batch", self.device, *self.args)
+
+
+def compress_batch(jobs: list[dict], encode_table, decode_table, buffer, **geometry_kw):
+    """Compress many tensors of one codebook and geometry into ``buffer``'s arena with four
+    launches.  Each job is a dict of tensors: ``src`` (int16 bits, contiguous), ``side``,
+    ``encoded``, ``center``, ``decode_table``, ``counts``, ``descriptor``, ``blocks`` plus
+    ``size`` and ``logical_numel``.  Returns the prepared batch (re-runnable)."""
+    batch = CompressBatch(jobs, encode_table, decode_table, buffer, **geometry_kw)
+    batch.run()
+    return batch
+
+
+class DecodeBatch:
+    """A prepared multi-tensor decode (one launch per ``run``).  Each job is
+    ``(operand, output int16 tensor, size, logical_numel)``."""
+
+    def __init__(self, jobs: list[tuple], *, block_symbols, lanes, steps, fixed_words, rare_length):
+        self.device = _require_cuda(jobs[0][1])
+        records = (DecodeJob * len(jobs))()
+        first = 0
+        for record, (operand, output, size, logical_numel) in zip(records, jobs):
+            if output.data_ptr() % 16:
+                raise ValueError("batched decode needs 16-byte aligned outputs")
+            record.operand = operand
+            record.out = output.data_ptr()
+            record.size = size
+            record.logical_numel = logical_numel
+            record.first_block = first
+            first += size // block_symbols
+        self.keep = jobs
+        self.table = _to_device(records, self.device)
+        self.args = (self.table.data_ptr(), len(jobs), first, block_symbols, steps, fixed_words,
+                     rare_length)
+
+    def run(self) -> None:
+        _call("lct_decode_batch", self.device, *self.args)
+
+
+def decode_batch(jobs: list[tuple], **geometry_kw):
+    """Decode many compressed tensors of one geometry in one launch."""
+    batch = DecodeBatch(jobs, **geometry_kw)
+    batch.run()
+    return batch
 
 
 # ---------------------------------------------------------------------------

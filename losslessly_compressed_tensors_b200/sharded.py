@@ -68,6 +68,10 @@ class Plan:
     offsets: list[list[dict[str, tuple[int, int]]]] = field(default_factory=list)
     arena_offset: list[int] = field(default_factory=list)
     wire_bytes: int = 0
+    # Prepared launches, keyed by the addresses they were prepared for: a training loop that
+    # re-encodes the same parameters into the same wire buffer every step pays the Python cost
+    # of describing 150+ shards once.
+    prepared: dict = field(default_factory=dict, repr=False, compare=False)
 
     def shard_blocks(self, shard: Shard) -> int:
         block_symbols = geometry(self.distribution)[0]
@@ -185,15 +189,38 @@ def shard_source(tensors: list[torch.Tensor], shard: Shard) -> torch.Tensor:
     return tensor[shard.row_start:shard.row_stop]
 
 
+def _compressed_view(plan: Plan, wire: torch.Tensor, shard: Shard, slots, arena_payload,
+                     buffer=None) -> CompressedTensor:
+    """The ``CompressedTensor`` whose tensors are the wire slots of one shard."""
+    stream_geometry = geometry(plan.distribution)
+    counts = _slot(wire, slots["counts"], "counts")
+    return CompressedTensor(
+        _slot(wire, slots["encoded"], "encoded"),
+        plan.shard_blocks(shard) * stream_geometry[0],
+        _slot(wire, slots["side"], "side"),
+        fallback_blocks=_slot(wire, slots["blocks"], "blocks"),
+        fallback_buffer=arena_payload,
+        fallback_descriptor=_slot(wire, slots["descriptor"], "descriptor"),
+        buffer=buffer,
+        fallback_count=counts[:1], fallback_used=counts[1:2],
+        distribution=plan.distribution, center=_slot(wire, slots["center"], "center"),
+        decode_table=_slot(wire, slots["decode_table"], "decode_table"),
+        shape=shard.shape, layout=StorageLayout.COMPRESSED, stream_geometry=stream_geometry,
+    )
+
+
 def encode_rank(plan: Plan, rank: int, tensors: list[torch.Tensor],
-                wire: torch.Tensor | None = None):
+                wire: torch.Tensor | None = None, *, batched: bool = True):
     """Compress this rank's shards straight into its wire buffer.
 
     Returns ``(wire, compressed, arena)``: the uint8 buffer of ``plan.wire_bytes`` bytes, the
     ``CompressedTensor`` of every shard (their tensors are views of ``wire``) and the rank's
-    ``TensorBuffer``.  Nothing here synchronises the host.
+    ``TensorBuffer``.  ``batched`` encodes all shards with four launches in total instead of
+    four per shard; the bytes are the same.  Nothing here synchronises the host.
     """
-    from .operations import compress
+    from .codec.encode import encode
+    from .compression.huffman_tables import get_distribution_tables
+    from .kernels import dispatch
     from .tensor_buffer import TensorBuffer
 
     device = tensors[0].device if tensors else torch.device("cuda")
@@ -201,27 +228,62 @@ def encode_rank(plan: Plan, rank: int, tensors: list[torch.Tensor],
         wire = torch.zeros(plan.wire_bytes, dtype=torch.uint8, device=device)
     elif wire.numel() != plan.wire_bytes or wire.dtype != torch.uint8:
         raise ValueError("wire buffer has the wrong size or dtype")
+    key = ("encode", rank, batched, wire.data_ptr(), tuple(t.data_ptr() for t in tensors))
+    hit = plan.prepared.get(key)
+    if hit is not None and batched:
+        batch, compressed, arena, metadata_bytes = hit
+        arena._storage[:metadata_bytes].zero_()   # same state as a freshly built arena
+        arena.reset()
+        batch.run()
+        return wire, compressed, arena
     start = plan.arena_offset[rank]
     arena_bytes = TensorBuffer.storage_bytes(plan.arena_capacity, plan.max_free_regions)
     arena = TensorBuffer(plan.arena_capacity, max_free_regions=plan.max_free_regions,
                          storage=wire[start:start + arena_bytes])
-    compressed = []
-    for shard, slots in zip(plan.shards[rank], plan.offsets[rank]):
+    sources = []
+    for shard in plan.shards[rank]:
         source = shard_source(tensors, shard)
         if tuple(source.shape) != shard.shape:
             raise ValueError(f"{shard.name}: expected shape {shard.shape}, got {tuple(source.shape)}")
-        from .codec.encode import encode
+        if source.dtype != torch.bfloat16:
+            raise TypeError(f"{shard.name}: the codec compresses bfloat16 tensors")
+        sources.append(source.detach())
+    if not batched or not sources:
+        compressed = [encode(source, plan.distribution, arena, out=_Placement(wire, slots))
+                      for source, slots in zip(sources, plan.offsets[rank])]
+        return wire, compressed, arena
 
-        compressed.append(encode(source.detach(), plan.distribution, arena,
-                                 out=_Placement(wire, slots)))
+    block_symbols, lanes, steps, fixed_words = geometry(plan.distribution)
+    encode_table, decode_table, _ = get_distribution_tables(plan.distribution, device)
+    compressed, jobs = [], []
+    for shard, source, slots in zip(plan.shards[rank], sources, plan.offsets[rank]):
+        c = _compressed_view(plan, wire, shard, slots, arena.data, arena)
+        flat = source.contiguous().view(-1).view(torch.int16)
+        jobs.append(dict(src=flat, side=c.sign_mantissa, encoded=c.data, center=c.center,
+                         decode_table=c.decode_table, counts=c.fallback_count,
+                         descriptor=c.fallback_descriptor, blocks=c.fallback_blocks,
+                         size=c.size, logical_numel=flat.numel()))
+        compressed.append(c)
+    batch = dispatch.compress_batch(jobs, encode_table, decode_table, arena,
+                                    block_symbols=block_symbols, lanes=lanes, steps=steps,
+                                    fixed_words=fixed_words)
+    if all(job["src"].data_ptr() == shard_source(tensors, shard).data_ptr()
+           for job, shard in zip(jobs, plan.shards[rank])):   # no temporary copies involved
+        plan.prepared[key] = (batch, compressed, arena,
+                              TensorBuffer.storage_bytes(0, plan.max_free_regions))
     return wire, compressed, arena
 
 
-def all_gather_wire(wire: torch.Tensor, plan: Plan, group=None) -> torch.Tensor:
-    """The one collective of the path: every rank receives every rank's wire buffer."""
+def all_gather_wire(wire: torch.Tensor, plan: Plan, group=None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """The one collective of the path: every rank receives every rank's wire buffer.
+    ``out`` reuses a previous result buffer (and with it the prepared decode launch)."""
     import torch.distributed as dist
 
-    gathered = torch.empty(plan.world * plan.wire_bytes, dtype=torch.uint8, device=wire.device)
+    gathered = out if out is not None else torch.empty(
+        plan.world * plan.wire_bytes, dtype=torch.uint8, device=wire.device)
+    if gathered.numel() != plan.world * plan.wire_bytes:
+        raise ValueError("gathered buffer has the wrong size")
     if plan.world == 1:
         gathered.copy_(wire)
     else:
@@ -237,8 +299,6 @@ def views_of(plan: Plan, gathered: torch.Tensor) -> list[tuple[Shard, Compressed
 
     if gathered.numel() != plan.world * plan.wire_bytes:
         raise ValueError("gathered buffer has the wrong size")
-    stream_geometry = geometry(plan.distribution)
-    block_symbols = stream_geometry[0]
     metadata = TensorBuffer.storage_bytes(0, plan.max_free_regions)
     result = []
     for rank in range(plan.world):
@@ -246,35 +306,45 @@ def views_of(plan: Plan, gathered: torch.Tensor) -> list[tuple[Shard, Compressed
         arena_start = plan.arena_offset[rank] + metadata
         arena_payload = wire[arena_start:arena_start + plan.arena_capacity]
         for shard, slots in zip(plan.shards[rank], plan.offsets[rank]):
-            counts = _slot(wire, slots["counts"], "counts")
-            result.append((shard, CompressedTensor(
-                _slot(wire, slots["encoded"], "encoded"),
-                plan.shard_blocks(shard) * block_symbols,
-                _slot(wire, slots["side"], "side"),
-                fallback_blocks=_slot(wire, slots["blocks"], "blocks"),
-                fallback_buffer=arena_payload,
-                fallback_descriptor=_slot(wire, slots["descriptor"], "descriptor"),
-                fallback_count=counts[:1], fallback_used=counts[1:2],
-                distribution=plan.distribution, center=_slot(wire, slots["center"], "center"),
-                decode_table=_slot(wire, slots["decode_table"], "decode_table"),
-                shape=shard.shape, layout=StorageLayout.COMPRESSED,
-                stream_geometry=stream_geometry,
-            )))
+            result.append((shard, _compressed_view(plan, wire, shard, slots, arena_payload)))
     return result
 
 
-def decode_all(plan: Plan, gathered: torch.Tensor, shapes: list[tuple[int, ...]]):
-    """Decode every shard from the gathered bytes and reassemble the weight set."""
+def decode_all(plan: Plan, gathered: torch.Tensor, shapes: list[tuple[int, ...]], *,
+               batched: bool = True, outputs: list[torch.Tensor] | None = None):
+    """Decode every shard from the gathered bytes and reassemble the weight set.  ``batched``
+    decodes all shards with one launch, straight into their rows of the output tensors;
+    ``outputs`` reuses existing BF16 tensors of the given shapes."""
+    from .codec.decode import operand_of
+    from .compression.huffman_tables import get_distribution_tables
+    from .kernels import dispatch
     from .operations import decompress
 
-    outputs = [torch.empty(shape, dtype=torch.bfloat16, device=gathered.device) for shape in shapes]
+    if outputs is None:
+        outputs = [torch.empty(shape, dtype=torch.bfloat16, device=gathered.device)
+                   for shape in shapes]
+    key = ("decode", batched, gathered.data_ptr(), tuple(t.data_ptr() for t in outputs))
+    hit = plan.prepared.get(key)
+    if hit is not None:
+        hit.run()
+        return outputs
+    jobs, direct = [], True
     for shard, compressed in views_of(plan, gathered):
-        dense = decompress(compressed)
         target = outputs[shard.index]
-        if target.dim() == 0:
-            target.copy_(dense.reshape(()))
-        else:
-            target[shard.row_start:shard.row_stop].copy_(dense)
+        rows = target.reshape(()) if target.dim() == 0 else target[shard.row_start:shard.row_stop]
+        flat = rows.view(-1).view(torch.int16) if rows.dim() else rows.reshape(1).view(torch.int16)
+        if batched and flat.numel() and flat.data_ptr() % 16 == 0:
+            jobs.append((operand_of(compressed), flat, compressed.size, flat.numel()))
+        elif flat.numel():
+            direct = False
+            rows.copy_(decompress(compressed).reshape(rows.shape))
+    if jobs:
+        block_symbols, lanes, steps, fixed_words = geometry(plan.distribution)
+        _, _, rare_length = get_distribution_tables(plan.distribution, gathered.device)
+        batch = dispatch.decode_batch(jobs, block_symbols=block_symbols, lanes=lanes, steps=steps,
+                                      fixed_words=fixed_words, rare_length=rare_length)
+        if direct:
+            plan.prepared[key] = batch
     return outputs
 
 

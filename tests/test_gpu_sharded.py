@@ -30,15 +30,16 @@ def _weights():
     return out
 
 
+@pytest.mark.parametrize("batched", [True, False], ids=["batched", "per-shard"])
 @pytest.mark.parametrize("world,row_shard", [(1, None), (3, None), (3, 30000), (8, 50000)])
-def test_encode_gather_decode_round_trip(oracle, world, row_shard):
+def test_encode_gather_decode_round_trip(oracle, world, row_shard, batched):
     dist = Distribution(DistType.EMPIRICAL)
     host = _weights()
     tensors = [w.cuda() for w in host]
     plan = sharded.make_plan(SHAPES, world, dist, row_shard_elements=row_shard, arena_fraction=0.5)
     wires = []
     for rank in range(world):
-        wire, compressed, arena = sharded.encode_rank(plan, rank, tensors)
+        wire, compressed, arena = sharded.encode_rank(plan, rank, tensors, batched=batched)
         assert wire.numel() == plan.wire_bytes and len(compressed) == len(plan.shards[rank])
         verify_buffer(arena)
         # every shard equals the oracle's encoding of that shard, arena offsets included
@@ -49,12 +50,22 @@ def test_encode_gather_decode_round_trip(oracle, world, row_shard):
         wires.append(wire)
     gathered = torch.cat(wires)          # what all_gather_into_tensor leaves on every rank
     assert torch.equal(sharded.all_gather_wire(wires[0], plan), wires[0]) if world == 1 else True
-    restored = sharded.decode_all(plan, gathered, [s for _, s in SHAPES])
+    restored = sharded.decode_all(plan, gathered, [s for _, s in SHAPES], batched=batched)
     for want, got in zip(host, restored):
         assert got.shape == want.shape
         assert np.array_equal(bits_of(got), bits_of(want))
     shards = sum(len(r) for r in plan.shards)
     assert len(sharded.views_of(plan, gathered)) == shards
+
+
+def test_batched_and_per_shard_paths_write_the_same_wire():
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 2, dist, row_shard_elements=30000, arena_fraction=0.5)
+    for rank in range(2):
+        one, _, _ = sharded.encode_rank(plan, rank, tensors, batched=False)
+        many, _, _ = sharded.encode_rank(plan, rank, tensors, batched=True)
+        assert torch.equal(one, many)
 
 
 def test_wire_buffer_is_reusable():
@@ -65,5 +76,17 @@ def test_wire_buffer_is_reusable():
     first = wire.clone()
     wire2, _, _ = sharded.encode_rank(plan, 0, tensors, wire=wire)   # second step of a training loop
     assert wire2 is wire and torch.equal(wire, first)
+    assert any(k[0] == "encode" for k in plan.prepared)               # the launch was prepared once
+    # new values in the same tensors: the prepared launch must pick them up
+    tensors[0].mul_(2.0)
+    sharded.encode_rank(plan, 0, tensors, wire=wire)
+    gathered = sharded.all_gather_wire(wire, plan)
+    outputs = sharded.decode_all(plan, gathered, [s for _, s in SHAPES])
+    assert all(torch.equal(a, b) for a, b in zip(outputs, tensors))
+    tensors[3].add_(1.0)
+    sharded.encode_rank(plan, 0, tensors, wire=wire)
+    sharded.all_gather_wire(wire, plan, out=gathered)
+    again = sharded.decode_all(plan, gathered, [s for _, s in SHAPES], outputs=outputs)
+    assert again is outputs and all(torch.equal(a, b) for a, b in zip(outputs, tensors))
     with pytest.raises(ValueError):
         sharded.encode_rank(plan, 0, tensors, wire=torch.zeros(16, dtype=torch.uint8, device="cuda"))
