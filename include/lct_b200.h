@@ -244,6 +244,36 @@ int lct_dual_scale_add(const lct_operand *a, const lct_operand *b /* host pointe
                        int block_symbols, int steps, int fixed_words, int rare_length,
                        void *stream);
 
+/* Fused update of compressed state, compA <- compA (op) B, without the split
+ * intermediate the reference writes between its pointwise kernel and its
+ * encoder (LCT/codec/pointwise.py:263-278).  Two launches plus the usual
+ * center / scan / tail launches:
+ *   lct_update_sample   result exponent bytes at the (up to) 4096 positions the
+ *                       center estimate samples (common/tables.py:24-28) into
+ *                       samples[min(logical_numel, 4096)]; feed them to
+ *                       lct_center_and_tables(samples, count, precomputed=1, ...)
+ *                       to get the new center and shifted tables;
+ *   lct_update_fused    decode A, apply op against dense B, re-encode with
+ *                       shifted_encode: writes side_out[size], encoded_out,
+ *                       extra_starts and summaries exactly as lct_encode does,
+ *                       and for lanes that overflow their budget the raw result
+ *                       exponents (from the overflow step on) into
+ *                       spill[logical offset], uint8[size], which is then the
+ *                       `src` of lct_compact_tails(precomputed=1).
+ * Results are bit-identical to lct_pointwise(compressed_output=1) followed by
+ * lct_center_and_tables / lct_encode(precomputed=1). */
+int lct_update_sample(const lct_operand *a /* host pointer */, const void *other,
+                      const float *alpha, const float *beta, int op, int alpha_is_one,
+                      int beta_is_one, uint8_t *samples, int64_t size, int64_t logical_numel,
+                      int block_symbols, int steps, int fixed_words, int rare_length,
+                      void *stream);
+int lct_update_fused(const lct_operand *a /* host pointer */, const void *other,
+                     const float *alpha, const float *beta, int op, int alpha_is_one,
+                     int beta_is_one, const int32_t *shifted_encode, uint8_t *side_out,
+                     int32_t *encoded_out, uint8_t *extra_starts, int32_t *summaries,
+                     uint8_t *spill, int64_t size, int64_t logical_numel, int block_symbols,
+                     int steps, int fixed_words, int rare_length, void *stream);
+
 /* ---- shared overflow arena (TensorBuffer) ---------------------------------- */
 /* storage layout: int32 free_starts[R] | free_sizes[R] | free_count | lock |
  * generation | pad to 16 bytes | payload[capacity]  (LCT/tensor_buffer.py:58-82).

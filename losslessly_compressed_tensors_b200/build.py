@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIBRARY = os.path.join(HERE, "liblct_b200.so")
-SOURCES = ("capi.cu", "tables.cu", "arena.cu", "encode.cu", "decode.cu")
+SOURCES = ("capi.cu", "tables.cu", "arena.cu", "encode.cu", "decode.cu", "update.cu")
 
 
 def _nvcc() -> str:

@@ -40,6 +40,8 @@ def encode_components(
     center: torch.Tensor | None = None,
     logical_numel: int,
     out=None,
+    center_samples: torch.Tensor | None = None,
+    launch_encode=None,
 ) -> CompressedTensor:
     """Encode int16 BF16 bits, or (``precomputed``) uint8 exponent bytes in logical order
     whose side bytes already sit in ``sign_mantissa``.  ``size`` is the padded element count.
@@ -68,10 +70,18 @@ def encode_components(
     shifted_decode = kept("decode_table", decode_table.numel(), torch.int32)
     if center is None:
         center = kept("center", 1, torch.int32)
-        dispatch.estimate_and_shift_encoding_table(
-            source_values, center, logical_numel, encode_table, shifted_encode,
-            decode_table, shifted_decode, min(logical_numel, CENTER_SAMPLE_SIZE), precomputed,
-        )
+        if center_samples is None:
+            dispatch.estimate_and_shift_encoding_table(
+                source_values, center, logical_numel, encode_table, shifted_encode,
+                decode_table, shifted_decode, min(logical_numel, CENTER_SAMPLE_SIZE), precomputed,
+            )
+        else:
+            # One sample per position: the estimator then reads every given byte exactly once.
+            count = center_samples.numel()
+            dispatch.estimate_and_shift_encoding_table(
+                center_samples, center, count, encode_table, shifted_encode,
+                decode_table, shifted_decode, min(count, CENTER_SAMPLE_SIZE), True,
+            )
     else:
         dispatch.shift_encoding_table(encode_table, center, shifted_encode, decode_table,
                                       shifted_decode)
@@ -85,6 +95,8 @@ def encode_components(
         # Nothing to encode: an empty tensor keeps well-defined (zero) metadata.
         encoded.zero_()
         counts.zero_()
+    elif launch_encode is not None:
+        launch_encode(shifted_encode, encoded, extra_starts, summaries)
     else:
         dispatch.encode_kernel(
             source_values, sign_mantissa, encoded, shifted_encode, extra_starts, summaries,

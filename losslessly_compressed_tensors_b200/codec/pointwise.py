@@ -81,6 +81,44 @@ def _launch_pointwise_compressed_dense(data, other, operation, dense_output, *, 
     return output, auxiliary
 
 
+# The compressed-output forms of ``compA (op) B`` run as one fused launch (decode, operate,
+# re-encode) after a small pre-pass that samples the result's center.  Setting this to False
+# restores the reference's two-stage order (split intermediate, then the encoder); the results
+# are bit-identical either way.
+FUSED_UPDATE = True
+
+
+def _fused_update(data, other, operation, result_distribution, buffer, *, alpha, beta,
+                  alpha_is_one):
+    scaled = operation.name == "scalar_mul_add"
+    device = data.data.device
+    other = other.contiguous().view(-1)
+    if other.dtype != torch.bfloat16:
+        raise TypeError("the dense operand must be bfloat16")
+    alpha = _scalar(alpha, device) if scaled and not alpha_is_one else None
+    beta = _scalar(beta, device) if scaled else None
+    _, _, rare_length = get_distribution_tables(data.distribution, device)
+    block_symbols, lanes, steps, fixed_words = data.codec_geometry
+    operand = operand_of(data)
+    meta = dict(op=operation.code, alpha_is_one=not scaled or alpha_is_one,
+                beta_is_one=not scaled or beta is None, rare_length=rare_length,
+                logical_numel=data.logical_numel, block_symbols=block_symbols, lanes=lanes,
+                steps=steps, fixed_words=fixed_words)
+    samples = torch.empty(min(data.logical_numel, 4096), dtype=torch.uint8, device=device)
+    dispatch.update_sample(operand, other, samples, data.size, alpha, beta, **meta)
+    side_out = torch.empty(data.size, dtype=torch.uint8, device=device)
+    spill = torch.empty(data.size, dtype=torch.uint8, device=device)  # touched by overflow lanes only
+
+    def launch(shifted_encode, encoded, extra_starts, summaries):
+        dispatch.update_fused(operand, other, shifted_encode, side_out, encoded, extra_starts,
+                              summaries, spill, data.size, alpha, beta, **meta)
+
+    return compress_components(
+        spill, side_out, data.size, result_distribution, buffer, data.shape, precomputed=True,
+        logical_numel=data.logical_numel, center_samples=samples, launch_encode=launch,
+    )
+
+
 def _launch_scalar_mul_add_compressed_compressed(data, other, alpha, dense_output):
     device = data.data.device
     _, _, rare_a = get_distribution_tables(data.distribution, device)
@@ -165,6 +203,9 @@ def pointwise_compressed_dense(
         result = _raw_result(data, other, operation, alpha, beta, alpha_is_one)
         return result if dense_output else compress_dense(result, result_distribution, buffer)
 
+    if not dense_output and FUSED_UPDATE and data.logical_numel:
+        return _fused_update(data, other, operation, result_distribution, buffer, alpha=alpha,
+                             beta=beta, alpha_is_one=alpha_is_one)
     values, auxiliary = _launch_pointwise_compressed_dense(
         data, other, operation, dense_output, alpha=alpha, beta=beta, alpha_is_one=alpha_is_one)
     if dense_output:

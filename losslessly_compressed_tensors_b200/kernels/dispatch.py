@@ -268,6 +268,35 @@ def pointwise_dense(operand: Operand, other, output, auxiliary, n_elements, alph
         logical_numel, block_symbols, steps, fixed_words, rare_length)
 
 
+def update_sample(operand: Operand, other, samples, n_elements, alpha, beta, *, op, alpha_is_one,
+                  beta_is_one, rare_length, logical_numel, block_symbols, lanes, steps,
+                  fixed_words):
+    """Exponent bytes of ``compA (op) other`` at the positions the center estimate samples."""
+    device = _require_cuda(samples)
+    _call(
+        "lct_update_sample", device,
+        ctypes.byref(operand), other.data_ptr(),
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        op, int(alpha_is_one), int(beta_is_one), samples.data_ptr(), n_elements, logical_numel,
+        block_symbols, steps, fixed_words, rare_length)
+
+
+def update_fused(operand: Operand, other, shifted_encode, side_out, encoded_out, extra_starts,
+                 summaries, spill, n_elements, alpha, beta, *, op, alpha_is_one, beta_is_one,
+                 rare_length, logical_numel, block_symbols, lanes, steps, fixed_words):
+    """Decode, apply ``op`` against dense ``other`` and re-encode in one launch."""
+    device = _require_cuda(side_out)
+    _call(
+        "lct_update_fused", device,
+        ctypes.byref(operand), other.data_ptr(),
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        op, int(alpha_is_one), int(beta_is_one), shifted_encode.data_ptr(), side_out.data_ptr(),
+        encoded_out.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(), spill.data_ptr(),
+        n_elements, logical_numel, block_symbols, steps, fixed_words, rare_length)
+
+
 def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements, *,
                    compressed_output, rare_length, logical_numel, block_symbols, lanes, steps,
                    fixed_words):

@@ -74,7 +74,11 @@ def _oracle_op(oracle, a_want, other_bits, spec, dense):
 @pytest.mark.parametrize("opname,spec", OPS, ids=[o[0] for o in OPS])
 @pytest.mark.parametrize("name,n,kind,dist", INPUTS, ids=[i[0] for i in INPUTS])
 @pytest.mark.parametrize("buffered", [False, True], ids=["private", "arena"])
-def test_compressed_dense_ops(oracle, opname, spec, name, n, kind, dist, buffered):
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "two-stage"])
+def test_compressed_dense_ops(oracle, monkeypatch, opname, spec, name, n, kind, dist, buffered, fused):
+    from losslessly_compressed_tensors_b200.codec import pointwise as pointwise_module
+
+    monkeypatch.setattr(pointwise_module, "FUSED_UPDATE", fused)
     bits = synth_bf16(n, 31, kind, -3 if kind == "outliers" else 0)
     other_bits = synth_bf16(n, 32, "normal", -1)
     buffer = TensorBuffer(4 << 20) if buffered else None
