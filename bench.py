@@ -44,9 +44,11 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 L2_FLUSH_BYTES = 512 << 20
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None until a capture of that kernel has been taken.
-NCU_TRAFFIC_BYTES = {"lct_encode": None, "lct_decode": None}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
+# summarised in profiles/encode_decode_config2.md.  Reads equal the algorithmic reads; part of the
+# written bytes is still in the 126 MB write-back L2 when the kernel ends, so the sum is below the
+# algorithmic 227.6 MB.
+NCU_TRAFFIC_BYTES = {"lct_encode": 184_723_712, "lct_decode": 174_332_416}
 
 
 def make_workload(seed: int) -> torch.Tensor:
@@ -246,6 +248,59 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
     }
 
 
+def update_leg(steps: int = 10, warmup: int = 3) -> dict:
+    """BASELINE configuration 4: momentum tensors of 4096 x 4096 BF16 ~ N(0, 1e-3), GAUSSIAN /
+    MEDIUM layout, shared arena; step = m <- 0.95 m + g on the compressed state (decode, fma,
+    re-encode in one launch), fresh g every step.  Timed per tensor-step with CUDA events."""
+    from losslessly_compressed_tensors_b200.LCTensor import LCTTensor
+    from losslessly_compressed_tensors_b200.codec import pointwise as pointwise_module
+    from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType, NoiseLevel
+    from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
+
+    dist_cfg = Distribution(DistType.GAUSSIAN, noise_level=NoiseLevel.MEDIUM)
+    buffer = TensorBuffer(64 << 20)
+    n_tensors, shape = 12, (4096, 4096)
+    gen = torch.Generator(device="cuda").manual_seed(10)
+    states = [LCTTensor((torch.randn(shape, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16),
+                        buffer, dist_cfg) for _ in range(n_tensors)]
+    grads = [(torch.randn(shape, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
+             for _ in range(4)]
+    alpha = torch.tensor([0.95], dtype=torch.float32, device="cuda")
+    c = states[0].x
+    per_tensor = 2 * (c.sign_mantissa.numel() + (c.data.numel() - 4) * 4) + 2 * c.logical_numel
+    out = {}
+    for label, fused in (("fused", True), ("two_stage", False)):
+        pointwise_module.FUSED_UPDATE = fused
+        times = []
+        for it in range(warmup + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for k, state in enumerate(states):
+                state.mul_add_(alpha, grads[(it + k) % len(grads)])
+            b.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(a.elapsed_time(b) / n_tensors)
+        out[label + "_ms_per_tensor_step"] = statistics.mean(times)
+        out[label + "_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
+    pointwise_module.FUSED_UPDATE = True
+    # the compressed state still decodes to what the dense recurrence gives
+    check = LCTTensor(torch.zeros(shape, dtype=torch.bfloat16, device="cuda"), buffer, dist_cfg)
+    dense = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    for g in grads:
+        check.mul_add_(alpha, g)
+        dense = torch.addcmul(g.float(), dense.float(), alpha).to(torch.bfloat16)
+    out["bit_exact_vs_dense_fma"] = bool(torch.equal(check.decompress().view(torch.int16),
+                                                     dense.view(torch.int16)))
+    for state in states + [check]:
+        state.free()
+    verify_buffer(buffer)
+    out["workload"] = ("config4: 12 x 4096x4096 BF16 momentum, GAUSSIAN/MEDIUM, m = 0.95 m + g; "
+                       "wall of the whole update incl. host launches")
+    out["algorithmic_bytes_per_tensor_step"] = per_tensor
+    return out
+
+
 def run_ours(args, rank: int, world: int, local: int):
     from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
     from losslessly_compressed_tensors_b200.kernels import dispatch
@@ -299,7 +354,6 @@ def run_ours(args, rank: int, world: int, local: int):
             one_step(spans)
         barrier(world)
         wall = time.perf_counter() - wall0
-    clocks = sampler.finish() if sampler else None
     enc_ms = [a.elapsed_time(b) for a, b, _, _ in spans]
     dec_ms = [c_.elapsed_time(d) for _, _, c_, d in spans]
     step_ms = (sum(enc_ms) + sum(dec_ms)) / args.steps
@@ -308,34 +362,64 @@ def run_ours(args, rank: int, world: int, local: int):
     launches = trace.count
     kernel_ms = {name: statistics.mean(trace.milliseconds(name)) for name in trace.timed}
 
-    # End to end: host buffers in, host buffers out, copies inside the timed region.
-    host_out = torch.empty_like(host_x).pin_memory()
-    dev_in = torch.empty_like(x)
+    # End to end: host buffers in, host buffers out, copies inside the timed region.  Every step
+    # copies its input from pinned host memory and its decoded result back to pinned host memory;
+    # the three stages of consecutive steps overlap on three streams (two copy engines and the
+    # SMs), with two sets of buffers, as a streaming user of the codec would run it.
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    host_out = [torch.empty_like(host_x).pin_memory() for _ in range(2)]
+    dev_in = [torch.empty_like(x) for _ in range(2)]
+    dev_out = [None, None]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_ready = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    for k in range(2):
+        in_free[k].record(main)
+        out_done[k].record(s_out)
 
-    def e2e_step():
-        dev_in.copy_(host_x, non_blocking=True)
-        c = compress(dev_in, dist_cfg, buffer)
-        y = decompress(c)
-        host_out.copy_(y, non_blocking=True)
+    def e2e_step(i):
+        k = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[k])               # the step two back has consumed dev_in[k]
+            dev_in[k].copy_(host_x, non_blocking=True)
+            in_ready[k].record(s_in)
+        main.wait_event(in_ready[k])
+        main.wait_event(out_done[k])                  # dev_out[k] of the step two back is on the host
+        c = compress(dev_in[k], dist_cfg, buffer)
+        in_free[k].record(main)
+        dev_out[k] = decompress(c)
         c.free()
+        out_ready[k].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(out_ready[k])
+            host_out[k].copy_(dev_out[k], non_blocking=True)
+            dev_out[k].record_stream(s_out)
+            out_done[k].record(s_out)
 
-    for _ in range(min(args.warmup, 3)):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
     barrier(world)
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(4, min(args.steps, 20))
     s, t = event(), event()
-    s.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    t.record()
+    s.record(main)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    main.wait_event(out_done[0])
+    main.wait_event(out_done[1])
+    t.record(main)
     barrier(world)
     e2e_ms = max_over_ranks(s.elapsed_time(t) / e2e_steps, world)
-    assert torch.equal(host_out.view(torch.int16), host_x.view(torch.int16))
+    for k in range(2):
+        assert torch.equal(host_out[k].view(torch.int16), host_x.view(torch.int16))
     verify_buffer(buffer)
     e2e_value = world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9
+    clocks = sampler.finish() if sampler else None   # sampled across both timed regions
 
-    del host_out, dev_in, x, flush
+    del host_out, dev_in, dev_out, x, flush
     sharded = sharded_leg(rank, world) if not args.no_sharded else None
+    update = update_leg() if (rank == 0 and not args.no_sharded) else None
     if rank != 0:
         return
     peak, peak_kind = peak_hbm_gbs()
@@ -367,7 +451,7 @@ def run_ours(args, rank: int, world: int, local: int):
         "roofline": roofline, "kernels": kernels,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
-        "gpu_launches": launches, "clocks": clocks, "sharded": sharded,
+        "gpu_launches": launches, "clocks": clocks, "sharded": sharded, "update": update,
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)
