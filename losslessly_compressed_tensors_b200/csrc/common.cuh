@@ -32,6 +32,7 @@ constexpr int kTileRows = 2 * kTilePairs;
 constexpr int kPairBits = 12;           // stream bits indexing the two-symbol table
 constexpr int kPairEntries = 1 << kPairBits;
 constexpr int kFirstMask = 1023;        // the codebook's first-level table covers 10 bits
+constexpr int kSampleCount = 4096;     // positions the exponent center is estimated from
 
 // Two-symbol table entry: byte0 = first symbol, byte1 = second symbol,
 // byte2 = bits consumed by the symbols present, byte3 = length of the first
@@ -96,6 +97,17 @@ __device__ __forceinline__ uint32_t index_to_exponent_byte(uint32_t index, int c
   const uint32_t zero_delta = (uint32_t)(-127 - center) & 255u;
   if (index == 0) return 0;
   return (index - (index <= zero_delta ? 1u : 0u) + (uint32_t)(center + 127)) & 255u;
+}
+
+// Position of center sample `idx` in a tensor of n elements: one jittered
+// position per equal slice, floor(idx*n/count) + floor(hash * slice / 2^32)
+// with count = min(n, 4096).  For n < 4096 every slice is one element, and
+// for n >= 4096 the divisor is 2^12, so no division is needed.
+__device__ __forceinline__ int64_t sample_position(int64_t idx, int64_t n) {
+  if (n < kSampleCount) return idx;
+  const int64_t start = (idx * n) >> 12, end = ((idx + 1) * n) >> 12;
+  const uint32_t hashed = (uint32_t)idx * 0x9E3779B9u;
+  return start + (int64_t)(((uint64_t)hashed * (uint64_t)(end - start)) >> 32);
 }
 
 // Number of leading steps of `lane` in block `block` that hold real elements.

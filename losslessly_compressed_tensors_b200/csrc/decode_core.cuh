@@ -61,6 +61,11 @@ __device__ __forceinline__ void cp_async_16(void* shared_dst, const void* global
   const uint32_t dst = (uint32_t)__cvta_generic_to_shared(shared_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(global_src) : "memory");
 }
+__device__ __forceinline__ void cp_async_4(void* shared_dst, const void* global_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(shared_dst)),
+               "l"(global_src));
+}
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }

@@ -21,6 +21,11 @@
 
 namespace lct {
 
+// Resident CTAs per SM the encoder is compiled for (register cap = 65536 / 256 / this).
+#ifndef LCT_ENCODE_MIN_CTAS
+#define LCT_ENCODE_MIN_CTAS 4
+#endif
+
 struct EncodeShape {
   int64_t size;
   int64_t logical_numel;
@@ -183,10 +188,10 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
     // ---- lane phase ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, lane32, step0, valid,
+        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, kLanes, lane32, step0, valid,
                                        budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, lane32, step0, valid,
+        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, kLanes, lane32, step0, valid,
                                       budget_bits, pos, lo, extra_start);
     }
     __syncwarp();
@@ -220,7 +225,7 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
 }
 
 template <bool kPrecomputed>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
 encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
               uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
               uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
@@ -248,7 +253,7 @@ __device__ __forceinline__ int find_encode_job(const lct_encode_job* jobs, int n
   return lo;
 }
 
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
 encode_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs,
                     const int32_t* __restrict__ shifted_encode, uint8_t* __restrict__ extra_starts,
                     int32_t* __restrict__ summaries, EncodeShape common) {

@@ -9,7 +9,8 @@ namespace lct {
 // Lane phase of one tile.  Returns false once the lane has overflowed.
 template <bool kCheckValid>
 __device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8_t* tile_bytes,
-                                                 uint32_t* payload_column, int lane32,
+                                                 uint32_t* payload_column, int64_t word_stride,
+                                                 int lane32,
                                                  int step0, int valid, int budget_bits, int& pos,
                                                  uint32_t& lo, int& extra_start) {
 #pragma unroll
@@ -29,12 +30,12 @@ __device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8
     if (next > budget_bits) {
       // First pair that does not fit: freeze the current word and stop.
       extra_start = step0 + 2 * p;
-      if (pos < budget_bits) payload_column[(pos >> 5) * kLanes] = lo;
+      if (pos < budget_bits) payload_column[(pos >> 5) * word_stride] = lo;
       return false;
     }
     lo |= code << shift;
     if (shift + length >= 32) {
-      payload_column[(pos >> 5) * kLanes] = lo;
+      payload_column[(pos >> 5) * word_stride] = lo;
       lo = __funnelshift_l(code, 0u, shift);  // the bits that did not fit; 0 when shift == 0
     }
     pos = next;

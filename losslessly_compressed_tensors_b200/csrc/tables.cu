@@ -6,8 +6,29 @@
 
 namespace lct {
 
-constexpr int kCenterSamples = 4096;
 constexpr int kTableThreads = 1024;
+
+static_assert(kTableThreads == kFirstMask + 1, "one first-level decode entry per thread");
+static_assert(kSampleCount == 4 * kTableThreads, "four center samples per thread");
+
+__device__ __forceinline__ int32_t shifted_encode_entry(const int32_t* base_encode, int raw,
+                                                        int center) {
+  const int zero_delta = (-127 - center) & 255;
+  const int exponent = raw - 127;
+  const int delta = (exponent - center) & 255;
+  const int index = exponent == -127 ? 0 : delta + (delta < zero_delta ? 1 : 0);
+  return base_encode[index];
+}
+
+__device__ __forceinline__ int32_t shifted_decode_entry(int32_t packed, int center) {
+  const int zero_delta = (-127 - center) & 255;
+  const int length = packed & 255;
+  const int symbol = (packed >> 8) & 255;
+  int delta = symbol == 0 ? 0 : symbol - (symbol <= zero_delta ? 1 : 0);
+  if (delta >= 128) delta -= 256;
+  const int exponent = symbol == 0 ? -127 : delta + center;
+  return length == 0 ? 0 : (int32_t)((uint32_t)length | ((uint32_t)exponent << 8));
+}
 
 // Shifted tables for a center: encode indexed by raw exponent byte, decode
 // storing the unbiased exponent above the code length.
@@ -15,31 +36,22 @@ __device__ __forceinline__ void write_shifted_tables(const int32_t* __restrict__
                                                      const int32_t* __restrict__ base_decode,
                                                      int center, int32_t* shifted_encode,
                                                      int32_t* shifted_decode) {
-  const int zero_delta = (-127 - center) & 255;
   if (shifted_encode != nullptr) {
-    for (int raw = threadIdx.x; raw < 256; raw += blockDim.x) {
-      const int exponent = raw - 127;
-      const int delta = (exponent - center) & 255;
-      const int index = exponent == -127 ? 0 : delta + (delta < zero_delta ? 1 : 0);
-      shifted_encode[raw] = base_encode[index];
-    }
+    for (int raw = threadIdx.x; raw < 256; raw += blockDim.x)
+      shifted_encode[raw] = shifted_encode_entry(base_encode, raw, center);
   }
   if (shifted_decode != nullptr) {
-    for (int i = threadIdx.x; i <= kFirstMask; i += blockDim.x) {
-      const int32_t packed = base_decode[i];
-      const int length = packed & 255;
-      const int symbol = (packed >> 8) & 255;
-      int delta = symbol == 0 ? 0 : symbol - (symbol <= zero_delta ? 1 : 0);
-      if (delta >= 128) delta -= 256;
-      const int exponent = symbol == 0 ? -127 : delta + center;
-      shifted_decode[i] = length == 0 ? 0 : (int32_t)((uint32_t)length | ((uint32_t)exponent << 8));
-    }
+    for (int i = threadIdx.x; i <= kFirstMask; i += blockDim.x)
+      shifted_decode[i] = shifted_decode_entry(base_decode[i], center);
   }
 }
 
-// One CTA.  Every thread takes up to four of the <= 4096 jittered sample
-// positions; the mean exponent of the samples with exponent >= -120, rounded
-// half away from zero, is the center.
+// One CTA of 1024 threads.  Every thread takes four of the <= 4096 jittered
+// sample positions; the mean exponent of the samples with exponent >= -120,
+// rounded half away from zero, is the center.  The kernel is one chain of
+// memory latencies, so everything independent is issued up front: the four
+// sample loads together, and the base-table rows the shifted tables are made
+// from before the samples come back.
 template <bool kPrecomputed>
 __device__ __forceinline__ void center_and_tables(const void* __restrict__ src, int64_t n,
                                                   const int32_t* __restrict__ base_encode,
@@ -47,41 +59,56 @@ __device__ __forceinline__ void center_and_tables(const void* __restrict__ src, 
                                                   int32_t* center_out, int32_t* shifted_encode,
                                                   int32_t* shifted_decode) {
   __shared__ int s_sum[32], s_kept[32], s_center;
-  const int64_t samples = n < kCenterSamples ? n : kCenterSamples;
-  int sum = 0, kept = 0;
-  for (int64_t idx = threadIdx.x; idx < samples; idx += blockDim.x) {
-    const uint32_t hashed = (uint32_t)idx * 0x9E3779B9u;
-    const int64_t start = idx * n / samples;
-    const int64_t end = (idx + 1) * n / samples;
-    const uint64_t jitter = ((uint64_t)hashed * (uint64_t)(end - start)) >> 32;
-    const int64_t pos = start + (int64_t)jitter;
-    int exponent;
-    if (kPrecomputed) {
-      exponent = (int)static_cast<const uint8_t*>(src)[pos] - 127;
-    } else {
-      exponent = (((int)static_cast<const uint16_t*>(src)[pos] >> 7) & 0xFF) - 127;
+  __shared__ int32_t s_encode[256];
+  const int tid = threadIdx.x;
+  const int64_t samples = n < kSampleCount ? n : kSampleCount;
+  int raw[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t idx = tid + k * kTableThreads;
+    raw[k] = -1;
+    if (idx < samples) {
+      const int64_t pos = sample_position(idx, n);
+      raw[k] = kPrecomputed ? (int)static_cast<const uint8_t*>(src)[pos]
+                            : ((int)static_cast<const uint16_t*>(src)[pos] >> 7) & 0xFF;
     }
-    if (exponent >= -120) { sum += exponent; ++kept; }
+  }
+  const int32_t decode_row = shifted_decode != nullptr ? base_decode[tid] : 0;
+  if (shifted_encode != nullptr && tid < 256) s_encode[tid] = base_encode[tid];
+  int sum = 0, kept = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int exponent = raw[k] - 127;
+    if (raw[k] >= 0 && exponent >= -120) { sum += exponent; ++kept; }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
     sum += __shfl_down_sync(0xFFFFFFFFu, sum, d);
     kept += __shfl_down_sync(0xFFFFFFFFu, kept, d);
   }
-  if ((threadIdx.x & 31) == 0) { s_sum[threadIdx.x >> 5] = sum; s_kept[threadIdx.x >> 5] = kept; }
+  if ((tid & 31) == 0) { s_sum[tid >> 5] = sum; s_kept[tid >> 5] = kept; }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int total = 0, count = 0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { total += s_sum[w]; count += s_kept[w]; }
-    const int safe = count > 0 ? count : 1;
-    int center = total >= 0 ? (total + safe / 2) / safe : -((-total + safe / 2) / safe);
-    if (count == 0) center = 0;
-    center = min(max(center, -128), 127);
-    s_center = center;
-    *center_out = center;
+  if (tid < 32) {
+    int total = s_sum[tid], count = s_kept[tid];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      total += __shfl_down_sync(0xFFFFFFFFu, total, d);
+      count += __shfl_down_sync(0xFFFFFFFFu, count, d);
+    }
+    if (tid == 0) {
+      const int safe = count > 0 ? count : 1;
+      int center = total >= 0 ? (total + safe / 2) / safe : -((-total + safe / 2) / safe);
+      if (count == 0) center = 0;
+      center = min(max(center, -128), 127);
+      s_center = center;
+      *center_out = center;
+    }
   }
   __syncthreads();
-  write_shifted_tables(base_encode, base_decode, s_center, shifted_encode, shifted_decode);
+  const int center = s_center;
+  if (shifted_encode != nullptr && tid < 256)
+    shifted_encode[tid] = shifted_encode_entry(s_encode, tid, center);
+  if (shifted_decode != nullptr) shifted_decode[tid] = shifted_decode_entry(decode_row, center);
 }
 
 template <bool kPrecomputed>

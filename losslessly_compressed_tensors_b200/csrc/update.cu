@@ -23,124 +23,120 @@
 
 namespace lct {
 
-constexpr int kSampleCount = 4096;
+// The sample kernel walks bit streams with the codebook's two-symbol table read
+// straight from global memory (16 KB, L1-resident after the first touches) in
+// table-index space: only code lengths matter until the sampled symbol itself,
+// which alone is mapped to an exponent byte.  Shared memory holds one payload
+// column per thread: fixed_words + 3 rows of 256 words (the window refill may
+// read one row past the two zero rows when a stream uses its whole budget; the
+// refill pointer is clamped to that last row on every pair).
 
-// Shared memory of the sample kernel: just the center-specific table.
-struct __align__(16) SampleShared {
-  uint32_t table[kPairEntries];
-  uint8_t index_to_byte[256];
-};
-
-// One symbol at the head of a 64-bit window read straight from global memory.
-struct GlobalReader {
-  const uint32_t* next_ptr;
-  int64_t stride;
-  uint32_t lo, hi;
-  int shift, word, fixed_words;
-
-  __device__ __forceinline__ void open(const uint32_t* encoded, int64_t streams, int64_t stream,
-                                       int fw) {
-    const uint32_t* p = encoded + stream;
-    stride = streams;
-    fixed_words = fw;
-    lo = p[0];
-    hi = p[streams];
-    next_ptr = p + 2 * streams;
-    shift = 0;
-    word = 0;
+// One symbol of table-index space from an entry and the bits it was looked up with.
+__device__ __forceinline__ uint32_t index_of(uint32_t entry, uint32_t bits, int rare_length,
+                                             int* length) {
+  if (entry & kEscape) {
+    *length = rare_length + 8;
+    return (bits >> rare_length) & 255u;
   }
-  __device__ __forceinline__ uint32_t peek() const { return __funnelshift_r(lo, hi, shift); }
-  __device__ __forceinline__ void advance(int bits) {  // bits <= 16
-    shift += bits;
-    if (shift >= 32) {
-      shift -= 32;
-      lo = hi;
-      ++word;
-      hi = (word + 1 < fixed_words) ? *next_ptr : 0u;
-      next_ptr += stride;
+  *length = (int)((entry >> 24) & 15u);
+  return entry & 255u;
+}
+
+// Raw-tail exponent byte of A at (block, step, lane), or -1 when that step is in the bit stream.
+__device__ __forceinline__ int tail_exponent_at(const OperandView& a, const Shape& g, int64_t block,
+                                                int step, int lane) {
+  if (a.mode == 0 || (a.mode == 2 && a.descriptor[2] != 0)) return -1;
+  const int count = a.blocks[block];
+  if (count <= 0) return -1;
+  const int64_t region = a.mode == 2 ? a.descriptor[0] : 0;
+  const int64_t total = a.mode == 2 ? *a.count : 0;
+  const int64_t first = a.blocks[g.n_blocks + block];
+  int64_t offset = a.blocks[2 * g.n_blocks + block];
+  for (int e = 0; e < count; ++e) {
+    const int entry_lane = a.lanes[region + first + e];
+    const int entry_start = a.starts[region + total + first + e];
+    if (entry_lane == lane) {
+      if (step < entry_start) return -1;
+      return (int)(((uint32_t)tail_origin(a)[offset + step - entry_start] + 127u) & 255u);
     }
+    offset += g.steps - entry_start;
   }
-};
+  return -1;
+}
 
-// Exponent byte of A at storage position (block, step, lane).
-__device__ __forceinline__ uint32_t exponent_at(const OperandView& a, const Shape& g,
-                                                const SampleShared& sh, int64_t block, int step,
-                                                int lane) {
-  if (a.mode != 0 && (a.mode != 2 || a.descriptor[2] == 0)) {
-    const int count = a.blocks[block];
-    if (count > 0) {
-      const int64_t region = a.mode == 2 ? a.descriptor[0] : 0;
-      const int64_t total = a.mode == 2 ? *a.count : 0;
-      const int64_t first = a.blocks[g.n_blocks + block];
-      int64_t offset = a.blocks[2 * g.n_blocks + block];
-      for (int e = 0; e < count; ++e) {
-        const int entry_lane = a.lanes[region + first + e];
-        const int entry_start = a.starts[region + total + first + e];
-        if (entry_lane == lane) {
-          if (step >= entry_start)
-            return ((uint32_t)tail_origin(a)[offset + step - entry_start] + 127u) & 255u;
-          break;
-        }
-        offset += g.steps - entry_start;
-      }
-    }
-  }
-  GlobalReader r;
-  r.open(a.encoded, g.streams, block * kLanes + lane, g.fixed_words);
-  uint32_t exponent = 0;
-  for (int s = 0; s <= step; ++s) {
-    const uint32_t bits = r.peek();
-    const uint32_t entry = sh.table[table_slot(bits)];
-    int length;
-    if (entry & kEscape) {
-      exponent = sh.index_to_byte[(bits >> g.rare_length) & 255u];
-      length = g.rare_length + 8;
+// Table index of the symbol at `step` of the stream staged in `column`.
+__device__ __forceinline__ uint32_t walk_to(const OperandView& a, const Shape& g,
+                                            const uint32_t* column, int step) {
+  const uint32_t* last_row = column + (g.fixed_words + 2) * kLanes;
+  BitReader r;
+  r.open(column);
+  uint32_t first_index = 0, second_index = 0;
+  for (int p = 0; p <= (step >> 1); ++p) {
+    if (r.next_row > last_row) r.next_row = last_row;
+    const uint32_t bits = r.peek0();
+    const uint32_t entry = __ldg(a.pair_table + table_slot(bits));
+    int consumed;
+    if ((int32_t)entry < 0) {
+      int l0, l1;
+      first_index = index_of(entry, bits, g.rare_length, &l0);
+      const uint32_t bits1 = r.peek(l0);
+      second_index = index_of(__ldg(a.pair_table + table_slot(bits1)), bits1, g.rare_length, &l1);
+      consumed = l0 + l1;
     } else {
-      exponent = entry & 255u;
-      length = (int)((entry >> 24) & 15u);
+      first_index = entry & 255u;
+      second_index = (entry >> 8) & 255u;
+      consumed = (int)((entry >> 16) & 255u);
     }
-    r.advance(length);
+    r.advance(consumed);
   }
-  return exponent;
+  return (step & 1) ? second_index : first_index;
 }
 
 // Result exponent bytes at the center-sample positions of the result tensor.
+// The kernel is a chain of memory latencies in front of a serial bit-stream
+// walk, so everything independent starts first: the lane's payload words go to
+// its shared column asynchronously while the overflow map is consulted.
 __global__ void __launch_bounds__(kThreads)
 update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, OpSpec spec,
                      uint8_t* __restrict__ samples) {
-  __shared__ SampleShared sh;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x;
-  const int center = *a.center;
-  sh.index_to_byte[tid] = (uint8_t)index_to_exponent_byte((uint32_t)tid, center);
-  __syncthreads();
-  for (int i = tid; i < kPairEntries; i += kThreads) {
-    const uint32_t e = a.pair_table[i];
-    sh.table[i] = (e & 0xFFFF0000u) | sh.index_to_byte[e & 255u] |
-                  ((uint32_t)sh.index_to_byte[(e >> 8) & 255u] << 8);
-  }
-  __syncthreads();
+  uint32_t* column = reinterpret_cast<uint32_t*>(smem_raw) + tid;
   const int64_t n = g.logical_numel;
   const int64_t count = n < kSampleCount ? n : kSampleCount;
   const int64_t idx = (int64_t)blockIdx.x * kThreads + tid;
   if (idx >= count) return;
   // Same jittered position as the center estimate (one per equal slice of the tensor).
-  const uint32_t hashed = (uint32_t)idx * 0x9E3779B9u;
-  const int64_t start = idx * n / count, end = (idx + 1) * n / count;
-  const int64_t pos = start + (int64_t)(((uint64_t)hashed * (uint64_t)(end - start)) >> 32);
+  const int64_t pos = sample_position(idx, n);
   const int64_t row = pos >> 8;
   const int lane = (int)(pos & 255) ^ (int)(row & 254);
   const int64_t block = row / g.steps;
   const int step = (int)(row - block * g.steps);
-  const uint32_t exponent = exponent_at(a, g, sh, block, step, lane);
+  // The 16 KB two-symbol table is read from global memory during the walk: pull
+  // its 128 lines into this SM's L1 now, one per thread, instead of missing on them
+  // one at a time inside the serial loop.
+  if (tid < kPairEntries / 32)
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(a.pair_table + tid * 32));
+  const uint32_t* words = a.encoded + block * kLanes + lane;
+  for (int w = 0; w < g.fixed_words; ++w)
+    cp_async_4(column + w * kLanes, words + (int64_t)w * g.streams);
+  column[g.fixed_words * kLanes] = 0u;
+  column[(g.fixed_words + 1) * kLanes] = 0u;
+  column[(g.fixed_words + 2) * kLanes] = 0u;
+  const uint32_t right = other[pos];
   const uint32_t side = a.side[block * (int64_t)g.block_symbols + (int64_t)step * kLanes + lane];
-  const uint32_t left = (exponent << 7) | (side & 0x7Fu) | ((side & 0x80u) << 8);
+  const int center = *a.center;
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
-  const uint32_t result = apply_op(left, other[pos], spec.op, spec.alpha_is_one != 0,
+  const int tail = tail_exponent_at(a, g, block, step, lane);
+  cp_async_wait_all();
+  const uint32_t exponent =
+      tail >= 0 ? (uint32_t)tail : index_to_exponent_byte(walk_to(a, g, column, step), center);
+  const uint32_t left = (exponent << 7) | (side & 0x7Fu) | ((side & 0x80u) << 8);
+  const uint32_t result = apply_op(left, right, spec.op, spec.alpha_is_one != 0,
                                    spec.beta_is_one != 0, alpha, beta);
   samples[idx] = (uint8_t)((result >> 7) & 0xFFu);
 }
-
 
 // Split one row of results (4 words, column order; padding already zeroed):
 // exponent bytes stay in column order, side bytes go to lane order.
@@ -155,8 +151,10 @@ __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint3
       make_uint2(prmt(c03, c47, pair_selector_low(q)), prmt(c03, c47, pair_selector_high(q)));
 }
 
-// Shared memory: [input payload image | DecodeShared | encode table | output payload image].
-__global__ void __launch_bounds__(kThreads, 2)
+// Shared memory: [input payload image | DecodeShared | encode table].  Finished output
+// words go straight to global memory (a warp's lanes write neighbouring words of the same
+// payload rows; L2 merges the sectors), which keeps four CTAs resident per SM.
+__global__ void __launch_bounds__(kThreads, 4)
 update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, bool other_vector_ok,
                     OpSpec spec, const int32_t* __restrict__ shifted_encode,
                     uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
@@ -167,7 +165,6 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + image);
   uint2* encode_table = reinterpret_cast<uint2*>(smem_raw + image + sizeof(DecodeShared));
-  uint32_t* out_image = reinterpret_cast<uint32_t*>(encode_table + 256);
 
   const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
@@ -178,7 +175,6 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
     const uint32_t packed = (uint32_t)shifted_encode[tid];
     encode_table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
   }
-  for (int w = 0; w < g.fixed_words; ++w) out_image[w * kLanes + tid] = 0u;
   if (block == 0 && tid < 4) encoded_out[g.streams * g.fixed_words + tid] = 0u;
   prepare_block(sh, payload, a, g, block);  // ends with a block barrier
 
@@ -193,7 +189,7 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   const uint32_t* last_row = payload + tid + (g.fixed_words + 2) * kLanes;
   uint16_t* tile = sh.tile[warp];
   const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
-  uint32_t* out_column = out_image + tid;
+  uint32_t* out_column = encoded_out + block * kLanes + tid;
   const int budget_bits = g.fixed_words * 32;
   uint32_t lo = 0;
   int pos = 0, extra_start = -1;
@@ -240,10 +236,10 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
     // ---- lane side: encode the result exponents ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(encode_table, tile_bytes, out_column, lane32, step0, valid,
+        open = encode_tile_rows<false>(encode_table, tile_bytes, out_column, g.streams, lane32, step0, valid,
                                        budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(encode_table, tile_bytes, out_column, lane32, step0, valid,
+        open = encode_tile_rows<true>(encode_table, tile_bytes, out_column, g.streams, lane32, step0, valid,
                                       budget_bits, pos, lo, extra_start);
     }
     if (!open) {
@@ -261,7 +257,11 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
     }
     __syncwarp();
   }
-  if (open && (pos & 31) != 0) out_column[(pos >> 5) * kLanes] = lo;
+  if (open) {
+    if ((pos & 31) != 0) out_column[(int64_t)(pos >> 5) * g.streams] = lo;
+    // Unused words of the lane are zero, as in the stand-alone encoder.
+    for (int w = (pos + 31) >> 5; w < g.fixed_words; ++w) out_column[(int64_t)w * g.streams] = 0u;
+  }
   extra_starts[block * kLanes + tid] = extra_start < 0 ? (uint8_t)255 : (uint8_t)extra_start;
 
   int bad = extra_start >= 0 ? 1 : 0;
@@ -272,18 +272,12 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
     bytes += __shfl_down_sync(0xFFFFFFFFu, bytes, d);
   }
   if (lane32 == 0) { sh.scan[warp] = bad; sh.scan[8 + warp] = bytes; }
-  __syncthreads();  // also publishes every lane's output words
+  __syncthreads();
   if (tid == 0) {
     int total_bad = 0, total_bytes = 0;
     for (int w = 0; w < kWarps; ++w) { total_bad += sh.scan[w]; total_bytes += sh.scan[8 + w]; }
     summaries[block] = total_bad;
     summaries[g.n_blocks + block] = total_bytes;
-  }
-  uint32_t* out = encoded_out + block * kLanes;
-  for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
-    const int w = i >> 6, c = (i & 63) * 4;
-    const uint4 v = *reinterpret_cast<const uint4*>(&out_image[w * kLanes + c]);
-    __stcs(reinterpret_cast<uint4*>(out + (int64_t)w * g.streams + c), v);
   }
 }
 
@@ -321,7 +315,9 @@ int lct_update_sample(const lct_operand* a, const void* other, const float* alph
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
   const int64_t count = logical_numel < lct::kSampleCount ? logical_numel : lct::kSampleCount;
   const unsigned grid = (unsigned)((count + lct::kThreads - 1) / lct::kThreads);
-  lct::update_sample_kernel<<<grid, lct::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  const size_t shared = lct::payload_image_bytes(fixed_words + 1);
+  if ((rc = lct::opt_in_shared(lct::update_sample_kernel, shared)) != 0) return rc;
+  lct::update_sample_kernel<<<grid, lct::kThreads, shared, static_cast<cudaStream_t>(stream)>>>(
       va, g, static_cast<const uint16_t*>(other), spec, samples);
   return (int)cudaGetLastError();
 }
@@ -342,8 +338,7 @@ int lct_update_fused(const lct_operand* a, const void* other, const float* alpha
     return LCT_E_NULL_POINTER;
   if (!lct::aligned16(side_out) || !lct::aligned16(encoded_out)) return LCT_E_ALIGNMENT;
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
-  const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2) +
-                        (size_t)fixed_words * lct::kLanes * 4;
+  const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
   if ((rc = lct::opt_in_shared(lct::update_fused_kernel, shared)) != 0) return rc;
   lct::update_fused_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared,
                              static_cast<cudaStream_t>(stream)>>>(
