@@ -348,7 +348,7 @@ def run_ours(args, rank: int, world: int, local: int):
     barrier(world)
     sampler = ClockSampler(local) if rank == 0 else None
     spans = []
-    with dispatch.LaunchTrace(timed=("lct_encode", "lct_decode")) as trace:
+    with dispatch.LaunchTrace(timed=("lct_decode",)) as trace:
         wall0 = time.perf_counter()
         for _ in range(args.steps):
             one_step(spans)
@@ -361,6 +361,19 @@ def run_ours(args, rank: int, world: int, local: int):
     value = world * 2 * bf16_bytes / (step_ms * 1e-3) / 1e9
     launches = trace.count
     kernel_ms = {name: statistics.mean(trace.milliseconds(name)) for name in trace.timed}
+    # The encoder kernel on its own: compress() above is one call whose four launches overlap,
+    # so the kernel is timed in a pass of its own through the stage-by-stage calls (same kernels).
+    from losslessly_compressed_tensors_b200.codec import encode as encode_module
+    encode_module.SINGLE_CALL_PIPELINE = False
+    try:
+        with dispatch.LaunchTrace(timed=("lct_encode",)) as encode_trace:
+            for _ in range(max(3, min(args.steps, 20))):
+                flush.zero_()
+                compress(x, dist_cfg, buffer).free()
+            torch.cuda.synchronize()
+    finally:
+        encode_module.SINGLE_CALL_PIPELINE = True
+    kernel_ms["lct_encode"] = statistics.mean(encode_trace.milliseconds("lct_encode"))
 
     # End to end: host buffers in, host buffers out, copies inside the timed region.  Every step
     # copies its input from pinned host memory and its decoded result back to pinned host memory;

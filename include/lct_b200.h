@@ -162,6 +162,24 @@ int lct_encode_noalloc(const void *src, uint8_t *side, int32_t *encoded,
                        int64_t logical_numel, int block_symbols, int steps, int fixed_words,
                        int precomputed, void *stream);
 
+/* The whole compression of one tensor into a shared arena as ONE call: the
+ * launches of lct_center_and_tables, lct_encode, lct_scan_allocate and
+ * lct_compact_tails, same arguments, same bytes everywhere.  Replaces the host
+ * sequence of LCT/codec/encode.py:62-186 (encode_components, buffered branch)
+ * with one crossing of the language boundary, and lets each kernel be
+ * scheduled while its predecessor is still running (programmatic stream
+ * serialisation): the encoder requests its first source rows while the center
+ * is being sampled and waits on the device only before it reads the shifted
+ * table.  `arena_storage` is the whole TensorBuffer storage (allocator words
+ * first); tails go to its payload region as with lct_compact_tails + a
+ * descriptor.  `side` may be NULL when `precomputed`. */
+int lct_compress(const void *src, int precomputed, uint8_t *side, int32_t *encoded,
+                 const int32_t *encode_table, const int32_t *decode_table, int32_t *center,
+                 int32_t *shifted_encode, int32_t *shifted_decode, uint8_t *extra_starts,
+                 int32_t *summaries, int32_t *counts, int32_t *descriptor, int32_t *blocks_out,
+                 void *arena_storage, int max_free_regions, int64_t size, int64_t logical_numel,
+                 int block_symbols, int steps, int fixed_words, void *stream);
+
 /* Many tensors of ONE codebook and geometry compressed by four launches in
  * total (centers, encode, scan + arena reservations in job order, tails),
  * overflow tails in a shared arena.  Equivalent to calling

@@ -27,6 +27,11 @@ from .geometry import geometry
 
 CENTER_SAMPLE_SIZE = 4096
 
+# Compress into a shared buffer through the single-call pipeline (``lct_compress``) instead of
+# one call per stage.  Same launches, same bytes; the switch exists so that the stages can be
+# timed one by one.
+SINGLE_CALL_PIPELINE = True
+
 
 def encode_components(
     source_values: torch.Tensor,
@@ -68,6 +73,29 @@ def encode_components(
         raise ValueError("placing the result needs a shared buffer (sizes must not depend on the data)")
     shifted_encode = scratch(256, torch.int32)
     shifted_decode = kept("decode_table", decode_table.numel(), torch.int32)
+    if (SINGLE_CALL_PIPELINE and buffer is not None and center is None and center_samples is None
+            and launch_encode is None and blocks > 0):
+        center = kept("center", 1, torch.int32)
+        encoded = kept("encoded", streams * fixed_words + 4, torch.int32)
+        extra_starts = scratch(streams, torch.uint8)
+        summaries = scratch(4 * blocks, torch.int32)
+        counts = kept("counts", 4, torch.int32)
+        blocks_out = kept("blocks", 3 * blocks, torch.int32)
+        descriptor = kept("descriptor", 4, torch.int32)
+        dispatch.compress_pipeline(
+            source_values, None if precomputed else sign_mantissa, encoded, encode_table,
+            decode_table, center, shifted_encode, shifted_decode, extra_starts, summaries, counts,
+            descriptor, blocks_out, buffer, size, precomputed=precomputed,
+            logical_numel=logical_numel, block_symbols=block_symbols, steps=steps,
+            fixed_words=fixed_words)
+        return CompressedTensor(
+            encoded, size, sign_mantissa,
+            fallback_starts=None, fallback_lanes=None, fallback_blocks=blocks_out,
+            fallback_buffer=buffer.data, fallback_descriptor=descriptor, buffer=buffer,
+            fallback_count=counts[:1], fallback_used=counts[1:2],
+            distribution=distribution, center=center, decode_table=shifted_decode, shape=shape,
+            layout=StorageLayout.COMPRESSED, stream_geometry=stream_geometry,
+        )
     if center is None:
         center = kept("center", 1, torch.int32)
         if center_samples is None:

@@ -121,6 +121,10 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
                      int64_t blocks, int regions) {
   __shared__ int scratch[33];
   __shared__ int alloc_scratch[2];
+  // The summaries come from the encoder in front of this kernel; the tail compaction behind
+  // it may be scheduled now and waits for this kernel itself.
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
   int running_count = 0, running_bytes = 0;
   for (int64_t base = 0; base < blocks; base += blockDim.x) {
     const int64_t i = base + threadIdx.x;
@@ -206,6 +210,17 @@ scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* 
   }
 }
 
+int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
+                         void* arena_storage, int64_t blocks, int max_free_regions,
+                         bool overlapped, cudaStream_t stream) {
+  if (overlapped)
+    return launch_overlapped(scan_allocate_kernel, 1, kScanThreads, 0, stream, summaries, counts,
+                             descriptor, arena_storage, blocks, max_free_regions);
+  scan_allocate_kernel<<<1, kScanThreads, 0, stream>>>(summaries, counts, descriptor, arena_storage,
+                                                       blocks, max_free_regions);
+  return (int)cudaGetLastError();
+}
+
 int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries,
                       void* arena_storage, int max_free_regions, int block_symbols,
                       cudaStream_t stream) {
@@ -254,9 +269,8 @@ int lct_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
   if (arena_storage != nullptr && descriptor == nullptr) return LCT_E_NULL_POINTER;
   if (blocks < 0) return LCT_E_BAD_ARGUMENT;
   if (arena_storage != nullptr && !power_of_two(max_free_regions)) return LCT_E_BAD_ARGUMENT;
-  lct::scan_allocate_kernel<<<1, lct::kScanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      summaries, counts, descriptor, arena_storage, blocks, max_free_regions);
-  return (int)cudaGetLastError();
+  return lct::launch_scan_allocate(summaries, counts, descriptor, arena_storage, blocks,
+                                   max_free_regions, false, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,5 +1,6 @@
-// Launchers of the multi-tensor kernels that live in other translation units
-// (lct_compress_batch in encode.cu strings them together).
+// Launchers of kernels that live in other translation units (lct_compress and
+// lct_compress_batch in encode.cu string them together), and the launch helper
+// for a kernel that may start while its predecessor in the stream still runs.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -16,5 +17,36 @@ int launch_center_batch(const lct_encode_job* jobs, int n_jobs, const int32_t* e
 int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries,
                       void* arena_storage, int max_free_regions, int block_symbols,
                       cudaStream_t stream);
+
+// tables.cu: center sample + shifted tables of one tensor.
+int launch_center(const void* src, int64_t logical_numel, bool precomputed,
+                  const int32_t* encode_table, const int32_t* decode_table, int32_t* center,
+                  int32_t* shifted_encode, int32_t* shifted_decode, cudaStream_t stream);
+
+// arena.cu: summary scan (+ arena reservation).  `overlapped`: see launch_overlapped.
+int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
+                         void* arena_storage, int64_t blocks, int max_free_regions,
+                         bool overlapped, cudaStream_t stream);
+
+// Launch with programmatic stream serialisation: the grid may be scheduled as soon as every
+// CTA of the previous kernel in the stream has exited or called
+// cudaTriggerProgrammaticLaunchCompletion(), and must call cudaGridDependencySynchronize()
+// before it touches anything that kernel (or anything before it) wrote.  Everything the
+// grid does ahead of that call overlaps the previous kernel's tail.
+template <typename... Params, typename... Args>
+int launch_overlapped(void (*kernel)(Params...), unsigned grid, unsigned threads, size_t shared,
+                      cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(threads);
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
 
 }  // namespace lct

@@ -112,13 +112,8 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   const int64_t block_base = block * (int64_t)g.block_symbols;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
 
-  {
-    const uint32_t packed = (uint32_t)shifted_encode[tid];
-    sh.table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
-  }
   for (int w = 0; w < g.fixed_words; ++w) payload[w * kLanes + tid] = 0u;
   if (block == 0 && tid < 4) encoded[g.streams * g.fixed_words + tid] = 0u;  // trailing pad words
-  __syncthreads();
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int budget_bits = g.fixed_words * 32;
@@ -142,6 +137,15 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   for (int u = 0; u < 2; ++u)
     source[u] = load_unit<kPrecomputed>(src, logical_of(2 * unit_p[u]), g.logical_numel,
                                         src_vector_ok, full_block);
+  // Everything above is independent of the tensor's center.  The shifted table may come from
+  // a kernel that is still running when this grid was launched with programmatic stream
+  // serialisation (lct_compress): wait for it only now, with the first source rows in flight.
+  cudaGridDependencySynchronize();
+  {
+    const uint32_t packed = (uint32_t)shifted_encode[tid];
+    sh.table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
+  }
+  __syncthreads();
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
     // ---- row phase ----
@@ -339,6 +343,7 @@ compact_tails_kernel(const void* __restrict__ src, uint8_t* lanes, uint8_t* star
                      const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
                      const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
                      EncodeShape g) {
+  cudaGridDependencySynchronize();  // prefixes and the reservation come from the scan in front
   compact_block<kPrecomputed>(src, lanes, starts, tail, descriptor, counts, blocks_out,
                               extra_starts, summaries, g, blockIdx.x);
 }
@@ -378,9 +383,11 @@ static int check_encode_shape(int64_t size, int64_t logical_numel, int block_sym
 
 extern "C" {
 
-int lct_encode(const void* src, uint8_t* side, int32_t* encoded, const int32_t* shifted_encode,
-               uint8_t* extra_starts, int32_t* summaries, int64_t size, int64_t logical_numel,
-               int block_symbols, int steps, int fixed_words, int precomputed, void* stream) {
+// Argument checks and launch shared by lct_encode and lct_compress.
+static int launch_encode(const void* src, uint8_t* side, int32_t* encoded,
+                         const int32_t* shifted_encode, uint8_t* extra_starts, int32_t* summaries,
+                         int64_t size, int64_t logical_numel, int block_symbols, int steps,
+                         int fixed_words, int precomputed, bool overlapped, cudaStream_t st) {
   lct::EncodeShape g;
   int rc = lct::check_encode_shape(size, logical_numel, block_symbols, steps, fixed_words, &g);
   if (rc) return rc;
@@ -395,29 +402,24 @@ int lct_encode(const void* src, uint8_t* side, int32_t* encoded, const int32_t* 
     return LCT_E_ALIGNMENT;
   const bool vector_ok = (s & (precomputed ? 7u : 15u)) == 0;
   const size_t shared = sizeof(lct::EncodeSharedHead) + (size_t)fixed_words * lct::kLanes * 4;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint32_t* words = reinterpret_cast<uint32_t*>(encoded);
-  if (precomputed) {
-    rc = (int)cudaFuncSetAttribute(lct::encode_kernel<true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (rc) return rc;
-    lct::encode_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, shared, st>>>(
-        src, vector_ok, side, words, shifted_encode, extra_starts, summaries, g);
-  } else {
-    rc = (int)cudaFuncSetAttribute(lct::encode_kernel<false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (rc) return rc;
-    lct::encode_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, shared, st>>>(
-        src, vector_ok, side, words, shifted_encode, extra_starts, summaries, g);
-  }
+  auto kernel = precomputed ? lct::encode_kernel<true> : lct::encode_kernel<false>;
+  rc = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+  if (rc) return rc;
+  if (overlapped)
+    return lct::launch_overlapped(kernel, (unsigned)g.n_blocks, lct::kThreads, shared, st, src,
+                                  vector_ok, side, words, shifted_encode, extra_starts, summaries, g);
+  kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, st>>>(src, vector_ok, side, words,
+                                                              shifted_encode, extra_starts,
+                                                              summaries, g);
   return (int)cudaGetLastError();
 }
 
-int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
-                      const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
-                      const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
-                      int64_t logical_numel, int block_symbols, int steps, int precomputed,
-                      void* stream) {
+static int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
+                          const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
+                          const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
+                          int64_t logical_numel, int block_symbols, int steps, int precomputed,
+                          bool overlapped, cudaStream_t st) {
   lct::EncodeShape g;
   int rc = lct::check_encode_shape(size, logical_numel, block_symbols, steps, 2, &g);
   if (rc) return rc;
@@ -426,14 +428,66 @@ int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t*
     return LCT_E_NULL_POINTER;
   // lanes/starts/tail may be NULL only when the tensor has no overflow at all
   // (zero-size private tensors); the kernel then never dereferences them.
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (precomputed)
-    lct::compact_tails_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, 0, st>>>(
-        src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts, summaries, g);
-  else
-    lct::compact_tails_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, 0, st>>>(
-        src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts, summaries, g);
+  auto kernel = precomputed ? lct::compact_tails_kernel<true> : lct::compact_tails_kernel<false>;
+  if (overlapped)
+    return lct::launch_overlapped(kernel, (unsigned)g.n_blocks, lct::kThreads, 0, st, src, lanes,
+                                  starts, tail, descriptor, counts, blocks_out, extra_starts,
+                                  summaries, g);
+  kernel<<<(unsigned)g.n_blocks, lct::kThreads, 0, st>>>(src, lanes, starts, tail, descriptor,
+                                                         counts, blocks_out, extra_starts,
+                                                         summaries, g);
   return (int)cudaGetLastError();
+}
+
+int lct_encode(const void* src, uint8_t* side, int32_t* encoded, const int32_t* shifted_encode,
+               uint8_t* extra_starts, int32_t* summaries, int64_t size, int64_t logical_numel,
+               int block_symbols, int steps, int fixed_words, int precomputed, void* stream) {
+  return launch_encode(src, side, encoded, shifted_encode, extra_starts, summaries, size,
+                       logical_numel, block_symbols, steps, fixed_words, precomputed, false,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
+                      const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
+                      const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
+                      int64_t logical_numel, int block_symbols, int steps, int precomputed,
+                      void* stream) {
+  return launch_compact(src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts,
+                        summaries, size, logical_numel, block_symbols, steps, precomputed, false,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int lct_compress(const void* src, int precomputed, uint8_t* side, int32_t* encoded,
+                 const int32_t* encode_table, const int32_t* decode_table, int32_t* center,
+                 int32_t* shifted_encode, int32_t* shifted_decode, uint8_t* extra_starts,
+                 int32_t* summaries, int32_t* counts, int32_t* descriptor, int32_t* blocks_out,
+                 void* arena_storage, int max_free_regions, int64_t size, int64_t logical_numel,
+                 int block_symbols, int steps, int fixed_words, void* stream) {
+  if (encode_table == nullptr || decode_table == nullptr || center == nullptr ||
+      shifted_encode == nullptr || counts == nullptr || descriptor == nullptr ||
+      arena_storage == nullptr || src == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 1. center + tables: an ordinary launch, so everything queued before this call is complete
+  //    and visible before any of the four kernels starts.
+  int rc = lct::launch_center(src, logical_numel, precomputed != 0, encode_table, decode_table,
+                              center, shifted_encode, shifted_decode, st);
+  if (rc) return rc;
+  // 2-4. each of these may be scheduled while its predecessor still runs and waits on the
+  //    device for it where its first dependent read is.
+  rc = launch_encode(src, side, encoded, shifted_encode, extra_starts, summaries, size,
+                     logical_numel, block_symbols, steps, fixed_words, precomputed, true, st);
+  if (rc) return rc;
+  rc = lct::launch_scan_allocate(summaries, counts, descriptor, arena_storage, size / block_symbols,
+                                 max_free_regions, true, st);
+  if (rc) return rc;
+  // The arena payload starts after the allocator words, padded to 16 bytes.
+  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
+  uint8_t* payload = static_cast<uint8_t*>(arena_storage) + metadata;
+  return launch_compact(src, payload, payload, payload, descriptor, counts, blocks_out,
+                        extra_starts, summaries, size, logical_numel, block_symbols, steps,
+                        precomputed, true, st);
 }
 
 }  // extern "C"

@@ -83,14 +83,14 @@ class LaunchTrace:
 _trace: LaunchTrace | None = None
 
 
-def _call(name: str, device: torch.device, *args) -> None:
-    """Launch entry point ``name`` on the current stream of ``device``."""
+def _call(name: str, device: torch.device, *args, launches: int = 1) -> None:
+    """Launch entry point ``name`` (``launches`` kernels) on the current stream of ``device``."""
     function = getattr(_lib.load(), name)
     trace = _trace
     with _on(device):
         stream = torch.cuda.current_stream(device)
         if trace is not None:
-            trace.count += 1
+            trace.count += launches
             if name in trace.timed:
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record(stream)
@@ -190,6 +190,25 @@ def prefix_allocate(summaries, counts, descriptor, buffer, blocks, buffered, max
         "lct_scan_allocate", device,
         summaries.data_ptr(), counts.data_ptr(), descriptor.data_ptr() if buffered else None,
         storage, blocks, max_free_regions)
+
+
+def compress_pipeline(source, side, encoded, encode_table, decode_table, center, shifted_encode,
+                      shifted_decode, extra_starts, summaries, counts, descriptor, blocks_out,
+                      buffer, size, *, precomputed, logical_numel, block_symbols, steps,
+                      fixed_words):
+    """Center, encode, scan + arena reservation and tail compaction of one tensor as one call
+    (four launches that overlap where their data allows); same bytes as the four wrappers
+    ``estimate_and_shift_encoding_table``, ``encode_kernel``, ``prefix_allocate`` and
+    ``compact_extra`` called in that order with a shared ``buffer``."""
+    device = _require_cuda(source)
+    _call(
+        "lct_compress", device,
+        _ptr(source), int(precomputed), _ptr(side), encoded.data_ptr(), encode_table.data_ptr(),
+        decode_table.data_ptr(), center.data_ptr(), shifted_encode.data_ptr(),
+        shifted_decode.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(),
+        counts.data_ptr(), descriptor.data_ptr(), blocks_out.data_ptr(),
+        buffer._storage.data_ptr(), buffer.max_free_regions, size, logical_numel, block_symbols,
+        steps, fixed_words, launches=4)
 
 
 def compact_extra(source, storage: FallbackStorage, final_counts, n_blocks, n_elements, *,

@@ -274,6 +274,40 @@ def test_shared_arena_many_live_tensors(oracle):
         assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
 
 
+@pytest.mark.parametrize("n,kind", [(1, "normal"), (65537, "normal"), (3 * 65536 + 77, "wide"),
+                                    (40 * 65536, "laplace")])
+def test_single_call_pipeline_matches_staged_calls(monkeypatch, n, kind):
+    """lct_compress (four overlapping launches behind one call) leaves exactly the bytes of the four
+    separate calls: every component, the arena contents and the allocator state."""
+    from losslessly_compressed_tensors_b200.codec import encode as encode_module
+    if kind == "laplace":
+        values = _laplace(n, 5, 0.02)
+    elif kind == "wide":   # exponents far outside the codebook: many overflowing lanes
+        values = _cpu_randn((n,), 6) * torch.exp2(torch.randint(-20, 20, (n,),
+                                                                generator=torch.Generator().manual_seed(7)).float())
+    else:
+        values = _cpu_randn((n,), 8)
+    x = values.to(torch.bfloat16).cuda()
+    dist = Distribution(DistType.LAPLACE, param=0.02)
+    results = []
+    for single in (True, False):
+        monkeypatch.setattr(encode_module, "SINGLE_CALL_PIPELINE", single)
+        buffer = TensorBuffer(8 << 20)
+        first = compress(x, dist, buffer)     # two live tensors: the second reservation starts
+        second = compress(x, dist, buffer)    # behind the first one
+        torch.cuda.synchronize()
+        assert torch.equal(decompress(second).view(torch.int16), x.view(torch.int16))
+        results.append((first, second, buffer))
+    (a1, a2, abuf), (b1, b2, bbuf) = results
+    for got, want in ((a1, b1), (a2, b2)):
+        for field in ("data", "sign_mantissa", "center", "decode_table", "fallback_blocks",
+                      "fallback_count", "fallback_used", "fallback_descriptor"):
+            assert torch.equal(getattr(got, field), getattr(want, field)), field
+        assert got.memory_size() == want.memory_size()
+    assert torch.equal(abuf._storage, bbuf._storage)
+    assert _free_regions_snapshot(abuf) == _free_regions_snapshot(bbuf)
+
+
 def test_full_size_round_trip_properties():
     """BASELINE configuration 2 at full size (64 Mi elements): size-independent properties."""
     n = 8192 * 8192
