@@ -292,6 +292,26 @@ int lct_update_fused(const lct_operand *a /* host pointer */, const void *other,
                      uint8_t *spill, int64_t size, int64_t logical_numel, int block_symbols,
                      int steps, int fixed_words, int rare_length, void *stream);
 
+/* The whole update into a shared arena as ONE call: lct_update_sample,
+ * lct_center_and_tables(samples, precomputed=1), lct_update_fused,
+ * lct_scan_allocate and lct_compact_tails(src=spill, precomputed=1), same
+ * arguments, same bytes; the later kernels are scheduled while their
+ * predecessors run (the fused kernel stages its input and builds its decode
+ * tables while the new center is computed).  `encode_table`/`decode_table` are
+ * the base tables of the RESULT's codebook, whose geometry must equal A's.
+ * Work buffers: samples uint8[min(logical_numel, 4096)], shifted_encode
+ * int32[256], extra_starts uint8[streams], summaries int32[4*blocks], spill
+ * uint8[size]. */
+int lct_update(const lct_operand *a /* host pointer */, const void *other, const float *alpha,
+               const float *beta, int op, int alpha_is_one, int beta_is_one,
+               const int32_t *encode_table, const int32_t *decode_table, uint8_t *samples,
+               int32_t *center, int32_t *shifted_encode, int32_t *shifted_decode,
+               uint8_t *side_out, int32_t *encoded_out, uint8_t *extra_starts,
+               int32_t *summaries, uint8_t *spill, int32_t *counts, int32_t *descriptor,
+               int32_t *blocks_out, void *arena_storage, int max_free_regions, int64_t size,
+               int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+               int rare_length, void *stream);
+
 /* ---- shared overflow arena (TensorBuffer) ---------------------------------- */
 /* storage layout: int32 free_starts[R] | free_sizes[R] | free_count | lock |
  * generation | pad to 16 bytes | payload[capacity]  (LCT/tensor_buffer.py:58-82).

@@ -18,6 +18,7 @@ from ..comp_tensor import CompressedTensor
 from ..compression.huffman_tables import get_distribution_tables
 from ..kernels import dispatch
 from ..tensor_buffer import TensorBuffer
+from . import encode as encode_module
 from .decode import decode as decode_dense, operand_of
 from .encode import encode as compress_dense, encode_components as compress_components
 from .geometry import geometry
@@ -105,9 +106,37 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
                 logical_numel=data.logical_numel, block_symbols=block_symbols, lanes=lanes,
                 steps=steps, fixed_words=fixed_words)
     samples = torch.empty(min(data.logical_numel, 4096), dtype=torch.uint8, device=device)
-    dispatch.update_sample(operand, other, samples, data.size, alpha, beta, **meta)
     side_out = torch.empty(data.size, dtype=torch.uint8, device=device)
     spill = torch.empty(data.size, dtype=torch.uint8, device=device)  # touched by overflow lanes only
+    if buffer is not None and encode_module.SINGLE_CALL_PIPELINE:
+        # One call for the whole update; same launches and bytes as the staged sequence below.
+        if buffer.capacity_bytes % 4:
+            raise ValueError("TensorBuffer capacity must be divisible by 4")
+        encode_table, decode_table, _ = get_distribution_tables(result_distribution, device)
+        blocks = data.size // block_symbols
+        streams = blocks * lanes
+
+        def new(n, dtype):
+            return torch.empty(n, dtype=dtype, device=device)
+
+        center, counts, descriptor = new(1, torch.int32), new(4, torch.int32), new(4, torch.int32)
+        shifted_decode = new(decode_table.numel(), torch.int32)
+        encoded = new(streams * fixed_words + 4, torch.int32)
+        blocks_out = new(3 * blocks, torch.int32)
+        dispatch.update_pipeline(
+            operand, other, alpha, beta, encode_table, decode_table, samples, center,
+            new(256, torch.int32), shifted_decode, side_out, encoded, new(streams, torch.uint8),
+            new(4 * blocks, torch.int32), spill, counts, descriptor, blocks_out, buffer, data.size,
+            **meta)
+        return CompressedTensor(
+            encoded, data.size, side_out, fallback_starts=None, fallback_lanes=None,
+            fallback_blocks=blocks_out, fallback_buffer=buffer.data,
+            fallback_descriptor=descriptor, buffer=buffer, fallback_count=counts[:1],
+            fallback_used=counts[1:2], distribution=result_distribution, center=center,
+            decode_table=shifted_decode, shape=data.shape, layout=StorageLayout.COMPRESSED,
+            stream_geometry=geometry(result_distribution),
+        )
+    dispatch.update_sample(operand, other, samples, data.size, alpha, beta, **meta)
 
     def launch(shifted_encode, encoded, extra_starts, summaries):
         dispatch.update_fused(operand, other, shifted_encode, side_out, encoded, extra_starts,

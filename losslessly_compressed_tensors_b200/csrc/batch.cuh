@@ -21,7 +21,15 @@ int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries
 // tables.cu: center sample + shifted tables of one tensor.
 int launch_center(const void* src, int64_t logical_numel, bool precomputed,
                   const int32_t* encode_table, const int32_t* decode_table, int32_t* center,
-                  int32_t* shifted_encode, int32_t* shifted_decode, cudaStream_t stream);
+                  int32_t* shifted_encode, int32_t* shifted_decode, bool overlapped,
+                  cudaStream_t stream);
+
+// encode.cu: overflow entries + raw tails of one tensor (argument checks included).
+int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
+                   const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
+                   const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
+                   int64_t logical_numel, int block_symbols, int steps, int precomputed,
+                   bool overlapped, cudaStream_t stream);
 
 // arena.cu: summary scan (+ arena reservation).  `overlapped`: see launch_overlapped.
 int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,

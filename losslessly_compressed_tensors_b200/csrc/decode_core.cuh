@@ -174,8 +174,16 @@ __device__ __forceinline__ void decode_tile_rows(BitReader& r, const DecodeShare
 
 // CTA prologue: stage the payload, build the center-specific symbol table and
 // this block's overflow map.  Ends with a block barrier.
+struct NoExtraWork {
+  __device__ __forceinline__ void operator()() const {}
+};
+
+// `before_barrier` runs once per thread after this block's loads have been issued and before
+// the closing barrier (work of the caller that the same barrier should publish).
+template <typename Extra = NoExtraWork>
 __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payload,
-                                              const OperandView& a, const Shape& g, int64_t block) {
+                                              const OperandView& a, const Shape& g, int64_t block,
+                                              Extra before_barrier = Extra()) {
   const int tid = threadIdx.x;
   // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
   const uint32_t* rows = a.encoded + block * kLanes;
@@ -232,6 +240,7 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
       }
     }
   }
+  before_barrier();
   cp_async_wait_all();
   __syncthreads();
 }

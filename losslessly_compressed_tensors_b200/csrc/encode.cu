@@ -415,7 +415,11 @@ static int launch_encode(const void* src, uint8_t* side, int32_t* encoded,
   return (int)cudaGetLastError();
 }
 
-static int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
+}  // extern "C"
+
+namespace lct {
+
+int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
                           const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
                           const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
                           int64_t logical_numel, int block_symbols, int steps, int precomputed,
@@ -439,6 +443,10 @@ static int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint
   return (int)cudaGetLastError();
 }
 
+}  // namespace lct
+
+extern "C" {
+
 int lct_encode(const void* src, uint8_t* side, int32_t* encoded, const int32_t* shifted_encode,
                uint8_t* extra_starts, int32_t* summaries, int64_t size, int64_t logical_numel,
                int block_symbols, int steps, int fixed_words, int precomputed, void* stream) {
@@ -452,7 +460,7 @@ int lct_compact_tails(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t*
                       const uint8_t* extra_starts, const int32_t* summaries, int64_t size,
                       int64_t logical_numel, int block_symbols, int steps, int precomputed,
                       void* stream) {
-  return launch_compact(src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts,
+  return lct::launch_compact(src, lanes, starts, tail, descriptor, counts, blocks_out, extra_starts,
                         summaries, size, logical_numel, block_symbols, steps, precomputed, false,
                         static_cast<cudaStream_t>(stream));
 }
@@ -472,7 +480,7 @@ int lct_compress(const void* src, int precomputed, uint8_t* side, int32_t* encod
   // 1. center + tables: an ordinary launch, so everything queued before this call is complete
   //    and visible before any of the four kernels starts.
   int rc = lct::launch_center(src, logical_numel, precomputed != 0, encode_table, decode_table,
-                              center, shifted_encode, shifted_decode, st);
+                              center, shifted_encode, shifted_decode, false, st);
   if (rc) return rc;
   // 2-4. each of these may be scheduled while its predecessor still runs and waits on the
   //    device for it where its first dependent read is.
@@ -485,7 +493,7 @@ int lct_compress(const void* src, int precomputed, uint8_t* side, int32_t* encod
   // The arena payload starts after the allocator words, padded to 16 bytes.
   const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
   uint8_t* payload = static_cast<uint8_t*>(arena_storage) + metadata;
-  return launch_compact(src, payload, payload, payload, descriptor, counts, blocks_out,
+  return lct::launch_compact(src, payload, payload, payload, descriptor, counts, blocks_out,
                         extra_starts, summaries, size, logical_numel, block_symbols, steps,
                         precomputed, true, st);
 }

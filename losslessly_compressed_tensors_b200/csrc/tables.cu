@@ -117,7 +117,9 @@ center_and_tables_kernel(const void* __restrict__ src, int64_t n,
                          const int32_t* __restrict__ base_encode,
                          const int32_t* __restrict__ base_decode, int32_t* center_out,
                          int32_t* shifted_encode, int32_t* shifted_decode) {
-  // A dependent encoder may start its table-independent prologue right away.
+  // The samples may come from a kernel that was still running when this one was scheduled;
+  // a dependent encoder may start its table-independent prologue right away.
+  cudaGridDependencySynchronize();
   cudaTriggerProgrammaticLaunchCompletion();
   center_and_tables<kPrecomputed>(src, n, base_encode, base_decode, center_out, shifted_encode,
                                   shifted_decode);
@@ -168,13 +170,14 @@ pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pai
 
 int launch_center(const void* src, int64_t logical_numel, bool precomputed,
                   const int32_t* encode_table, const int32_t* decode_table, int32_t* center,
-                  int32_t* shifted_encode, int32_t* shifted_decode, cudaStream_t stream) {
-  if (precomputed)
-    center_and_tables_kernel<true><<<1, kTableThreads, 0, stream>>>(
-        src, logical_numel, encode_table, decode_table, center, shifted_encode, shifted_decode);
-  else
-    center_and_tables_kernel<false><<<1, kTableThreads, 0, stream>>>(
-        src, logical_numel, encode_table, decode_table, center, shifted_encode, shifted_decode);
+                  int32_t* shifted_encode, int32_t* shifted_decode, bool overlapped,
+                  cudaStream_t stream) {
+  auto kernel = precomputed ? center_and_tables_kernel<true> : center_and_tables_kernel<false>;
+  if (overlapped)
+    return launch_overlapped(kernel, 1, kTableThreads, 0, stream, src, logical_numel, encode_table,
+                             decode_table, center, shifted_encode, shifted_decode);
+  kernel<<<1, kTableThreads, 0, stream>>>(src, logical_numel, encode_table, decode_table, center,
+                                          shifted_encode, shifted_decode);
   return (int)cudaGetLastError();
 }
 
@@ -207,7 +210,8 @@ int lct_center_and_tables(const void* src, int64_t logical_numel, int precompute
   if (logical_numel < 0) return LCT_E_BAD_ARGUMENT;
   if (logical_numel > 0 && src == nullptr) return LCT_E_NULL_POINTER;
   return lct::launch_center(src, logical_numel, precomputed != 0, encode_table, decode_table, center,
-                            shifted_encode, shifted_decode, static_cast<cudaStream_t>(stream));
+                            shifted_encode, shifted_decode, false,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int lct_shift_tables(const int32_t* encode_table, const int32_t* decode_table,

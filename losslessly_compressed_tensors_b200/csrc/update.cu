@@ -18,6 +18,7 @@
 // Lanes whose output overflows their bit budget also store their raw result
 // exponents from the overflow step on into `spill` (logical order), which is
 // what the tail compaction reads afterwards; nothing else touches `spill`.
+#include "batch.cuh"
 #include "decode_core.cuh"
 #include "encode_core.cuh"
 
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(kThreads)
 update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, OpSpec spec,
                      uint8_t* __restrict__ samples) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  cudaTriggerProgrammaticLaunchCompletion();  // the center kernel behind this one waits on its own
   const int tid = threadIdx.x;
   uint32_t* column = reinterpret_cast<uint32_t*>(smem_raw) + tid;
   const int64_t n = g.logical_numel;
@@ -171,12 +173,15 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
-  {
+  if (block == 0 && tid < 4) encoded_out[g.streams * g.fixed_words + tid] = 0u;
+  // The input operand does not depend on the result's center: its payload is staged and its
+  // tables are built before this grid waits for the kernel that writes the shifted encode
+  // table (which may still be running when the grid was launched by lct_update).
+  prepare_block(sh, payload, a, g, block, [&] {
+    cudaGridDependencySynchronize();
     const uint32_t packed = (uint32_t)shifted_encode[tid];
     encode_table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
-  }
-  if (block == 0 && tid < 4) encoded_out[g.streams * g.fixed_words + tid] = 0u;
-  prepare_block(sh, payload, a, g, block);  // ends with a block barrier
+  });  // ends with a block barrier
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
@@ -302,10 +307,10 @@ static int check_update_args(const lct_operand* a, const void* other, const floa
   return 0;
 }
 
-int lct_update_sample(const lct_operand* a, const void* other, const float* alpha,
-                      const float* beta, int op, int alpha_is_one, int beta_is_one,
-                      uint8_t* samples, int64_t size, int64_t logical_numel, int block_symbols,
-                      int steps, int fixed_words, int rare_length, void* stream) {
+static int launch_sample(const lct_operand* a, const void* other, const float* alpha,
+                         const float* beta, int op, int alpha_is_one, int beta_is_one,
+                         uint8_t* samples, int64_t size, int64_t logical_numel, int block_symbols,
+                         int steps, int fixed_words, int rare_length, cudaStream_t stream) {
   lct::Shape g;
   lct::OperandView va;
   int rc = lct::check_shape(size, logical_numel, block_symbols, steps, fixed_words, rare_length, &g);
@@ -317,17 +322,17 @@ int lct_update_sample(const lct_operand* a, const void* other, const float* alph
   const unsigned grid = (unsigned)((count + lct::kThreads - 1) / lct::kThreads);
   const size_t shared = lct::payload_image_bytes(fixed_words + 1);
   if ((rc = lct::opt_in_shared(lct::update_sample_kernel, shared)) != 0) return rc;
-  lct::update_sample_kernel<<<grid, lct::kThreads, shared, static_cast<cudaStream_t>(stream)>>>(
+  lct::update_sample_kernel<<<grid, lct::kThreads, shared, stream>>>(
       va, g, static_cast<const uint16_t*>(other), spec, samples);
   return (int)cudaGetLastError();
 }
 
-int lct_update_fused(const lct_operand* a, const void* other, const float* alpha,
-                     const float* beta, int op, int alpha_is_one, int beta_is_one,
-                     const int32_t* shifted_encode, uint8_t* side_out, int32_t* encoded_out,
-                     uint8_t* extra_starts, int32_t* summaries, uint8_t* spill, int64_t size,
-                     int64_t logical_numel, int block_symbols, int steps, int fixed_words,
-                     int rare_length, void* stream) {
+static int launch_fused(const lct_operand* a, const void* other, const float* alpha,
+                        const float* beta, int op, int alpha_is_one, int beta_is_one,
+                        const int32_t* shifted_encode, uint8_t* side_out, int32_t* encoded_out,
+                        uint8_t* extra_starts, int32_t* summaries, uint8_t* spill, int64_t size,
+                        int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                        int rare_length, bool overlapped, cudaStream_t stream) {
   lct::Shape g;
   lct::OperandView va;
   int rc = lct::check_shape(size, logical_numel, block_symbols, steps, fixed_words, rare_length, &g);
@@ -340,11 +345,74 @@ int lct_update_fused(const lct_operand* a, const void* other, const float* alpha
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
   const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
   if ((rc = lct::opt_in_shared(lct::update_fused_kernel, shared)) != 0) return rc;
-  lct::update_fused_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared,
-                             static_cast<cudaStream_t>(stream)>>>(
-      va, g, static_cast<const uint16_t*>(other), lct::aligned16(other), spec, shifted_encode,
-      side_out, reinterpret_cast<uint32_t*>(encoded_out), extra_starts, summaries, spill);
+  const uint16_t* dense = static_cast<const uint16_t*>(other);
+  uint32_t* words = reinterpret_cast<uint32_t*>(encoded_out);
+  if (overlapped)
+    return lct::launch_overlapped(lct::update_fused_kernel, (unsigned)g.n_blocks, lct::kThreads,
+                                  shared, stream, va, g, dense, lct::aligned16(other), spec,
+                                  shifted_encode, side_out, words, extra_starts, summaries, spill);
+  lct::update_fused_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, stream>>>(
+      va, g, dense, lct::aligned16(other), spec, shifted_encode, side_out, words, extra_starts,
+      summaries, spill);
   return (int)cudaGetLastError();
+}
+
+int lct_update_sample(const lct_operand* a, const void* other, const float* alpha,
+                      const float* beta, int op, int alpha_is_one, int beta_is_one,
+                      uint8_t* samples, int64_t size, int64_t logical_numel, int block_symbols,
+                      int steps, int fixed_words, int rare_length, void* stream) {
+  return launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples, size,
+                       logical_numel, block_symbols, steps, fixed_words, rare_length,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int lct_update_fused(const lct_operand* a, const void* other, const float* alpha,
+                     const float* beta, int op, int alpha_is_one, int beta_is_one,
+                     const int32_t* shifted_encode, uint8_t* side_out, int32_t* encoded_out,
+                     uint8_t* extra_starts, int32_t* summaries, uint8_t* spill, int64_t size,
+                     int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                     int rare_length, void* stream) {
+  return launch_fused(a, other, alpha, beta, op, alpha_is_one, beta_is_one, shifted_encode,
+                      side_out, encoded_out, extra_starts, summaries, spill, size, logical_numel,
+                      block_symbols, steps, fixed_words, rare_length, false,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int lct_update(const lct_operand* a, const void* other, const float* alpha, const float* beta,
+               int op, int alpha_is_one, int beta_is_one, const int32_t* encode_table,
+               const int32_t* decode_table, uint8_t* samples, int32_t* center,
+               int32_t* shifted_encode, int32_t* shifted_decode, uint8_t* side_out,
+               int32_t* encoded_out, uint8_t* extra_starts, int32_t* summaries, uint8_t* spill,
+               int32_t* counts, int32_t* descriptor, int32_t* blocks_out, void* arena_storage,
+               int max_free_regions, int64_t size, int64_t logical_numel, int block_symbols,
+               int steps, int fixed_words, int rare_length, void* stream) {
+  if (encode_table == nullptr || decode_table == nullptr || center == nullptr ||
+      counts == nullptr || descriptor == nullptr || arena_storage == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 1. the sample pre-pass: an ordinary launch, so everything queued before this call is
+  //    complete and visible before any of the five kernels starts.
+  int rc = launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples, size,
+                         logical_numel, block_symbols, steps, fixed_words, rare_length, st);
+  if (rc) return rc;
+  // 2-5. each may be scheduled while its predecessor runs and waits for it on the device.
+  const int64_t count = logical_numel < lct::kSampleCount ? logical_numel : lct::kSampleCount;
+  rc = lct::launch_center(samples, count, true, encode_table, decode_table, center, shifted_encode,
+                          shifted_decode, true, st);
+  if (rc) return rc;
+  rc = launch_fused(a, other, alpha, beta, op, alpha_is_one, beta_is_one, shifted_encode, side_out,
+                    encoded_out, extra_starts, summaries, spill, size, logical_numel, block_symbols,
+                    steps, fixed_words, rare_length, true, st);
+  if (rc) return rc;
+  rc = lct::launch_scan_allocate(summaries, counts, descriptor, arena_storage, size / block_symbols,
+                                 max_free_regions, true, st);
+  if (rc) return rc;
+  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
+  uint8_t* payload = static_cast<uint8_t*>(arena_storage) + metadata;
+  return lct::launch_compact(spill, payload, payload, payload, descriptor, counts, blocks_out,
+                             extra_starts, summaries, size, logical_numel, block_symbols, steps, 1,
+                             true, st);
 }
 
 }  // extern "C"

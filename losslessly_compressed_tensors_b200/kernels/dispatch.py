@@ -316,6 +316,28 @@ def update_fused(operand: Operand, other, shifted_encode, side_out, encoded_out,
         n_elements, logical_numel, block_symbols, steps, fixed_words, rare_length)
 
 
+def update_pipeline(operand: Operand, other, alpha, beta, encode_table, decode_table, samples,
+                    center, shifted_encode, shifted_decode, side_out, encoded_out, extra_starts,
+                    summaries, spill, counts, descriptor, blocks_out, buffer, n_elements, *, op,
+                    alpha_is_one, beta_is_one, rare_length, logical_numel, block_symbols, lanes,
+                    steps, fixed_words):
+    """Sample, center, decode-op-encode, scan + reservation and tail compaction of a fused update
+    as one call (five launches that overlap where their data allows)."""
+    device = _require_cuda(side_out)
+    _call(
+        "lct_update", device,
+        ctypes.byref(operand), other.data_ptr(),
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        op, int(alpha_is_one), int(beta_is_one), encode_table.data_ptr(), decode_table.data_ptr(),
+        samples.data_ptr(), center.data_ptr(), shifted_encode.data_ptr(),
+        shifted_decode.data_ptr(), side_out.data_ptr(), encoded_out.data_ptr(),
+        extra_starts.data_ptr(), summaries.data_ptr(), spill.data_ptr(), counts.data_ptr(),
+        descriptor.data_ptr(), blocks_out.data_ptr(), buffer._storage.data_ptr(),
+        buffer.max_free_regions, n_elements, logical_numel, block_symbols, steps, fixed_words,
+        rare_length, launches=5)
+
+
 def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements, *,
                    compressed_output, rare_length, logical_numel, block_symbols, lanes, steps,
                    fixed_words):
