@@ -67,7 +67,7 @@ typedef struct lct_operand {
   const uint8_t *side;           /* uint8[size] sign+mantissa bytes, storage order */
   const int32_t *shifted_decode; /* int32[1024], built at encode time */
   const int32_t *center;         /* int32[1] */
-  const uint32_t *pair_table;    /* uint32[4096] from lct_build_pair_table for this codebook */
+  const uint32_t *pair_table;    /* uint32[LCT_PAIR_TABLE_WORDS] from lct_build_pair_table for this codebook */
   lct_overflow overflow;
 } lct_operand;
 
@@ -78,11 +78,15 @@ const char *lct_error_string(int code);
 
 /* ---- codebook preparation ------------------------------------------------ */
 
-/* Two-symbol lookup table over 12 stream bits, in table-index space, derived
- * from a codebook's first-level decode table (int32[1024]).  Depends only on
- * the Distribution, so callers build it once per codebook and device.  No
- * counterpart in the reference (its decoders look up one symbol at a time,
- * LCT/kernels/primitives.py:17-36). */
+/* Two-symbol lookup tables over 12 stream bits, derived from a codebook's
+ * first-level decode table (int32[1024]): LCT_PAIR_TABLE_WORDS words, one
+ * 4096-entry table per possible center (-128..127) with the symbols already
+ * stored as exponent bytes, so a decoder CTA copies the 16 KB of its tensor's
+ * center and needs no per-tensor table of its own.  Depends only on the
+ * Distribution: callers build it once per codebook and device (4 MiB).  No
+ * counterpart in the reference (its decoders look up one symbol at a time
+ * in the per-tensor shifted table, LCT/kernels/primitives.py:17-36). */
+#define LCT_PAIR_TABLE_WORDS (256 * 4096)
 int lct_build_pair_table(const int32_t *decode_table, int rare_length, uint32_t *pair_table,
                          void *stream);
 

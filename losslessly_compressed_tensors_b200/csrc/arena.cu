@@ -155,13 +155,23 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
 
 // All jobs of a batch.  Phase 1: every warp takes jobs in turn and scans that
 // job's block summaries with shuffles.  Phase 2: the reservations, strictly in
-// job order (so the arena ends up exactly as after one call per job); jobs
-// without overflow get the "empty request" descriptor without touching the lock,
-// which is what the locked path would have written.
+// job order, so the arena ends up exactly as after one call per job.  The lock
+// is taken once and the free list is worked on in shared memory (one thread,
+// no global round trips per job), then written back; arenas with more free-list
+// slots than fit there take the per-job path.  Jobs without overflow get the
+// "empty request" descriptor, which is what the allocator would have written.
+constexpr int kListSlots = 1024;
+
 __global__ void __launch_bounds__(kScanThreads)
 scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* summaries,
                   void* arena_storage, int regions, int block_symbols) {
   __shared__ int alloc_scratch[2];
+  __shared__ int32_t list_starts[kListSlots], list_sizes[kListSlots];
+  __shared__ int32_t job_request[kScanThreads], job_start[kScanThreads], job_size[kScanThreads];
+  __shared__ int list_count;
+  // Summaries come from the encoder in front; the compaction behind may be scheduled now.
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   for (int j = warp; j < n_jobs; j += warps) {
     const lct_encode_job& job = jobs[j];
@@ -195,19 +205,85 @@ scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* 
   __threadfence_block();
   __syncthreads();
   const Arena arena = arena_of(arena_storage, regions);
-  for (int j = 0; j < n_jobs; ++j) {
-    const lct_encode_job& job = jobs[j];
-    const int32_t request = job.counts[1] + 2 * job.counts[0];  // uniform across the CTA
-    if (request > 0) {
-      arena_allocate(arena, regions, request, job.descriptor, alloc_scratch);
-      __syncthreads();
-    } else if (threadIdx.x == 0) {
-      job.descriptor[0] = -1;
-      job.descriptor[1] = 0;
-      job.descriptor[2] = 2;
-      job.descriptor[3] = *arena.generation;
+  if (regions > kListSlots) {
+    for (int j = 0; j < n_jobs; ++j) {
+      const lct_encode_job& job = jobs[j];
+      const int32_t request = job.counts[1] + 2 * job.counts[0];  // uniform across the CTA
+      if (request > 0) {
+        arena_allocate(arena, regions, request, job.descriptor, alloc_scratch);
+        __syncthreads();
+      } else if (threadIdx.x == 0) {
+        job.descriptor[0] = -1;
+        job.descriptor[1] = 0;
+        job.descriptor[2] = 2;
+        job.descriptor[3] = *arena.generation;
+      }
     }
+    return;
   }
+  const int32_t generation = *arena.generation;
+  const bool locked = arena_lock(arena, alloc_scratch);
+  const int first_count = locked ? *arena.count : 0;
+  for (int i = threadIdx.x; i < first_count; i += blockDim.x) {
+    list_starts[i] = arena.starts[i];
+    list_sizes[i] = arena.sizes[i];
+  }
+  if (threadIdx.x == 0) list_count = first_count;
+  for (int base = 0; base < n_jobs; base += blockDim.x) {
+    const int j = base + threadIdx.x;
+    if (j < n_jobs) job_request[threadIdx.x] = jobs[j].counts[1] + 2 * jobs[j].counts[0];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int count = list_count;
+      const int chunk = min((int)blockDim.x, n_jobs - base);
+      for (int k = 0; k < chunk; ++k) {
+        const int32_t request = job_request[k];
+        int32_t start = -1, size = 0;
+        if (request > 0 && locked) {
+          const int32_t wanted = (request + 15) / 16 * 16;
+          int slot = 0;
+          while (slot < count && list_sizes[slot] < wanted) ++slot;
+          if (slot < count) {
+            start = list_starts[slot];
+            size = wanted;
+            if (list_sizes[slot] == wanted) {  // exact fit: the region disappears
+              for (int i = slot; i + 1 < count; ++i) {
+                list_starts[i] = list_starts[i + 1];
+                list_sizes[i] = list_sizes[i + 1];
+              }
+              --count;
+            } else {
+              list_starts[slot] = start + wanted;
+              list_sizes[slot] -= wanted;
+            }
+          }
+        }
+        job_start[k] = start;
+        job_size[k] = size;
+      }
+      list_count = count;
+    }
+    __syncthreads();
+    if (j < n_jobs) {
+      const int32_t request = job_request[threadIdx.x];
+      int32_t* descriptor = jobs[j].descriptor;
+      descriptor[0] = job_start[threadIdx.x];
+      descriptor[1] = job_size[threadIdx.x];
+      descriptor[2] = request <= 0 ? 2
+                      : !locked    ? kStatusLockTimeout
+                                   : (job_start[threadIdx.x] >= 0 ? 0 : 1);
+      descriptor[3] = generation;
+    }
+    __syncthreads();
+  }
+  if (!locked) return;
+  // Slots that left the list keep their last contents, as after per-job calls.
+  for (int i = threadIdx.x; i < first_count; i += blockDim.x) {
+    arena.starts[i] = list_starts[i];
+    arena.sizes[i] = list_sizes[i];
+  }
+  if (threadIdx.x == 0) *arena.count = list_count;
+  arena_unlock(arena);
 }
 
 int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
@@ -224,9 +300,8 @@ int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descripto
 int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries,
                       void* arena_storage, int max_free_regions, int block_symbols,
                       cudaStream_t stream) {
-  scan_batch_kernel<<<1, kScanThreads, 0, stream>>>(jobs, n_jobs, summaries, arena_storage,
-                                                    max_free_regions, block_symbols);
-  return (int)cudaGetLastError();
+  return launch_overlapped(scan_batch_kernel, 1, kScanThreads, 0, stream, jobs, n_jobs, summaries,
+                           arena_storage, max_free_regions, block_symbols);
 }
 
 }  // namespace lct

@@ -31,6 +31,7 @@ constexpr int kTilePairs = 16;          // row pairs per warp tile (32 rows)
 constexpr int kTileRows = 2 * kTilePairs;
 constexpr int kPairBits = 12;           // stream bits indexing the two-symbol table
 constexpr int kPairEntries = 1 << kPairBits;
+constexpr int kCenterValues = 256;     // centers -128..127: one two-symbol table each
 constexpr int kFirstMask = 1023;        // the codebook's first-level table covers 10 bits
 constexpr int kSampleCount = 4096;     // positions the exponent center is estimated from
 

@@ -352,6 +352,7 @@ __global__ void __launch_bounds__(kThreads)
 compact_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, uint8_t* arena_payload,
                      const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
                      EncodeShape common) {
+  cudaGridDependencySynchronize();  // prefixes and reservations come from the scan in front
   const int64_t block = blockIdx.x;
   const lct_encode_job& job = jobs[find_encode_job(jobs, n_jobs, block)];
   const EncodeShape g = shape_of_job(job, common);
@@ -523,17 +524,20 @@ int lct_compress_batch(const lct_encode_job* jobs, int n_jobs, int64_t total_blo
   rc = (int)cudaFuncSetAttribute(lct::encode_batch_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   if (rc) return rc;
-  lct::encode_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, shared, st>>>(
-      jobs, n_jobs, shifted_encode, extra_starts, summaries, g);
-  if ((rc = (int)cudaGetLastError())) return rc;
+  // Centers first (ordinary launch); the three kernels behind it may each be scheduled while
+  // their predecessor still runs and wait for it on the device.
+  if ((rc = lct::launch_overlapped(lct::encode_batch_kernel, (unsigned)total_blocks, lct::kThreads,
+                                   shared, st, jobs, n_jobs, shifted_encode, extra_starts,
+                                   summaries, g)))
+    return rc;
   if ((rc = lct::launch_scan_batch(jobs, n_jobs, summaries, arena_storage, max_free_regions,
                                    block_symbols, st)))
     return rc;
   // The arena payload starts after the allocator words, padded to 16 bytes.
   const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
-  lct::compact_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, 0, st>>>(
-      jobs, n_jobs, static_cast<uint8_t*>(arena_storage) + metadata, extra_starts, summaries, g);
-  return (int)cudaGetLastError();
+  return lct::launch_overlapped(lct::compact_batch_kernel, (unsigned)total_blocks, lct::kThreads, 0,
+                                st, jobs, n_jobs, static_cast<uint8_t*>(arena_storage) + metadata,
+                                extra_starts, summaries, g);
 }
 
 }  // extern "C"

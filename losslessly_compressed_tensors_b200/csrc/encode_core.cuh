@@ -6,6 +6,14 @@
 
 namespace lct {
 
+// Unroll factor of the lane-phase loop (16 pairs per tile).
+#ifndef LCT_ENCODE_UNROLL
+#define LCT_ENCODE_UNROLL 16
+#endif
+#define LCT_ENCODE_PRAGMA(x) _Pragma(#x)
+#define LCT_ENCODE_UNROLL_(n) LCT_ENCODE_PRAGMA(unroll n)
+#define LCT_ENCODE_UNROLL_PRAGMA LCT_ENCODE_UNROLL_(LCT_ENCODE_UNROLL)
+
 // Lane phase of one tile.  Returns false once the lane has overflowed.
 template <bool kCheckValid>
 __device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8_t* tile_bytes,
@@ -13,7 +21,7 @@ __device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8
                                                  int lane32,
                                                  int step0, int valid, int budget_bits, int& pos,
                                                  uint32_t& lo, int& extra_start) {
-#pragma unroll
+  LCT_ENCODE_UNROLL_PRAGMA
   for (int p = 0; p < kTilePairs; ++p) {
     // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
     const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ (2 * p)));

@@ -128,6 +128,7 @@ center_and_tables_kernel(const void* __restrict__ src, int64_t n,
 __global__ void __launch_bounds__(kTableThreads)
 center_batch_kernel(const lct_encode_job* __restrict__ jobs, const int32_t* __restrict__ base_encode,
                     const int32_t* __restrict__ base_decode, int32_t* shifted_encode) {
+  cudaTriggerProgrammaticLaunchCompletion();  // the encoder behind waits where it needs the tables
   const lct_encode_job& job = jobs[blockIdx.x];
   center_and_tables<false>(job.src, job.logical_numel, base_encode, base_decode, job.center,
                            shifted_encode + 256 * (int64_t)blockIdx.x, job.shifted_decode);
@@ -140,12 +141,15 @@ shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __re
   write_shifted_tables(base_encode, base_decode, *center, shifted_encode, shifted_decode);
 }
 
-// Two symbols per lookup over 12 stream bits, in table-index space (so it is
-// valid for every center).  The second symbol is present only when both codes
-// are direct and fit in the 12 bits together.  The entry for stream window i
-// is stored at table_slot(i) (common.cuh).
+// Two symbols per lookup over 12 stream bits, one 4096-entry table per possible
+// center (CTA c serves center c - 128), symbols stored as raw exponent bytes so
+// a decoder copies the table of its tensor's center and uses it as it is.  The
+// second symbol is present only when both codes are direct and fit in the 12
+// bits together.  The entry for stream window i is stored at table_slot(i).
 __global__ void __launch_bounds__(kTableThreads)
 pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pair_table) {
+  const int center = (int)blockIdx.x - 128;
+  uint32_t* table = pair_table + (size_t)blockIdx.x * kPairEntries;
   for (int slot = threadIdx.x; slot < kPairEntries; slot += blockDim.x) {
     const int i = (int)table_window((uint32_t)slot);
     const int32_t first = decode[i & kFirstMask];
@@ -154,17 +158,18 @@ pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pai
       entry = kSlow | kEscape;
     } else {
       const uint32_t len0 = (uint32_t)first & 255u;
-      const uint32_t idx0 = ((uint32_t)first >> 8) & 255u;
-      entry = idx0 | (len0 << 24);
+      const uint32_t byte0 = index_to_exponent_byte(((uint32_t)first >> 8) & 255u, center);
+      entry = byte0 | (len0 << 24);
       const int32_t second = decode[(i >> len0) & kFirstMask];
       const uint32_t len1 = (uint32_t)second & 255u;
       if (second != 0 && len0 + len1 <= (uint32_t)kPairBits) {
-        entry |= (((uint32_t)second >> 8) & 255u) << 8 | (len0 + len1) << 16;
+        const uint32_t byte1 = index_to_exponent_byte(((uint32_t)second >> 8) & 255u, center);
+        entry |= byte1 << 8 | (len0 + len1) << 16;
       } else {
         entry |= kSlow | (len0 << 16);
       }
     }
-    pair_table[slot] = entry;
+    table[slot] = entry;
   }
 }
 
@@ -196,8 +201,8 @@ int lct_build_pair_table(const int32_t* decode_table, int rare_length, uint32_t*
                          void* stream) {
   if (decode_table == nullptr || pair_table == nullptr) return LCT_E_NULL_POINTER;
   if (rare_length < 0 || rare_length > 8) return LCT_E_BAD_ARGUMENT;
-  lct::pair_table_kernel<<<1, lct::kTableThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      decode_table, pair_table);
+  lct::pair_table_kernel<<<lct::kCenterValues, lct::kTableThreads, 0,
+                           static_cast<cudaStream_t>(stream)>>>(decode_table, pair_table);
   return (int)cudaGetLastError();
 }
 

@@ -24,20 +24,19 @@
 
 namespace lct {
 
-// The sample kernel walks bit streams with the codebook's two-symbol table read
-// straight from global memory (16 KB, L1-resident after the first touches) in
-// table-index space: only code lengths matter until the sampled symbol itself,
-// which alone is mapped to an exponent byte.  Shared memory holds one payload
-// column per thread: fixed_words + 3 rows of 256 words (the window refill may
-// read one row past the two zero rows when a stream uses its whole budget; the
-// refill pointer is clamped to that last row on every pair).
+// The sample kernel walks bit streams with the two-symbol table of the tensor's
+// center read straight from global memory (16 KB, L1-resident after the first
+// touches).  Shared memory holds one payload column per thread: fixed_words + 3
+// rows of 256 words (the window refill may read one row past the two zero rows
+// when a stream uses its whole budget; the refill pointer is clamped to that
+// last row on every pair).
 
-// One symbol of table-index space from an entry and the bits it was looked up with.
-__device__ __forceinline__ uint32_t index_of(uint32_t entry, uint32_t bits, int rare_length,
-                                             int* length) {
+// One symbol (exponent byte) from an entry and the bits it was looked up with.
+__device__ __forceinline__ uint32_t byte_of(uint32_t entry, uint32_t bits, int rare_length,
+                                            int center, int* length) {
   if (entry & kEscape) {
     *length = rare_length + 8;
-    return (bits >> rare_length) & 255u;
+    return index_to_exponent_byte((bits >> rare_length) & 255u, center);
   }
   *length = (int)((entry >> 24) & 15u);
   return entry & 255u;
@@ -65,32 +64,32 @@ __device__ __forceinline__ int tail_exponent_at(const OperandView& a, const Shap
   return -1;
 }
 
-// Table index of the symbol at `step` of the stream staged in `column`.
-__device__ __forceinline__ uint32_t walk_to(const OperandView& a, const Shape& g,
-                                            const uint32_t* column, int step) {
+// Exponent byte of the symbol at `step` of the stream staged in `column`.
+__device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, const Shape& g,
+                                            const uint32_t* column, int step, int center) {
   const uint32_t* last_row = column + (g.fixed_words + 2) * kLanes;
   BitReader r;
   r.open(column);
-  uint32_t first_index = 0, second_index = 0;
+  uint32_t first = 0, second = 0;
   for (int p = 0; p <= (step >> 1); ++p) {
     if (r.next_row > last_row) r.next_row = last_row;
     const uint32_t bits = r.peek0();
-    const uint32_t entry = __ldg(a.pair_table + table_slot(bits));
+    const uint32_t entry = __ldg(table + table_slot(bits));
     int consumed;
     if ((int32_t)entry < 0) {
       int l0, l1;
-      first_index = index_of(entry, bits, g.rare_length, &l0);
+      first = byte_of(entry, bits, g.rare_length, center, &l0);
       const uint32_t bits1 = r.peek(l0);
-      second_index = index_of(__ldg(a.pair_table + table_slot(bits1)), bits1, g.rare_length, &l1);
+      second = byte_of(__ldg(table + table_slot(bits1)), bits1, g.rare_length, center, &l1);
       consumed = l0 + l1;
     } else {
-      first_index = entry & 255u;
-      second_index = (entry >> 8) & 255u;
+      first = entry & 255u;
+      second = (entry >> 8) & 255u;
       consumed = (int)((entry >> 16) & 255u);
     }
     r.advance(consumed);
   }
-  return (step & 1) ? second_index : first_index;
+  return (step & 1) ? second : first;
 }
 
 // Result exponent bytes at the center-sample positions of the result tensor.
@@ -114,11 +113,6 @@ update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other,
   const int lane = (int)(pos & 255) ^ (int)(row & 254);
   const int64_t block = row / g.steps;
   const int step = (int)(row - block * g.steps);
-  // The 16 KB two-symbol table is read from global memory during the walk: pull
-  // its 128 lines into this SM's L1 now, one per thread, instead of missing on them
-  // one at a time inside the serial loop.
-  if (tid < kPairEntries / 32)
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(a.pair_table + tid * 32));
   const uint32_t* words = a.encoded + block * kLanes + lane;
   for (int w = 0; w < g.fixed_words; ++w)
     cp_async_4(column + w * kLanes, words + (int64_t)w * g.streams);
@@ -128,12 +122,12 @@ update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other,
   const uint32_t right = other[pos];
   const uint32_t side = a.side[block * (int64_t)g.block_symbols + (int64_t)step * kLanes + lane];
   const int center = *a.center;
+  const uint32_t* table = a.pair_table + (size_t)((center + 128) & 255) * kPairEntries;
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
   const int tail = tail_exponent_at(a, g, block, step, lane);
   cp_async_wait_all();
-  const uint32_t exponent =
-      tail >= 0 ? (uint32_t)tail : index_to_exponent_byte(walk_to(a, g, column, step), center);
+  const uint32_t exponent = tail >= 0 ? (uint32_t)tail : walk_to(table, g, column, step, center);
   const uint32_t left = (exponent << 7) | (side & 0x7Fu) | ((side & 0x80u) << 8);
   const uint32_t result = apply_op(left, right, spec.op, spec.alpha_is_one != 0,
                                    spec.beta_is_one != 0, alpha, beta);

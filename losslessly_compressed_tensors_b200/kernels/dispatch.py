@@ -83,10 +83,29 @@ class LaunchTrace:
 _trace: LaunchTrace | None = None
 
 
+try:  # raw handle of the current stream without building a torch.cuda.Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover - older/newer torch without the private helper
+    def _raw_stream(index: int) -> int:
+        return torch.cuda.current_stream(index).cuda_stream
+
+_functions: dict = {}
+
+
 def _call(name: str, device: torch.device, *args, launches: int = 1) -> None:
     """Launch entry point ``name`` (``launches`` kernels) on the current stream of ``device``."""
-    function = getattr(_lib.load(), name)
+    function = _functions.get(name)
+    if function is None:
+        function = _functions[name] = getattr(_lib.load(), name)
+    index = device.index
+    if index is None:
+        index = torch.cuda.current_device()
     trace = _trace
+    if trace is None and index == torch.cuda.current_device():
+        code = function(*args, _raw_stream(index))
+        if code:
+            _lib.check(code, name)
+        return
     with _on(device):
         stream = torch.cuda.current_stream(device)
         if trace is not None:
@@ -110,7 +129,8 @@ _pair_tables: dict = {}
 
 
 def pair_table_for(distribution, device: torch.device) -> torch.Tensor:
-    """Two-symbol decode table (uint32[4096] stored as int32) of a codebook on ``device``."""
+    """Two-symbol decode tables of a codebook on ``device``: one 4096-entry table per possible
+    center, uint32[256 * 4096] stored as int32 (4 MiB, built once)."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
@@ -118,7 +138,7 @@ def pair_table_for(distribution, device: torch.device) -> torch.Tensor:
     table = _pair_tables.get(key)
     if table is None:
         _, decode_table, rare_length = get_distribution_tables(distribution, device)
-        table = torch.empty(4096, dtype=torch.int32, device=device)
+        table = torch.empty(256 * 4096, dtype=torch.int32, device=device)
         _call(
             "lct_build_pair_table", device,
             decode_table.data_ptr(), rare_length, table.data_ptr())

@@ -140,7 +140,12 @@ class TensorBuffer:
             raise ValueError("allocation belongs to a different allocator")
         if allocation.descriptor.device != self.device:
             raise ValueError("allocation must be on the allocator device")
-        return tensor_buffer_free(self._storage, allocation.descriptor, self.max_free_regions)
+        if torch.compiler.is_compiling():
+            return tensor_buffer_free(self._storage, allocation.descriptor, self.max_free_regions)
+        # Eager mode: the same launch without the operator dispatcher in between.
+        status = torch.empty(1, dtype=torch.int32, device=self.device)
+        dispatch.buffer_free(self._storage, allocation.descriptor, status, self.max_free_regions)
+        return status
 
     def reset(self) -> None:
         """Forget every allocation; outstanding descriptors become stale (generation bump)."""
