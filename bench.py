@@ -248,6 +248,57 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
     }
 
 
+def arena_leg(batches: int = 3) -> dict:
+    """BASELINE configuration 3: ReLU activations 16384 x 4096 BF16 (about half exact zeros),
+    LAPLACE zero_prob 0.5 / SPARSE layout, ONE 64 MiB arena; batches of 16 live compressed
+    tensors: compress all, decode all, free all.  Four distinct inputs are cycled (the compressed
+    results all stay live).  Reports device time per tensor and the arena's high-water mark."""
+    from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType, NoiseLevel
+    from losslessly_compressed_tensors_b200.operations import compress, decompress
+    from losslessly_compressed_tensors_b200.tensor_buffer import (
+        TensorBuffer, _free_regions_snapshot, verify_buffer)
+
+    dist_cfg = Distribution(DistType.LAPLACE, param=1.0, zero_prob=0.5, noise_level=NoiseLevel.SPARSE)
+    capacity = 64 << 20
+    buffer = TensorBuffer(capacity)
+    inputs = []
+    for seed in range(4):
+        g = torch.Generator().manual_seed(2 + seed)
+        inputs.append(torch.randn(16384, 4096, generator=g).relu_().to(torch.bfloat16).cuda())
+    live_count, n = 16, inputs[0].numel()
+    enc, dec, exact, high_water, ratio = [], [], True, 0, 0.0
+    for batch in range(batches + 1):   # first batch is the warm-up
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        e[0].record()
+        live = [compress(inputs[i % 4], dist_cfg, buffer) for i in range(live_count)]
+        e[1].record()
+        free_bytes = sum(size for _, size in _free_regions_snapshot(buffer))   # host sync
+        high_water = max(high_water, capacity - free_bytes)
+        e[2].record()
+        outs = [decompress(c) for c in live]
+        e[3].record()
+        torch.cuda.synchronize()
+        for i in (0, 5, 10, 15):
+            exact &= torch.equal(outs[i].view(torch.int16), inputs[i % 4].view(torch.int16))
+        ratio = 2 * n / live[0].memory_size()
+        del outs
+        for c in live:
+            c.free()
+        verify_buffer(buffer)
+        if batch:
+            enc.append(e[0].elapsed_time(e[1]) / live_count)
+            dec.append(e[2].elapsed_time(e[3]) / live_count)
+    assert _free_regions_snapshot(buffer) == [(0, capacity)]
+    return {
+        "workload": "config3: 16 live 16384x4096 BF16 ReLU activations, LAPLACE zp 0.5 / SPARSE, "
+                    "one 64 MiB arena; back-to-back launches, L2 not flushed between tensors "
+                    "(each tensor is 128 MiB, larger than L2)",
+        "encode_ms_per_tensor": statistics.mean(enc), "decode_ms_per_tensor": statistics.mean(dec),
+        "encode_gbps": 2 * n / statistics.mean(enc) / 1e6, "decode_gbps": 2 * n / statistics.mean(dec) / 1e6,
+        "compression_ratio": ratio, "arena_high_water_bytes": high_water, "bit_exact": bool(exact),
+    }
+
+
 def update_leg(steps: int = 10, warmup: int = 3) -> dict:
     """BASELINE configuration 4: momentum tensors of 4096 x 4096 BF16 ~ N(0, 1e-3), GAUSSIAN /
     MEDIUM layout, shared arena; step = m <- 0.95 m + g on the compressed state (decode, fma,
@@ -374,6 +425,18 @@ def run_ours(args, rank: int, world: int, local: int):
     finally:
         encode_module.SINGLE_CALL_PIPELINE = True
     kernel_ms["lct_encode"] = statistics.mean(encode_trace.milliseconds("lct_encode"))
+    # Without a shared arena (the reference's other mode): exact-size private overflow tensors
+    # need the two totals on the host, i.e. one synchronisation inside every compress.
+    private_ms = []
+    for _ in range(max(3, min(args.steps, 10))):
+        flush.zero_()
+        a, b = event(), event()
+        a.record()
+        c = compress(x, dist_cfg, None)
+        b.record()
+        torch.cuda.synchronize()
+        private_ms.append(a.elapsed_time(b))
+        del c
 
     # End to end: host buffers in, host buffers out, copies inside the timed region.  Every step
     # copies its input from pinned host memory and its decoded result back to pinned host memory;
@@ -433,6 +496,7 @@ def run_ours(args, rank: int, world: int, local: int):
     del host_out, dev_in, dev_out, x, flush
     sharded = sharded_leg(rank, world) if not args.no_sharded else None
     update = update_leg() if (rank == 0 and not args.no_sharded) else None
+    arena = arena_leg() if (rank == 0 and not args.no_sharded) else None
     if rank != 0:
         return
     peak, peak_kind = peak_hbm_gbs()
@@ -465,6 +529,7 @@ def run_ours(args, rank: int, world: int, local: int):
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
         "gpu_launches": launches, "clocks": clocks, "sharded": sharded, "update": update,
+        "arena": arena, "encode_ms_without_arena": statistics.mean(private_ms),
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)

@@ -1,0 +1,218 @@
+"""Optimizers that keep their BF16 state compressed between steps.
+
+Drop-in for the three optimizers of the reference (``LCT/components/sparse_utils.py``:
+``SparseSGDM`` :13-66, ``SparseMuon`` :98-160, ``SparseAdamW`` :163-214): same constructor
+arguments, same update arithmetic in the same order, so a training script switches by
+changing the import.  What differs is underneath: every update of compressed state runs
+through this library's launch chains (``LCTTensor.mul_add_``: sample, center, decode -> fma
+-> re-encode, scan, tails behind ONE library call; ``add_comp_``: both operands compressed).
+
+The codec is lossless, so wherever the compressed and the dense variant of an optimizer run
+the same arithmetic on the dense values (Muon, AdamW) their trajectories are bit-identical;
+``tests/test_gpu_optimizers.py`` checks exactly that.
+
+Not taken over from the reference: the literal ``device="cuda"`` of its scalar tensors (the
+parameters' device is used) and the tracing compiler around the Muon update (it runs eagerly).
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable
+
+import torch
+from torch import Tensor
+
+from ..LCTensor import LCTTensor
+from ..operations import a_compA_add_B
+from ..tensor_buffer import TensorBuffer
+from .dist_configs import momentum_dist, momentum_first_dist
+
+
+def _scalar(value: float, like: Tensor) -> Tensor:
+    return torch.tensor([value], dtype=torch.float32, device=like.device)
+
+
+def _checked(params, *, matrices_only: bool = False) -> list:
+    params = list(params)
+    for p in params:
+        if not isinstance(p, (LCTTensor, Tensor)):
+            raise AssertionError("params must be a list of LCTTensor or Tensor")
+        if matrices_only and p.ndim < 2:
+            raise AssertionError("Muon requires matrix parameters")
+    return params
+
+
+class _Slot:
+    """One piece of optimizer state: dense, or compressed while it is not being updated."""
+
+    __slots__ = ("value",)
+
+    def __init__(self):
+        self.value: Tensor | LCTTensor | None = None
+
+    def take_dense(self, like: Tensor, dtype: torch.dtype | None = None) -> Tensor:
+        """The dense value (zeros shaped like ``like`` before the first step); a compressed one is
+        decoded and its arena region released."""
+        value, self.value = self.value, None
+        if value is None:
+            return torch.zeros_like(like, dtype=dtype)
+        if isinstance(value, LCTTensor):
+            return value.decompress_free()
+        return value
+
+    def put(self, dense: Tensor, *, compress: bool, buffer, dist) -> None:
+        if compress and dense.dtype == torch.bfloat16:
+            self.value = LCTTensor(dense, buffer=buffer, dist=dist)
+        else:
+            self.value = dense
+
+
+class _Base:
+    def _all_params(self):
+        return self.params
+
+    def zero_grad(self):
+        for p in self._all_params():
+            p.grad = None
+
+
+class SparseSGDM(_Base):
+    """``mom <- momentum * mom + g`` then ``p <- p - lr * mom``; with ``compressed`` the momentum
+    never exists densely after its first step: both lines are fused kernels on the compressed
+    state (fp32 fma, one rounding to BF16 each)."""
+
+    def __init__(self, params: Iterable[LCTTensor | Tensor], lr, momentum=0.9,
+                 buffer: TensorBuffer | None = None, compressed=True):
+        self.params = _checked(params)
+        self.lr, self.compressed, self.buffer = lr, compressed, buffer
+        anchor = self.params[0] if self.params else torch.empty(0, device="cuda")
+        self.momentum = torch.tensor(momentum, dtype=torch.float32, device=anchor.device)
+        self.neg_lr = _scalar(-lr, anchor)
+        self.momentums: list[Tensor | LCTTensor | None] = [None] * len(self.params)
+
+    def _advance_momentum(self, index: int, grad: Tensor):
+        state = self.momentums[index]
+        if state is None:                      # first step: the gradient itself
+            state = LCTTensor(grad, buffer=self.buffer, dist=momentum_dist) if self.compressed else grad
+            self.momentums[index] = state
+        elif self.compressed:
+            state.mul_add_(self.momentum, grad)
+        else:
+            torch.add(grad, state, alpha=0.9, out=state)   # the reference's dense branch (literal 0.9)
+        return state
+
+    @torch.no_grad()
+    def step(self):
+        for index, p in enumerate(self.params):
+            state = self._advance_momentum(index, p.grad)
+            if not self.compressed:
+                p.add_(state * self.neg_lr)
+            elif isinstance(p, LCTTensor):
+                p.add_comp_(state, self.neg_lr)
+            else:   # decode + fma in one kernel, written back into the same parameter storage
+                p.copy_(a_compA_add_B(state.x, self.neg_lr, p))
+
+
+def zeropower_via_newtonschulz5(G: Tensor, ns_iters: int) -> Tensor:
+    """Quintic Newton-Schulz iteration towards the orthogonal polar factor, in BF16, with the
+    coefficients (2, -1.5, 0.5) the reference uses (``sparse_utils.py:69-84``)."""
+    assert G.ndim >= 2
+    tall = G.size(-2) > G.size(-1)
+    X = G.bfloat16().mT if tall else G.bfloat16()
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(ns_iters):
+        gram = X @ X.mT
+        X = 2 * X + (-1.5 * gram + 0.5 * gram @ gram) @ X
+    return X.mT if tall else X
+
+
+def muon_update(grad: Tensor, momentum: Tensor, mu=0.95, nesterov=True, ns_iters=5) -> Tensor:
+    """In-place momentum step and the orthogonalised update (``sparse_utils.py:87-95``)."""
+    momentum.lerp_(grad.to(momentum.dtype), 1 - mu)
+    direction = grad.lerp_(momentum.to(grad.dtype), mu) if nesterov else momentum
+    update = zeropower_via_newtonschulz5(direction, ns_iters)
+    update *= max(1, grad.size(-2) / grad.size(-1)) ** 0.5
+    return update
+
+
+class SparseMuon(_Base):
+    """Muon with BF16 momentum that is decoded, updated densely and re-compressed every step
+    (the first step with the many-zeros codebook when ``zero_first_step``)."""
+
+    def __init__(self, params: Iterable[LCTTensor | Tensor], lr=0.02, weight_decay=0, mu=0.95,
+                 buffer: TensorBuffer | None = None, compressed=True, distribution=None,
+                 zero_first_step=False, ns_iters=5):
+        self.params = _checked(params, matrices_only=True)
+        self.lr, self.weight_decay, self.mu, self.ns_iters = lr, weight_decay, mu, ns_iters
+        self.buffer, self.compressed = buffer, compressed
+        self.distribution = distribution or momentum_dist
+        self.first_step = zero_first_step
+        anchor = self.params[0] if self.params else torch.empty(0, device="cuda")
+        self.decay = _scalar(1 - lr * weight_decay, anchor)
+        self.neg_lr = _scalar(-lr, anchor)
+        self._slots = [_Slot() for _ in self.params]
+
+    @property
+    def momentums(self):
+        return [slot.value for slot in self._slots]
+
+    @torch.no_grad()
+    def step(self):
+        for slot, p in zip(self._slots, self.params):
+            grad = p.grad
+            if grad is None:
+                continue
+            momentum = slot.take_dense(grad, torch.bfloat16)
+            update = muon_update(grad, momentum, mu=self.mu, ns_iters=self.ns_iters)
+            slot.put(momentum, compress=self.compressed, buffer=self.buffer,
+                     dist=momentum_first_dist if self.first_step else self.distribution)
+            del momentum
+            if isinstance(p, LCTTensor):   # decay and update in one fused pass over the weights
+                p.mul_add_(self.decay, update, beta=self.neg_lr, alpha_is_one=self.weight_decay == 0)
+            else:
+                p.mul_(1 - self.lr * self.weight_decay)
+                p.add_(update, alpha=-self.lr)
+        self.first_step = False
+
+
+class SparseAdamW(_Base):
+    """AdamW whose BF16 moments (and compressed matrix weights) are stored losslessly
+    compressed; FP32 parameters and their moments stay dense.  Both modes run the same dense
+    arithmetic on the decoded values."""
+
+    def __init__(self, param_groups, *, betas=(0.8, 0.95), eps=1e-10, weight_decay=0,
+                 compressed=True, buffer=None):
+        self.param_groups = [dict(group, params=list(group["params"])) for group in param_groups]
+        self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
+        self.compressed, self.buffer = compressed, buffer
+        self.state: dict = {}
+
+    def _all_params(self):
+        return [p for group in self.param_groups for p in group["params"]]
+
+    def _update_one(self, p, grad: Tensor, lr: float) -> None:
+        beta1, beta2 = self.betas
+        state = self.state.setdefault(p, {"step": 0, "exp_avg": _Slot(), "exp_avg_sq": _Slot()})
+        state["step"] += 1
+        t = state["step"]
+        avg = state["exp_avg"].take_dense(grad)
+        square_avg = state["exp_avg_sq"].take_dense(grad)
+        avg.lerp_(grad, 1 - beta1)
+        square_avg.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
+        denom = square_avg.sqrt().div_(math.sqrt(1 - beta2 ** t)).add_(self.eps)
+        weight = p.decompress() if isinstance(p, LCTTensor) else p
+        weight.mul_(1 - lr * self.weight_decay)
+        weight.addcdiv_(avg, denom, value=-lr / (1 - beta1 ** t))
+        if isinstance(p, LCTTensor):
+            previous = p.x
+            p.x = LCTTensor(weight, buffer=previous.buffer, dist=previous.distribution).x
+            previous.free()
+        for key, dense in (("exp_avg", avg), ("exp_avg_sq", square_avg)):
+            state[key].put(dense, compress=self.compressed, buffer=self.buffer, dist=momentum_dist)
+
+    @torch.no_grad()
+    def step(self):
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is not None:
+                    self._update_one(p, p.grad, group["lr"])

@@ -31,20 +31,29 @@ namespace lct {
 __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& g,
                                              uint16_t* __restrict__ out, int64_t block) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
+#ifdef LCT_PAYLOAD_GLOBAL
+  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
+  prepare_block(sh, nullptr, a, g, block);
+#else
+  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
+  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
   prepare_block(sh, payload, a, g, block);
+#endif
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
+#ifdef LCT_PAYLOAD_GLOBAL
+  GlobalBitReader reader;
+  reader.open(a.encoded + block * kLanes + tid, g.streams, g.fixed_words);
+#else
   BitReader reader;
-  reader.open(payload + tid);
-  const uint32_t* last_row = payload + tid + (g.fixed_words + 2) * kLanes;
+  reader.open(payload + tid, g.fixed_words);
+#endif
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
   uint16_t* tile = sh.tile[warp];
 
@@ -59,8 +68,7 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
       side_regs[u][0] = __ldcs(reinterpret_cast<const uint2*>(s));
       side_regs[u][1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
     }
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
-                     last_row);
+    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -88,7 +96,10 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
   }
 }
 
-__global__ void __launch_bounds__(kThreads)
+#ifndef LCT_DECODE_MIN_CTAS
+#define LCT_DECODE_MIN_CTAS 4
+#endif
+__global__ void __launch_bounds__(kThreads, LCT_DECODE_MIN_CTAS)
 decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
   decode_block(a, g, out, blockIdx.x);
 }
@@ -122,7 +133,7 @@ __device__ __forceinline__ int find_job(const Job* jobs, int n_jobs, int64_t blo
   return lo;
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, LCT_DECODE_MIN_CTAS)
 decode_batch_kernel(const lct_decode_job* __restrict__ jobs, int n_jobs, Shape common) {
   const int64_t block = blockIdx.x;
   const lct_decode_job& job = jobs[find_job(jobs, n_jobs, block)];
@@ -165,10 +176,8 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
   const int a_coded = min(valid, a_tail_from);
   const uint8_t* a_tail = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
   BitReader reader_a, reader_b;
-  reader_a.open(payload + tid);
-  reader_b.open(payload_b + tid);
-  const uint32_t* last_row_a = payload + tid + (g.fixed_words + 2) * kLanes;
-  const uint32_t* last_row_b = payload_b + tid + (g.fixed_words + 2) * kLanes;
+  reader_a.open(payload + tid, g.fixed_words);
+  reader_b.open(payload_b + tid, g.fixed_words);
   int b_tail_from = g.steps, b_coded = 0;
   const uint8_t* b_tail = nullptr;
   if (kDual) {
@@ -181,10 +190,10 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
     decode_tile_rows(reader_a, sh, tile, lane32, step0, a_coded, a_tail_from, a_tail,
-                     g.rare_length, last_row_a);
+                     g.rare_length);
     if (kDual)
       decode_tile_rows(reader_b, sh_b, tile_b, lane32, step0, b_coded, b_tail_from, b_tail,
-                       g.rare_length, last_row_b);
+                       g.rare_length);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -219,6 +228,16 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
 
 }  // namespace lct
 
+// Shared memory of the plain decoders.
+static size_t decode_shared_bytes(int fixed_words) {
+#ifdef LCT_PAYLOAD_GLOBAL
+  (void)fixed_words;
+  return sizeof(lct::DecodeShared);
+#else
+  return lct::operand_shared_bytes(fixed_words);
+#endif
+}
+
 extern "C" {
 
 int lct_decode(const lct_operand* a, int16_t* out, int64_t size, int64_t logical_numel,
@@ -230,7 +249,7 @@ int lct_decode(const lct_operand* a, int16_t* out, int64_t size, int64_t logical
   if ((rc = lct::view_of(a, &va)) != 0) return rc;
   if (out == nullptr) return LCT_E_NULL_POINTER;
   if (!lct::aligned16(out)) return LCT_E_ALIGNMENT;
-  const size_t shared = lct::operand_shared_bytes(fixed_words);
+  const size_t shared = decode_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::decode_kernel, shared)) != 0) return rc;
   lct::decode_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared,
                        static_cast<cudaStream_t>(stream)>>>(va, g, reinterpret_cast<uint16_t*>(out));
@@ -245,7 +264,7 @@ int lct_decode_batch(const lct_decode_job* jobs, int n_jobs, int64_t total_block
   int rc = lct::check_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words,
                             rare_length, &g);
   if (rc) return rc;
-  const size_t shared = lct::operand_shared_bytes(fixed_words);
+  const size_t shared = decode_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::decode_batch_kernel, shared)) != 0) return rc;
   lct::decode_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, shared,
                              static_cast<cudaStream_t>(stream)>>>(jobs, n_jobs, g);

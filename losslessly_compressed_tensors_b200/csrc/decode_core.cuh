@@ -77,15 +77,23 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // the lookup's dependency chain.
 struct BitReader {
   const uint32_t* next_row;  // image word that enters the window at the next refill
+  const uint32_t* last_row;  // the image's second zero row
   uint32_t cur, n1, n2;
   int shift;                 // 0..31 between pairs
 
-  __device__ __forceinline__ void open(const uint32_t* column) {
+  // `column`: this lane's column of an image of fixed_words + 2 rows.
+  __device__ __forceinline__ void open(const uint32_t* column, int fixed_words) {
     cur = column[0];
     n1 = column[kLanes];
     n2 = column[2 * kLanes];
     next_row = column + 3 * kLanes;
+    last_row = column + (fixed_words + 1) * kLanes;
     shift = 0;
+  }
+  // A well-formed stream never refills past the image's second zero row; a
+  // corrupt one is pulled back here, once per tile (at most 16 refills each).
+  __device__ __forceinline__ void tile_start() {
+    if (next_row > last_row) next_row = last_row;
   }
   // 32 stream bits starting `extra` bits after the position (shift + extra < 64).
   __device__ __forceinline__ uint32_t peek(int extra) const {
@@ -102,6 +110,51 @@ struct BitReader {
       n1 = n2;
       n2 = *next_row;
       next_row += kLanes;
+    }
+  }
+};
+
+// The same window fed straight from the payload in global memory (through L1):
+// no shared image, so a CTA needs only its tables and tiles.  Word w of the
+// lane's stream is `stride` words after word w - 1.  Every refill clamps its
+// row to the last word of the stream, so a corrupt stream re-reads that word
+// instead of leaving the payload.
+struct GlobalBitReader {
+  const uint32_t* base;
+  int64_t stride;
+  int row, last;
+  uint32_t cur, n1, n2;
+  int shift;
+
+  __device__ __forceinline__ void open(const uint32_t* column, int64_t stride_words, int fixed_words) {
+    base = column;
+    stride = stride_words;
+    last = fixed_words - 1;  // fixed_words >= 2
+    cur = __ldg(column);
+    n1 = __ldg(column + stride);
+    n2 = __ldg(column + (int64_t)min(2, last) * stride);
+    row = min(3, last);
+    shift = 0;
+  }
+  __device__ __forceinline__ void tile_start() {
+#ifdef LCT_PAYLOAD_PREFETCH
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(base + (int64_t)min(row + LCT_PAYLOAD_PREFETCH, last) * stride));
+#endif
+  }
+  __device__ __forceinline__ uint32_t peek(int extra) const {
+    const int s = shift + extra;
+    const bool far = s >= 32;
+    return __funnelshift_r(far ? n1 : cur, far ? n2 : n1, s);
+  }
+  __device__ __forceinline__ uint32_t peek0() const { return __funnelshift_r(cur, n1, shift); }
+  __device__ __forceinline__ void advance(int bits) {
+    shift += bits;
+    if (shift >= 32) {
+      shift -= 32;
+      cur = n1;
+      n1 = n2;
+      n2 = __ldg(base + (int64_t)row * stride);
+      row = min(row + 1, last);
     }
   }
 };
@@ -130,7 +183,8 @@ __device__ __forceinline__ uint32_t symbol_of(uint32_t entry, uint32_t bits, con
 // Pair whose table entry is not "two direct symbols": take the first symbol
 // from the entry already in hand, look the second one up on its own.
 // Returns the pair in table-entry form (bytes: first, second, bits consumed).
-__device__ __forceinline__ uint32_t slow_pair(const BitReader& r, uint32_t entry, uint32_t bits,
+template <typename Reader>
+__device__ __forceinline__ uint32_t slow_pair(const Reader& r, uint32_t entry, uint32_t bits,
                                               const DecodeShared& sh, int rare_length) {
   int l0, l1;
   const uint32_t e0 = symbol_of(entry, bits, sh, rare_length, &l0);
@@ -142,13 +196,12 @@ __device__ __forceinline__ uint32_t slow_pair(const BitReader& r, uint32_t entry
 // Lane phase for one tile.  `coded` = number of leading steps of this lane that
 // are in the bit stream (its overflow start or its valid length, whichever is
 // first); steps from `tail_from` on come from the raw tail.
-__device__ __forceinline__ void decode_tile_rows(BitReader& r, const DecodeShared& sh,
+template <typename Reader>
+__device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& sh,
                                                  uint16_t* tile, int lane32, int step0, int coded,
                                                  int tail_from, const uint8_t* tail_bytes,
-                                                 int rare_length, const uint32_t* last_row) {
-  // A well-formed stream never refills past the image's second zero row; a
-  // corrupt one is pulled back here, once per tile (at most 16 refills each).
-  if (r.next_row > last_row) r.next_row = last_row;
+                                                 int rare_length) {
+  r.tile_start();
   // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
   if (__all_sync(0xFFFFFFFFu, step0 + kTileRows <= coded)) {
     LCT_UNROLL(LCT_DECODE_UNROLL)
@@ -195,14 +248,16 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
                                               const OperandView& a, const Shape& g, int64_t block,
                                               Extra before_barrier = Extra()) {
   const int tid = threadIdx.x;
-  // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
-  const uint32_t* rows = a.encoded + block * kLanes;
-  for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
-    const int w = i >> 6, c = (i & 63) * 4;
-    cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
+  if (payload != nullptr) {  // nullptr: the caller reads the payload from global memory
+    // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
+    const uint32_t* rows = a.encoded + block * kLanes;
+    for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
+      const int w = i >> 6, c = (i & 63) * 4;
+      cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
+    }
+    payload[g.fixed_words * kLanes + tid] = 0u;
+    payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
   }
-  payload[g.fixed_words * kLanes + tid] = 0u;
-  payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
 
   // The codebook's table for this tensor's center, ready to use (symbols are exponent bytes).
   const int center = *a.center;

@@ -67,12 +67,11 @@ __device__ __forceinline__ int tail_exponent_at(const OperandView& a, const Shap
 // Exponent byte of the symbol at `step` of the stream staged in `column`.
 __device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, const Shape& g,
                                             const uint32_t* column, int step, int center) {
-  const uint32_t* last_row = column + (g.fixed_words + 2) * kLanes;
   BitReader r;
-  r.open(column);
+  r.open(column, g.fixed_words + 1);  // the column has one more (zero) row than a decoder image
   uint32_t first = 0, second = 0;
   for (int p = 0; p <= (step >> 1); ++p) {
-    if (r.next_row > last_row) r.next_row = last_row;
+    r.tile_start();
     const uint32_t bits = r.peek0();
     const uint32_t entry = __ldg(table + table_slot(bits));
     int consumed;
@@ -184,8 +183,7 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
   BitReader reader;
-  reader.open(payload + tid);
-  const uint32_t* last_row = payload + tid + (g.fixed_words + 2) * kLanes;
+  reader.open(payload + tid, g.fixed_words);
   uint16_t* tile = sh.tile[warp];
   const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
   uint32_t* out_column = encoded_out + block * kLanes + tid;
@@ -195,8 +193,7 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   bool open = true;
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
-                     last_row);
+    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length);
     __syncwarp();
     // ---- row side: A (op) B, new side bytes out, new exponents back into the tile ----
 #pragma unroll
