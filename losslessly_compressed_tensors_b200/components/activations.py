@@ -1,0 +1,113 @@
+"""Activations kept compressed between forward and backward.
+
+The reference does this inside hand-written ``autograd.Function`` layers of its nanoGPT
+example (``LCT/components/layers.py:22-305``, ``mlps.py``): each layer compresses the tensor
+it needs for backward into one shared arena (``compress(x, distribution=act_dist,
+buffer=buffer)`` when ``x.numel() >= min_elements``), and its backward decodes it and releases
+the arena region.  Here the same ownership pattern is offered for ANY module, in two forms:
+
+* ``ActivationCache`` - the explicit form: ``handle = cache.store(x)`` in a forward,
+  ``x = handle.load()`` in the backward (decode, then the region goes back to the arena);
+* ``compressed_saved_tensors(...)`` - a context manager over autograd's saved-tensor hooks that
+  applies the cache to every eligible tensor the wrapped forward saves.
+
+Eligible: CUDA, bfloat16, at least ``min_elements`` elements, not a parameter (leaf that
+requires grad).  Everything else is kept as it is.  The codec is lossless, so gradients are
+bit-identical with and without the cache.
+"""
+from __future__ import annotations
+
+import contextlib
+
+import torch
+from torch import Tensor
+
+from ..LCTensor import LCTTensor
+from ..comp_format import Distribution
+from ..operations import compress, decompress
+from ..tensor_buffer import TensorBuffer
+from .dist_configs import act_dist, weight_dist
+
+
+class _Handle:
+    """One cached activation.  ``load`` may be called more than once (retained graphs); the
+    compressed form is released at the first call and the dense tensor is kept from then on."""
+
+    __slots__ = ("_compressed", "_dense")
+
+    def __init__(self, compressed=None, dense=None):
+        self._compressed, self._dense = compressed, dense
+
+    @property
+    def is_compressed(self) -> bool:
+        return self._compressed is not None
+
+    def load(self) -> Tensor:
+        if self._compressed is not None:
+            self._dense = decompress(self._compressed)
+            self._compressed.free()
+            self._compressed = None
+        return self._dense
+
+    def discard(self) -> None:
+        """Release without decoding (a forward whose backward never runs)."""
+        if self._compressed is not None:
+            self._compressed.free()
+            self._compressed = None
+        self._dense = None
+
+
+class ActivationCache:
+    """Stores eligible tensors compressed in ``buffer`` (or in private tensors without one)."""
+
+    def __init__(self, buffer: TensorBuffer | None = None, distribution: Distribution | None = None,
+                 min_elements: int = 65536):
+        self.buffer = buffer
+        self.distribution = distribution or act_dist
+        self.min_elements = int(min_elements)
+        self.stored = 0           # tensors compressed so far
+        self.dense_bytes = 0      # their BF16 bytes
+        self.compressed_bytes = 0
+
+    def eligible(self, tensor: Tensor) -> bool:
+        return (tensor.device.type == "cuda" and tensor.dtype == torch.bfloat16
+                and tensor.numel() >= self.min_elements
+                and not (tensor.is_leaf and tensor.requires_grad)
+                and not isinstance(tensor, LCTTensor))
+
+    def store(self, tensor: Tensor, *, track_sizes: bool = False) -> _Handle:
+        if not self.eligible(tensor):
+            return _Handle(dense=tensor)
+        compressed = compress(tensor.detach(), distribution=self.distribution, buffer=self.buffer)
+        self.stored += 1
+        if track_sizes:   # memory_size() reads device counters: a host synchronisation
+            self.dense_bytes += tensor.numel() * 2
+            self.compressed_bytes += compressed.memory_size()
+        return _Handle(compressed=compressed)
+
+
+@contextlib.contextmanager
+def compressed_saved_tensors(buffer: TensorBuffer | None = None,
+                             distribution: Distribution | None = None, min_elements: int = 65536,
+                             cache: ActivationCache | None = None):
+    """Within the block, tensors that autograd saves for backward go through an
+    ``ActivationCache`` (yielded, for its counters)."""
+    cache = cache or ActivationCache(buffer, distribution, min_elements)
+    with torch.autograd.graph.saved_tensors_hooks(cache.store, _Handle.load):
+        yield cache
+
+
+def dense_weight(weight: Tensor) -> Tensor:
+    """The BF16 values of a weight that may be stored compressed (``layers.py:12-13``)."""
+    return weight.decompress() if isinstance(weight, LCTTensor) else weight
+
+
+def compress_weight(module: torch.nn.Module, buffer: TensorBuffer | None = None,
+                    distribution: Distribution | None = None) -> None:
+    """Replace ``module.weight`` (BF16) by its compressed form, once, after initialisation and
+    checkpoint loading (``layers.py:289-295``)."""
+    if isinstance(module.weight, LCTTensor):
+        return
+    packed = LCTTensor(module.weight.detach(), buffer=buffer, dist=distribution or weight_dist)
+    del module._parameters["weight"]
+    module.weight = packed

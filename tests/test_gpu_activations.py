@@ -1,0 +1,86 @@
+"""Compressed activation cache (GPU): lossless, so gradients must not change by one bit, and
+every arena region must be back when the backward pass is over."""
+import pytest
+import torch
+
+from losslessly_compressed_tensors_b200.LCTensor import LCTTensor
+from losslessly_compressed_tensors_b200.components.activations import (
+    ActivationCache, compress_weight, compressed_saved_tensors, dense_weight,
+)
+from losslessly_compressed_tensors_b200.components.dist_configs import act_relu_dist
+from losslessly_compressed_tensors_b200.tensor_buffer import (
+    TensorBuffer, _free_regions_snapshot, verify_buffer,
+)
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(seed):
+    torch.manual_seed(seed)
+    model = torch.nn.Sequential(
+        torch.nn.Linear(256, 1024), torch.nn.ReLU(), torch.nn.Linear(1024, 1024), torch.nn.GELU(),
+        torch.nn.Linear(1024, 64)).cuda().to(torch.bfloat16)
+    return model
+
+
+def _run(model, x, context):
+    for p in model.parameters():
+        p.grad = None
+    x = x.clone().requires_grad_(True)
+    with context:
+        loss = model(x).float().square().mean()
+    loss.backward()
+    return [x.grad.clone()] + [p.grad.clone() for p in model.parameters()], loss.detach()
+
+
+def test_saved_tensor_hooks_keep_gradients_bit_identical_and_release_the_arena():
+    import contextlib
+    model = _model(0)
+    x = torch.randn(512, 256, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)
+                    ).to(torch.bfloat16)
+    want, want_loss = _run(model, x, contextlib.nullcontext())
+    buffer = TensorBuffer(4 << 20)
+    cache = ActivationCache(buffer, min_elements=65536)
+    got, got_loss = _run(model, x, compressed_saved_tensors(cache=cache))
+    assert cache.stored >= 3          # x (512x256) and the 512x1024 activations
+    assert torch.equal(got_loss, want_loss)
+    for g, w in zip(got, want):
+        assert torch.equal(g.view(torch.int16), w.view(torch.int16))
+    verify_buffer(buffer)
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
+
+
+def test_small_fp32_and_parameter_tensors_are_left_alone():
+    cache = ActivationCache(None, min_elements=1000)
+    small = torch.zeros(10, dtype=torch.bfloat16, device="cuda")
+    single = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    parameter = torch.nn.Parameter(torch.zeros(4096, dtype=torch.bfloat16, device="cuda"))
+    for t in (small, single, parameter):
+        handle = cache.store(t)
+        assert not handle.is_compressed and handle.load() is t
+    assert cache.stored == 0
+
+
+def test_explicit_store_load_discard_with_a_sparse_codebook():
+    buffer = TensorBuffer(1 << 20)
+    cache = ActivationCache(buffer, act_relu_dist, min_elements=1)
+    x = torch.randn(300, 700, device="cuda").relu().to(torch.bfloat16)
+    handle = cache.store(x, track_sizes=True)
+    assert handle.is_compressed and cache.compressed_bytes < cache.dense_bytes
+    y = handle.load()
+    assert torch.equal(y.view(torch.int16), x.view(torch.int16))
+    assert handle.load() is y and not handle.is_compressed   # second load: the kept dense tensor
+    other = cache.store(x)
+    other.discard()
+    verify_buffer(buffer)
+    assert _free_regions_snapshot(buffer) == [(0, 1 << 20)]
+
+
+def test_compress_weight_replaces_the_parameter():
+    layer = torch.nn.Linear(512, 256).cuda().to(torch.bfloat16)
+    before = layer.weight.detach().clone()
+    compress_weight(layer)
+    assert isinstance(layer.weight, LCTTensor) and "weight" not in layer._parameters
+    assert torch.equal(dense_weight(layer.weight).view(torch.int16), before.view(torch.int16))
+    compress_weight(layer)   # idempotent
+    assert dense_weight(before) is before
