@@ -34,26 +34,16 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
-#ifdef LCT_PAYLOAD_GLOBAL
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw);
-  prepare_block(sh, nullptr, a, g, block);
-#else
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
   prepare_block(sh, payload, a, g, block);
-#endif
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-#ifdef LCT_PAYLOAD_GLOBAL
-  GlobalBitReader reader;
-  reader.open(a.encoded + block * kLanes + tid, g.streams, g.fixed_words);
-#else
   BitReader reader;
   reader.open(payload + tid, g.fixed_words);
-#endif
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
   uint16_t* tile = sh.tile[warp];
 
@@ -228,16 +218,6 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
 
 }  // namespace lct
 
-// Shared memory of the plain decoders.
-static size_t decode_shared_bytes(int fixed_words) {
-#ifdef LCT_PAYLOAD_GLOBAL
-  (void)fixed_words;
-  return sizeof(lct::DecodeShared);
-#else
-  return lct::operand_shared_bytes(fixed_words);
-#endif
-}
-
 extern "C" {
 
 int lct_decode(const lct_operand* a, int16_t* out, int64_t size, int64_t logical_numel,
@@ -249,7 +229,7 @@ int lct_decode(const lct_operand* a, int16_t* out, int64_t size, int64_t logical
   if ((rc = lct::view_of(a, &va)) != 0) return rc;
   if (out == nullptr) return LCT_E_NULL_POINTER;
   if (!lct::aligned16(out)) return LCT_E_ALIGNMENT;
-  const size_t shared = decode_shared_bytes(fixed_words);
+  const size_t shared = lct::operand_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::decode_kernel, shared)) != 0) return rc;
   lct::decode_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared,
                        static_cast<cudaStream_t>(stream)>>>(va, g, reinterpret_cast<uint16_t*>(out));
@@ -264,7 +244,7 @@ int lct_decode_batch(const lct_decode_job* jobs, int n_jobs, int64_t total_block
   int rc = lct::check_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words,
                             rare_length, &g);
   if (rc) return rc;
-  const size_t shared = decode_shared_bytes(fixed_words);
+  const size_t shared = lct::operand_shared_bytes(fixed_words);
   if ((rc = lct::opt_in_shared(lct::decode_batch_kernel, shared)) != 0) return rc;
   lct::decode_batch_kernel<<<(unsigned)total_blocks, lct::kThreads, shared,
                              static_cast<cudaStream_t>(stream)>>>(jobs, n_jobs, g);

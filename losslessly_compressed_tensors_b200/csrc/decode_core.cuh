@@ -114,51 +114,6 @@ struct BitReader {
   }
 };
 
-// The same window fed straight from the payload in global memory (through L1):
-// no shared image, so a CTA needs only its tables and tiles.  Word w of the
-// lane's stream is `stride` words after word w - 1.  Every refill clamps its
-// row to the last word of the stream, so a corrupt stream re-reads that word
-// instead of leaving the payload.
-struct GlobalBitReader {
-  const uint32_t* base;
-  int64_t stride;
-  int row, last;
-  uint32_t cur, n1, n2;
-  int shift;
-
-  __device__ __forceinline__ void open(const uint32_t* column, int64_t stride_words, int fixed_words) {
-    base = column;
-    stride = stride_words;
-    last = fixed_words - 1;  // fixed_words >= 2
-    cur = __ldg(column);
-    n1 = __ldg(column + stride);
-    n2 = __ldg(column + (int64_t)min(2, last) * stride);
-    row = min(3, last);
-    shift = 0;
-  }
-  __device__ __forceinline__ void tile_start() {
-#ifdef LCT_PAYLOAD_PREFETCH
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(base + (int64_t)min(row + LCT_PAYLOAD_PREFETCH, last) * stride));
-#endif
-  }
-  __device__ __forceinline__ uint32_t peek(int extra) const {
-    const int s = shift + extra;
-    const bool far = s >= 32;
-    return __funnelshift_r(far ? n1 : cur, far ? n2 : n1, s);
-  }
-  __device__ __forceinline__ uint32_t peek0() const { return __funnelshift_r(cur, n1, shift); }
-  __device__ __forceinline__ void advance(int bits) {
-    shift += bits;
-    if (shift >= 32) {
-      shift -= 32;
-      cur = n1;
-      n1 = n2;
-      n2 = __ldg(base + (int64_t)row * stride);
-      row = min(row + 1, last);
-    }
-  }
-};
-
 // Unroll factor of the lane-phase loop (16 pairs per tile).  Measured on B200
 // (64 Mi elements): 16 -> 81.9 us, 8 -> 80.8, 4 -> 80.0, 2 -> 80.9; the fully
 // unrolled loop pays in instruction-cache misses for what it saves in address
@@ -248,16 +203,14 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
                                               const OperandView& a, const Shape& g, int64_t block,
                                               Extra before_barrier = Extra()) {
   const int tid = threadIdx.x;
-  if (payload != nullptr) {  // nullptr: the caller reads the payload from global memory
-    // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
-    const uint32_t* rows = a.encoded + block * kLanes;
-    for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
-      const int w = i >> 6, c = (i & 63) * 4;
-      cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
-    }
-    payload[g.fixed_words * kLanes + tid] = 0u;
-    payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
+  // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
+  const uint32_t* rows = a.encoded + block * kLanes;
+  for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
+    const int w = i >> 6, c = (i & 63) * 4;
+    cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
   }
+  payload[g.fixed_words * kLanes + tid] = 0u;
+  payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
 
   // The codebook's table for this tensor's center, ready to use (symbols are exponent bytes).
   const int center = *a.center;

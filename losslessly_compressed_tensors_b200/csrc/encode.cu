@@ -112,9 +112,6 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   const int64_t block_base = block * (int64_t)g.block_symbols;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
 
-  for (int w = 0; w < g.fixed_words; ++w) payload[w * kLanes + tid] = 0u;
-  if (block == 0 && tid < 4) encoded[g.streams * g.fixed_words + tid] = 0u;  // trailing pad words
-
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
   const int budget_bits = g.fixed_words * 32;
   uint16_t* tile = sh.tile[warp];
@@ -143,6 +140,9 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   cudaGridDependencySynchronize();
   {
     const uint32_t packed = (uint32_t)shifted_encode[tid];
+    // Clearing the payload image hides the latency of the table load.
+    for (int w = 0; w < g.fixed_words; ++w) payload[w * kLanes + tid] = 0u;
+    if (block == 0 && tid < 4) encoded[g.streams * g.fixed_words + tid] = 0u;  // trailing pad words
     sh.table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
   }
   __syncthreads();
