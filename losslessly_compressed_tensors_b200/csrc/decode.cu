@@ -4,16 +4,17 @@
 // every warp runs on its own (see common.cuh: a warp's 32 lanes own one
 // 64-byte segment of every row).
 //
-// Prologue: the block's payload tile (fixed_words rows of 256 words) is copied
-// into shared memory with cp.async while the codebook's two-symbol table is
-// remapped to this tensor's center and the block's overflow map is expanded.
+// Prologue: the block's payload tile (fixed_words rows of 256 words) and the
+// 16 KB two-symbol table of this tensor's center are copied into shared memory
+// with cp.async while the block's overflow map is expanded.
 //
 // Per 32-row tile, per warp:
-//   lane phase - thread = lane: reads the two payload words under its absolute
-//                bit position from shared memory, funnel-shifts, looks 12 bits
-//                up in the two-symbol table, advances.  No per-lane refill
-//                branch; the only divergent path is the rare "not two direct
-//                symbols" entry, decoded one symbol at a time;
+//   lane phase - thread = lane: a 96-bit register window over the lane's column
+//                of the payload image; 12 bits of it index the two-symbol table
+//                (two exponent bytes + bits consumed per lookup); the window is
+//                refilled from the image one word at a time, off the lookup's
+//                dependency chain.  The only divergent path is the rare "not two
+//                direct symbols" entry, decoded one symbol at a time;
 //   row phase  - thread = 8 columns of a row pair: 128-bit read of the tile,
 //                64-bit side-byte loads (issued before the lane phase), four
 //                bytes at a time rebuilt into BF16 low/high bytes, optional

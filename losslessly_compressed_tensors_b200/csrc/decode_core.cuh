@@ -1,6 +1,6 @@
 // Device building blocks shared by the decoder, the fused pointwise kernels and
-// the fused update kernel: operand views, the per-CTA prologue (payload staging,
-// center-specific two-symbol table, overflow map), the lane-side bit reader and
+// the fused update kernel: operand views, the per-CTA prologue (staging of the
+// payload and of the center's two-symbol table, overflow map), the lane-side bit reader and
 // tile decoder, the row-side BF16 join/split, the arithmetic of the fused
 // operations, and the host-side argument checks.
 #pragma once

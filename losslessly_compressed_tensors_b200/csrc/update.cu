@@ -13,7 +13,12 @@
 //     lane side  decode this lane's pairs            -> exponent tile (shared)
 //     row side   join with side bytes, load B, op    -> new side bytes to HBM,
 //                new exponent bytes back into the tile
-//     lane side  encode this lane's pairs from the tile into the output payload image
+//     lane side  encode this lane's pairs from the tile; finished words go straight
+//                to the output payload in HBM
+//
+// lct_update strings the five launches of an update (sample, center, this kernel,
+// scan, tail compaction) together behind one call, each scheduled while its
+// predecessor runs (programmatic stream serialisation, see batch.cuh).
 //
 // Lanes whose output overflows their bit budget also store their raw result
 // exponents from the overflow step on into `spill` (logical order), which is

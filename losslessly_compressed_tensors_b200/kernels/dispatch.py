@@ -8,8 +8,10 @@ reference's layer, all invisible to the pipelines' results:
 
 * overflow rows of the fused operations are handled inside ``pointwise_dense``
   and ``dual_scale_add`` (no separate fix-up launch, no per-stream maps);
-* the decoders use a two-symbol lookup table per codebook, cached per device
-  by ``pair_table_for``;
+* the decoders use two-symbol lookup tables per codebook (one per possible
+  center), cached per device by ``pair_table_for``;
+* ``compress_pipeline`` and ``update_pipeline`` put all launches of a buffered
+  compression / fused update behind one call;
 * every launch goes to ``torch.cuda.current_stream`` of the tensors' device.
 """
 from __future__ import annotations
