@@ -123,7 +123,10 @@ def distributed_setup(n_gpus: int):
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=180))
     elif n_gpus > 1:
         raise SystemExit("launch N > 1 with torch.distributed.run (one process per GPU)")
     else:
@@ -235,6 +238,7 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
                 times[key].append(e[a].elapsed_time(e[b]))
     exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors, restored))
     ms = {k: max_over_ranks(statistics.mean(v), world) for k, v in times.items()}
+    peer = peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup) if world > 1 else None
     return {
         "workload": "config5: GPT-2-small-shaped weight set, 148 tensors, EMPIRICAL/CLEAN, "
                     "row-shards <= 4 Mi elements",
@@ -245,6 +249,47 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
         "all_gather_gbps": world * plan.wire_bytes / ms["gather"] / 1e6,
         "decode_gbps_aggregate": world * dense_bytes / ms["decode"] / 1e6,
         "note": "batched launches prepared once: 4 launches per encode, 1 per decode-all",
+        "peer_decode": peer,
+    }
+
+
+def peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup) -> dict:
+    """The same weight set without the collective: wire buffers in symmetric memory, every rank
+    decodes all shards by loading the other ranks' bytes straight over NVLink inside the decode
+    launch (jobs interleaved over the sources, each rank starting at its right neighbour)."""
+    from losslessly_compressed_tensors_b200 import sharded
+
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    try:
+        peer = sharded.PeerWire(plan, rank)
+    except Exception as error:  # symmetric memory not available on this box / build
+        return {"unavailable": f"{type(error).__name__}: {error}"[:200]}
+    restored = [torch.empty(s, dtype=torch.bfloat16, device="cuda") for _, s in shapes]
+    encode, decode = [], []
+    for it in range(warmup + steps):
+        barrier(world)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        sharded.encode_rank(plan, rank, tensors, wire=peer.local)
+        e[1].record()
+        peer.fence()                       # every rank's wire is complete
+        sharded.decode_all(plan, peer.buffers, [s for _, s in shapes], outputs=restored,
+                           interleave_from=rank + 1)
+        e[2].record()
+        peer.fence()                       # nobody still reads what the next step overwrites
+        torch.cuda.synchronize()
+        if it >= warmup:
+            encode.append(e[0].elapsed_time(e[1]))
+            decode.append(e[1].elapsed_time(e[2]))
+    exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors, restored))
+    dense_bytes = 2 * sum(t.numel() for t in tensors)
+    decode_ms = max_over_ranks(statistics.mean(decode), world)
+    return {
+        "bit_exact": bool(exact), "multicast_bound": peer.multicast,
+        "encode_ms": max_over_ranks(statistics.mean(encode), world),
+        "fence_and_decode_all_ms": decode_ms,
+        "decode_gbps_aggregate": world * dense_bytes / decode_ms / 1e6,
+        "note": "replaces all_gather_ms + decode_all_ms above",
     }
 
 

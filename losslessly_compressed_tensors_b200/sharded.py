@@ -293,16 +293,26 @@ def all_gather_wire(wire: torch.Tensor, plan: Plan, group=None,
     return gathered
 
 
-def views_of(plan: Plan, gathered: torch.Tensor) -> list[tuple[Shard, CompressedTensor]]:
-    """Rebuild a ``CompressedTensor`` for every shard of every rank as views of ``gathered``."""
-    from .tensor_buffer import TensorBuffer
-
+def _wires_of(plan: Plan, gathered) -> list[torch.Tensor]:
+    """Per-rank wire buffers from either one gathered buffer or a list of (peer) buffers."""
+    if isinstance(gathered, (list, tuple)):
+        if len(gathered) != plan.world or any(w.numel() != plan.wire_bytes for w in gathered):
+            raise ValueError("expected one wire buffer of plan.wire_bytes per rank")
+        return list(gathered)
     if gathered.numel() != plan.world * plan.wire_bytes:
         raise ValueError("gathered buffer has the wrong size")
+    return [gathered[rank * plan.wire_bytes:(rank + 1) * plan.wire_bytes] for rank in range(plan.world)]
+
+
+def views_of(plan: Plan, gathered) -> list[tuple[Shard, CompressedTensor]]:
+    """Rebuild a ``CompressedTensor`` for every shard of every rank as views of the wire bytes:
+    ``gathered`` is the all-gathered buffer, or a list with every rank's wire buffer (which may
+    live in peer GPUs' memory, see ``PeerWire``).  Rank-major order."""
+    from .tensor_buffer import TensorBuffer
+
     metadata = TensorBuffer.storage_bytes(0, plan.max_free_regions)
     result = []
-    for rank in range(plan.world):
-        wire = gathered[rank * plan.wire_bytes:(rank + 1) * plan.wire_bytes]
+    for rank, wire in enumerate(_wires_of(plan, gathered)):
         arena_start = plan.arena_offset[rank] + metadata
         arena_payload = wire[arena_start:arena_start + plan.arena_capacity]
         for shard, slots in zip(plan.shards[rank], plan.offsets[rank]):
@@ -310,26 +320,50 @@ def views_of(plan: Plan, gathered: torch.Tensor) -> list[tuple[Shard, Compressed
     return result
 
 
-def decode_all(plan: Plan, gathered: torch.Tensor, shapes: list[tuple[int, ...]], *,
-               batched: bool = True, outputs: list[torch.Tensor] | None = None):
-    """Decode every shard from the gathered bytes and reassemble the weight set.  ``batched``
+def _interleaved(plan: Plan, views: list, first_rank: int) -> list:
+    """Reorder rank-major (shard, tensor) pairs round-robin over the source ranks, starting at
+    ``first_rank``: consecutive CTAs of a decode launch then read from different sources, and
+    when every rank starts one source further on, no source serves all readers at once."""
+    per_rank, at = [], 0
+    for rank in range(plan.world):
+        count = len(plan.shards[rank])
+        per_rank.append(views[at:at + count])
+        at += count
+    order = [(first_rank + k) % plan.world for k in range(plan.world)]
+    out = []
+    for k in range(max(len(v) for v in per_rank)):
+        out.extend(per_rank[r][k] for r in order if k < len(per_rank[r]))
+    return out
+
+
+def decode_all(plan: Plan, gathered, shapes: list[tuple[int, ...]], *, batched: bool = True,
+               outputs: list[torch.Tensor] | None = None, interleave_from: int | None = None):
+    """Decode every shard from the wire bytes and reassemble the weight set.  ``gathered``: the
+    all-gathered buffer, or a list of per-rank wire buffers (``PeerWire.buffers``: the decoder
+    then reads the other ranks' bytes straight from their memory, no collective).  ``batched``
     decodes all shards with one launch, straight into their rows of the output tensors;
-    ``outputs`` reuses existing BF16 tensors of the given shapes."""
+    ``outputs`` reuses existing BF16 tensors of the given shapes; ``interleave_from`` orders the
+    launch's jobs round-robin over the source ranks starting at that rank."""
     from .codec.decode import operand_of
     from .compression.huffman_tables import get_distribution_tables
     from .kernels import dispatch
     from .operations import decompress
 
+    wires = _wires_of(plan, gathered)
+    device = wires[0].device
     if outputs is None:
-        outputs = [torch.empty(shape, dtype=torch.bfloat16, device=gathered.device)
-                   for shape in shapes]
-    key = ("decode", batched, gathered.data_ptr(), tuple(t.data_ptr() for t in outputs))
+        outputs = [torch.empty(shape, dtype=torch.bfloat16, device=device) for shape in shapes]
+    key = ("decode", batched, interleave_from, tuple(w.data_ptr() for w in wires),
+           tuple(t.data_ptr() for t in outputs))
     hit = plan.prepared.get(key)
     if hit is not None:
         hit.run()
         return outputs
+    views = views_of(plan, wires)
+    if interleave_from is not None:
+        views = _interleaved(plan, views, interleave_from % plan.world)
     jobs, direct = [], True
-    for shard, compressed in views_of(plan, gathered):
+    for shard, compressed in views:
         target = outputs[shard.index]
         rows = target.reshape(()) if target.dim() == 0 else target[shard.row_start:shard.row_stop]
         flat = rows.view(-1).view(torch.int16) if rows.dim() else rows.reshape(1).view(torch.int16)
@@ -340,12 +374,63 @@ def decode_all(plan: Plan, gathered: torch.Tensor, shapes: list[tuple[int, ...]]
             rows.copy_(decompress(compressed).reshape(rows.shape))
     if jobs:
         block_symbols, lanes, steps, fixed_words = geometry(plan.distribution)
-        _, _, rare_length = get_distribution_tables(plan.distribution, gathered.device)
+        _, _, rare_length = get_distribution_tables(plan.distribution, device)
         batch = dispatch.decode_batch(jobs, block_symbols=block_symbols, lanes=lanes, steps=steps,
                                       fixed_words=fixed_words, rare_length=rare_length)
         if direct:
             plan.prepared[key] = batch
     return outputs
+
+
+class PeerWire:
+    """Every rank's wire buffer, addressable from this rank's kernels.
+
+    The alternative to ``all_gather_wire``: the buffers live in symmetric memory (one
+    allocation per rank, mapped into every peer over NVLink), each rank encodes into its own,
+    and ``decode_all(plan, peer.buffers, ..., interleave_from=rank + 1)`` decodes every shard
+    by plain loads from the owner's memory - the transfer is the decoder's own input stream, so
+    it overlaps the decoding instead of preceding it, and no gathered copy exists.  ``fence()``
+    orders the ranks on their streams (a one-element all-reduce): call it after encoding and
+    before decoding, and again before the buffers are written the next time.
+
+    Loads only: nothing here uses multicast (the multicast binding of the symmetric memory is
+    switched off where the installed PyTorch honours ``TORCH_SYMM_MEM_DISABLE_MULTICAST``)."""
+
+    def __init__(self, plan: Plan, rank: int, group=None, device: torch.device | None = None):
+        import os
+
+        self.plan, self.rank = plan, rank
+        device = (torch.device(device) if device is not None
+                  else torch.device("cuda", torch.cuda.current_device()))
+        if plan.world == 1:
+            self.handle = None
+            self.local = torch.zeros(plan.wire_bytes, dtype=torch.uint8, device=device)
+            self.buffers = [self.local]
+            self.multicast = False
+            return
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group if group is not None else dist.group.WORLD
+        if dist.get_world_size(self.group) != plan.world:
+            raise ValueError("plan was made for a different number of ranks")
+        self.local = symmetric.empty(plan.wire_bytes, dtype=torch.uint8, device=device)
+        self.local.zero_()
+        self.handle = symmetric.rendezvous(self.local, self.group)
+        self.buffers = [self.local if r == rank
+                        else self.handle.get_buffer(r, (plan.wire_bytes,), torch.uint8)
+                        for r in range(plan.world)]
+        self.multicast = bool(getattr(self.handle, "multicast_ptr", 0))
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def fence(self) -> None:
+        """All ranks' earlier work on their current streams is complete before any rank's later
+        work starts (stream-ordered; the host is not blocked)."""
+        if self.plan.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(self._token, group=self.group)
 
 
 def gpt2_small_shapes(layers: int = 12, d_model: int = 768, vocab: int = 50304,

@@ -90,3 +90,39 @@ def test_wire_buffer_is_reusable():
     assert again is outputs and all(torch.equal(a, b) for a, b in zip(outputs, tensors))
     with pytest.raises(ValueError):
         sharded.encode_rank(plan, 0, tensors, wire=torch.zeros(16, dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("world,row_shard,start", [(3, 30000, 1), (8, 50000, 5), (1, None, 0)])
+def test_decode_from_per_rank_buffers_matches_the_gathered_path(world, row_shard, start):
+    """The peer-memory form: decode_all takes one wire buffer per rank (here ordinary local
+    tensors standing in for the peers' memory) and may interleave its jobs over the sources."""
+    dist = Distribution(DistType.EMPIRICAL)
+    host = _weights()
+    tensors = [w.cuda() for w in host]
+    plan = sharded.make_plan(SHAPES, world, dist, row_shard_elements=row_shard, arena_fraction=0.5)
+    wires = [sharded.encode_rank(plan, rank, tensors)[0].clone() for rank in range(world)]
+    shapes = [s for _, s in SHAPES]
+    for interleave in (None, start):
+        restored = sharded.decode_all(plan, wires, shapes, interleave_from=interleave)
+        for want, got in zip(host, restored):
+            assert np.array_equal(bits_of(got), bits_of(want))
+    # same launch prepared once per set of buffers, reused on the second call
+    before = len(plan.prepared)
+    sharded.decode_all(plan, wires, shapes, outputs=restored, interleave_from=start)
+    assert len(plan.prepared) == before
+    order = sharded._interleaved(plan, sharded.views_of(plan, wires), start % world)
+    assert len(order) == sum(len(r) for r in plan.shards)
+    assert len({id(c) for _, c in order}) == len(order)
+    with pytest.raises(ValueError):
+        sharded.decode_all(plan, wires[:-1] if world > 1 else [wires[0][:-1]], shapes)
+
+
+def test_peer_wire_single_rank_is_a_plain_buffer():
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 1, dist, arena_fraction=0.5)
+    peer = sharded.PeerWire(plan, 0)
+    sharded.encode_rank(plan, 0, tensors, wire=peer.local)
+    peer.fence()
+    outputs = sharded.decode_all(plan, peer.buffers, [s for _, s in SHAPES], interleave_from=1)
+    assert all(torch.equal(a, b) for a, b in zip(outputs, tensors)) and not peer.multicast
