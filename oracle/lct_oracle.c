@@ -40,10 +40,16 @@ int orc_set_threads(int n) {
 /* Geometry helpers: LCT/kernels/generic/layout.py:15-18                     */
 /* ------------------------------------------------------------------------ */
 
+/* layout.py:15-33: the default "swizzle" mapping XORs the lane with the even
+ * row mask (row & 254); "linear" (config.lane_mapping) leaves the lane as it is. */
+static int g_lane_mask = 254;
+
+void orc_set_lane_mapping(int linear) { g_lane_mask = linear ? 0 : 254; }
+
 /* Logical (flattened tensor) offset of storage position (block, step, lane). */
 static int64_t logical_offset(int64_t block, int steps, int step, int lane) {
   int64_t row = block * steps + step;
-  return row * LANES + (lane ^ (int)(row & 254));
+  return row * LANES + (lane ^ (int)(row & g_lane_mask));
 }
 
 /* ------------------------------------------------------------------------ */

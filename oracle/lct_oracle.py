@@ -53,6 +53,14 @@ def set_threads(n: int) -> int:
     return int(lib().orc_set_threads(ctypes.c_int(n)))
 
 
+def set_lane_mapping(name: str) -> None:
+    """``"swizzle"`` (default) or ``"linear"``: the reference's ``config.lane_mapping``
+    (``LCT/kernels/generic/layout.py:15-33``).  Process-wide, like the reference's setting."""
+    if name not in ("swizzle", "linear"):
+        raise ValueError(name)
+    lib().orc_set_lane_mapping(ctypes.c_int(1 if name == "linear" else 0))
+
+
 def _p(array):
     if array is None:
         return ctypes.c_void_p(0)

@@ -1,6 +1,7 @@
 """Regenerate the golden fixtures by running the UNMODIFIED reference on the CPU.
 
-    python tests/golden/make_golden.py            # writes tables.npz, codec.json, allocator.json
+    python tests/golden/make_golden.py            # writes tables.npz, codec.json
+    LCT_GOLDEN_LANE_MAPPING=linear python tests/golden/make_golden.py linear   # adds the linear-mapping cases
 
 Needs the reference checkout (``LCT_REFERENCE_ROOT``, default ``/root/reference``)
 and runs its Triton kernels under ``TRITON_INTERPRET=1`` through
@@ -177,9 +178,18 @@ CODEC_CASES = [
 ]
 
 
-def make_codec():
+# Subsets recorded a second time with ``config.lane_mapping = "linear"`` (a run of its own:
+# ``LCT_GOLDEN_LANE_MAPPING=linear python tests/golden/make_golden.py linear``).
+LINEAR_CODEC = ("gauss_clean_wide", "laplace_clean_outliers", "sparse_buffered",
+                "medium_small_values", "high_wide_buffered", "n257", "block_plus_one")
+LINEAR_POINTWISE = ("scale_exact_wide_buffered", "two_scale_exact_medium", "dual_exact_buffered")
+
+
+def make_codec(only=None):
     cases = []
     for spec in CODEC_CASES:
+        if only is not None and spec["name"] not in only:
+            continue
         t0 = time.time()
         bits = synth_bf16(spec["n"], spec["seed"], spec["kind"], spec.get("base", 0))
         x = torch.from_numpy(bits.copy()).view(torch.bfloat16)
@@ -230,9 +240,11 @@ POINTWISE_CASES = [
 ]
 
 
-def make_pointwise():
+def make_pointwise(only=None):
     cases = []
     for spec in POINTWISE_CASES:
+        if only is not None and spec["name"] not in only:
+            continue
         t0 = time.time()
         bits = synth_bf16(spec["n"], spec["seed"], spec["kind"], spec.get("base", 0))
         x = torch.from_numpy(bits.copy()).view(torch.bfloat16)
@@ -320,6 +332,10 @@ def make_config1():
 
 def main():
     which = set(sys.argv[1:]) or {"tables", "codec", "pointwise", "allocator", "config1"}
+    mapping = os.environ.get("LCT_GOLDEN_LANE_MAPPING", "swizzle")
+    if ("linear" in which) != (mapping == "linear") or ("linear" in which and len(which) > 1):
+        raise SystemExit("the linear fixtures are a run of their own: "
+                         "LCT_GOLDEN_LANE_MAPPING=linear python make_golden.py linear")
     if "tables" in which:
         make_tables()
     path = os.path.join(HERE, "codec.json")
@@ -332,6 +348,9 @@ def main():
         data["allocator"] = make_allocator()
     if "config1" in which:
         data["config1"] = make_config1()
+    if "linear" in which:
+        data["codec_linear"] = make_codec(LINEAR_CODEC)
+        data["pointwise_linear"] = make_pointwise(LINEAR_POINTWISE)
     data["generator"] = {"torch": torch.__version__, "numpy": np.__version__,
                          "note": "reference run under TRITON_INTERPRET=1 on CPU"}
     with open(path, "w") as handle:

@@ -32,9 +32,16 @@ def _check_components(oracle, c, want, arena=None):
         assert [list(r) for r in oracle.free_regions(arena)] == want["free_regions"]
 
 
-def test_codec_cases(oracle, golden):
-    assert len(golden["codec"]) >= 15
-    for case in golden["codec"]:
+@pytest.fixture
+def linear_lanes(oracle):
+    """The reference's other lane mapping (config.lane_mapping = "linear") for one test."""
+    oracle.set_lane_mapping("linear")
+    yield
+    oracle.set_lane_mapping("swizzle")
+
+
+def _check_codec_cases(oracle, cases):
+    for case in cases:
         bits = input_of(case)
         assert sha(bits) == case["input_sha"], "synthetic input generator changed"
         arena = None
@@ -55,6 +62,20 @@ def test_codec_cases(oracle, golden):
             assert [list(r) for r in oracle.free_regions(arena)] == case["free_regions_after_free"]
 
 
+def test_codec_cases(oracle, golden):
+    assert len(golden["codec"]) >= 15
+    _check_codec_cases(oracle, golden["codec"])
+
+
+def test_codec_cases_linear_lane_mapping(oracle, golden, linear_lanes):
+    assert len(golden["codec_linear"]) >= 7
+    swizzled = {c["name"]: c for c in golden["codec"]}
+    for case in golden["codec_linear"]:   # the mapping really changes the payload (rows 0, 1: mask 0)
+        if case["n"] > 512:
+            assert case["encoded_sha"] != swizzled[case["name"]]["encoded_sha"], case["name"]
+    _check_codec_cases(oracle, golden["codec_linear"])
+
+
 def test_config1_known_answer(oracle, golden):
     torch = pytest.importorskip("torch")
     want = golden["config1"]
@@ -71,7 +92,16 @@ def test_config1_known_answer(oracle, golden):
 
 
 def test_fused_operation_cases(oracle, golden):
-    for case in golden["pointwise"]:
+    _check_fused_cases(oracle, golden["pointwise"])
+
+
+def test_fused_operation_cases_linear_lane_mapping(oracle, golden, linear_lanes):
+    assert len(golden["pointwise_linear"]) >= 3
+    _check_fused_cases(oracle, golden["pointwise_linear"])
+
+
+def _check_fused_cases(oracle, cases):
+    for case in cases:
         bits = input_of(case)
         assert sha(bits) == case["input_sha"]
         dist = dist_of(case)
