@@ -76,6 +76,15 @@ const char *lct_version(void);
 /* Text for a return code of this library (host pointer, static storage). */
 const char *lct_error_string(int code);
 
+/* Lane mapping of every later launch of this library in this process: 0 = the
+ * default "swizzle" (lane l of global row n holds element n*256 + (l ^ (n & 254))),
+ * 1 = "linear" (lane l holds element n*256 + l).  The reference fixes it at
+ * import time (LCT/config.py:16-18, LCT/kernels/generic/layout.py:12-42) and asks
+ * to keep it fixed while compressed tensors are in use; the same holds here.
+ * Not stream-ordered: it is read on the host when a launch is enqueued. */
+int lct_set_lane_mapping(int linear);
+int lct_get_lane_mapping(void);
+
 /* ---- codebook preparation ------------------------------------------------ */
 
 /* Two-symbol lookup tables over 12 stream bits, derived from a codebook's

@@ -1,9 +1,26 @@
 // Library identity and error text.
 #include <cuda_runtime.h>
 
+#include "common.cuh"
 #include "lct_b200.h"
 
+namespace lct {
+
+static int g_lane_mask = 254;
+
+int lane_mask_now() { return g_lane_mask; }
+
+}  // namespace lct
+
 extern "C" {
+
+int lct_set_lane_mapping(int linear) {
+  if (linear != 0 && linear != 1) return LCT_E_BAD_ARGUMENT;
+  lct::g_lane_mask = linear ? 0 : 254;
+  return 0;
+}
+
+int lct_get_lane_mapping(void) { return lct::g_lane_mask == 0 ? 1 : 0; }
 
 const char* lct_version(void) { return "lct-b200 0.1.0 sm_100a"; }
 

@@ -1,7 +1,9 @@
 // Shared device helpers of the sm_100a codec kernels.
 //
 // Data layout recap.  A block is `steps` rows of 256 lanes.  Lane l at global
-// row n holds logical element n*256 + (l ^ (n & 254)); rows 2k and 2k+1 share
+// row n holds logical element n*256 + (l ^ (n & lane_mask)), lane_mask = 254 (the
+// default "swizzle" mapping; 0 = the reference's "linear" mapping, for which every
+// XOR below vanishes and the same code runs unchanged); rows 2k and 2k+1 share
 // one XOR mask, and the mask is even, so lanes 2p/2p+1 stay adjacent.  The
 // mask's bits 5..7 move a warp's 32 lanes to another aligned group of 32
 // columns and its bits 1..4 permute them inside that group, so in every row
@@ -111,15 +113,19 @@ __device__ __forceinline__ int64_t sample_position(int64_t idx, int64_t n) {
   return start + (int64_t)(((uint64_t)hashed * (uint64_t)(end - start)) >> 32);
 }
 
+// Lane mapping in force (host side, process-wide like the reference's import-time
+// config.lane_mapping): 254 or 0.  Set through lct_set_lane_mapping (capi.cu).
+int lane_mask_now();
+
 // Number of leading steps of `lane` in block `block` that hold real elements.
 __device__ __forceinline__ int valid_steps_of(int64_t block, int lane, int steps, int block_symbols,
-                                              int64_t logical_numel) {
+                                              int64_t logical_numel, int lane_mask) {
   const int64_t in_block = logical_numel - block * (int64_t)block_symbols;
   if (in_block >= block_symbols) return steps;
   if (in_block <= 0) return 0;
   const int full_rows = (int)(in_block >> 8);
   const int rem = (int)(in_block & 255);
-  const int mask = (int)((block * steps + full_rows) & 254);
+  const int mask = (int)((block * steps + full_rows) & lane_mask);
   return full_rows + ((rem > 0 && ((lane ^ mask) < rem)) ? 1 : 0);
 }
 

@@ -39,7 +39,7 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
   prepare_block(sh, payload, a, g, block);
 
-  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
+  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
@@ -54,12 +54,13 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
     uint2 side_regs[2][2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      place[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base);
+      place[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base, g.lane_mask);
       const uint8_t* s = a.side + place[u].storage;
       side_regs[u][0] = __ldcs(reinterpret_cast<const uint2*>(s));
       side_regs[u][1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
     }
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length);
+    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
+                     g.lane_mask);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -162,7 +163,7 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
-  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
+  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   const int a_tail_from = sh.overflow_start[tid];
   const int a_coded = min(valid, a_tail_from);
   const uint8_t* a_tail = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
@@ -181,15 +182,15 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
     decode_tile_rows(reader_a, sh, tile, lane32, step0, a_coded, a_tail_from, a_tail,
-                     g.rare_length);
+                     g.rare_length, g.lane_mask);
     if (kDual)
       decode_tile_rows(reader_b, sh_b, tile_b, lane32, step0, b_coded, b_tail_from, b_tail,
-                       g.rare_length);
+                       g.rare_length, g.lane_mask);
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
-      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base);
+      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base, g.lane_mask);
       const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
       uint4 words_b = make_uint4(0, 0, 0, 0);
       if (kDual) words_b = *reinterpret_cast<const uint4*>(&tile_b[p * 32 + 8 * j4]);

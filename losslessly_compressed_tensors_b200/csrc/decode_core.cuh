@@ -34,6 +34,7 @@ struct Shape {
   int steps;
   int fixed_words;
   int rare_length;
+  int lane_mask;  // 254: lane ^ (row & 254) ("swizzle"); 0: "linear"
 };
 
 // Shared memory of a CTA: the payload image(s) first (fixed_words + 2 rows of
@@ -155,16 +156,16 @@ template <typename Reader>
 __device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& sh,
                                                  uint16_t* tile, int lane32, int step0, int coded,
                                                  int tail_from, const uint8_t* tail_bytes,
-                                                 int rare_length) {
+                                                 int rare_length, int lane_mask) {
   r.tile_start();
-  // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
+  // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p & lane_mask.
   if (__all_sync(0xFFFFFFFFu, step0 + kTileRows <= coded)) {
     LCT_UNROLL(LCT_DECODE_UNROLL)
     for (int p = 0; p < kTilePairs; ++p) {
       const uint32_t bits = r.peek0();
       uint32_t entry = sh.table[table_slot(bits)];
       if ((int32_t)entry < 0) entry = slow_pair(r, entry, bits, sh, rare_length);
-      tile[p * 32 + (lane32 ^ (2 * p))] = (uint16_t)entry;
+      tile[p * 32 + (lane32 ^ ((2 * p) & lane_mask))] = (uint16_t)entry;
       r.advance((int)prmt(entry, 0, 0x4442));
     }
     return;
@@ -186,7 +187,7 @@ __device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& 
       pair = symbol_of(sh.table[table_slot(bits)], bits, sh, rare_length, &l0);
       r.advance(l0);
     }
-    tile[p * 32 + (lane32 ^ (2 * p))] = (uint16_t)pair;
+    tile[p * 32 + (lane32 ^ ((2 * p) & lane_mask))] = (uint16_t)pair;
   }
 }
 
@@ -267,14 +268,15 @@ struct UnitPlace {
 };
 
 __device__ __forceinline__ UnitPlace place_unit(int warp, int p, int j4, int64_t row0, int step0,
-                                                int64_t block_base) {
-  // All 32 rows of a tile share mask bits 5..7; bits 1..4 of pair p are 2p.
+                                                int64_t block_base, int lane_mask) {
+  // All 32 rows of a tile share mask bits 5..7; bits 1..4 of pair p are 2p (all & lane_mask).
   const int64_t tile_row = row0 + step0;
-  const int group = warp ^ ((int)(tile_row >> 5) & 7);
+  const int in_tile = (2 * p) & lane_mask;
+  const int group = warp ^ ((int)(tile_row & lane_mask) >> 5);
   UnitPlace u;
   u.logical = (tile_row + 2 * p) * kLanes + 32 * group + 8 * j4;
-  u.storage = block_base + (int64_t)(step0 + 2 * p) * kLanes + 32 * warp + ((8 * j4) ^ ((2 * p) & 0x18));
-  u.q = (uint32_t)p & 3u;
+  u.storage = block_base + (int64_t)(step0 + 2 * p) * kLanes + 32 * warp + ((8 * j4) ^ (in_tile & 0x18));
+  u.q = (uint32_t)(in_tile >> 1) & 3u;
   return u;
 }
 
@@ -409,6 +411,7 @@ static inline int check_shape(int64_t size, int64_t logical_numel, int block_sym
   g->steps = steps;
   g->fixed_words = fixed_words;
   g->rare_length = rare_length;
+  g->lane_mask = lane_mask_now();
   return 0;
 }
 

@@ -34,6 +34,7 @@ struct EncodeShape {
   int block_symbols;
   int steps;
   int fixed_words;
+  int lane_mask;  // 254: lane ^ (row & 254) ("swizzle"); 0: "linear"
 };
 
 // Fixed part of the dynamic shared memory; the payload image follows it.
@@ -112,7 +113,7 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   const int64_t block_base = block * (int64_t)g.block_symbols;
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
 
-  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
+  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   const int budget_bits = g.fixed_words * 32;
   uint16_t* tile = sh.tile[warp];
   const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
@@ -127,7 +128,7 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   const int unit_p[2] = {lane32 >> 2, (lane32 >> 2) + 8};
   auto logical_of = [&](int step) {
     const int64_t row = row0 + step;
-    return row * kLanes + 32 * (warp ^ ((int)(row >> 5) & 7)) + 8 * j4;
+    return row * kLanes + 32 * (warp ^ ((int)(row & g.lane_mask) >> 5)) + 8 * j4;
   };
   UnitSource source[2];
 #pragma unroll
@@ -166,9 +167,10 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
         e_top03 = exponent_bytes(tl03, th03); e_top47 = exponent_bytes(tl47, th47);
         e_bot03 = exponent_bytes(bl03, bh03); e_bot47 = exponent_bytes(bl47, bh47);
         // Side bytes: column order -> lane order, one 8-byte store per row.
-        // mask bits 1..4 of this row pair are 2p (tiles start on multiples of 32 rows).
-        const uint32_t q = (uint32_t)p & 3u;
-        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ ((2 * p) & 0x18));
+        // mask bits 1..4 of this row pair are 2p & lane_mask (tiles start on multiples of 32 rows).
+        const int in_tile = (2 * p) & g.lane_mask;
+        const uint32_t q = (uint32_t)(in_tile >> 1) & 3u;
+        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (in_tile & 0x18));
         const uint32_t ts03 = side_bytes(tl03, th03), ts47 = side_bytes(tl47, th47);
         const uint32_t bs03 = side_bytes(bl03, bh03), bs47 = side_bytes(bl47, bh47);
         __stcs(reinterpret_cast<uint2*>(s),
@@ -192,10 +194,10 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
     // ---- lane phase ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, kLanes, lane32, step0, valid,
+        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, kLanes, lane32, g.lane_mask, step0, valid,
                                        budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, kLanes, lane32, step0, valid,
+        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, kLanes, lane32, g.lane_mask, step0, valid,
                                       budget_bits, pos, lo, extra_start);
     }
     __syncwarp();
@@ -326,7 +328,7 @@ __device__ __forceinline__ void compact_block(const void* __restrict__ src, uint
     uint8_t* dst = tail + tail_off + byte_base + lane_local;
     for (int row = lane_start + lane_in_warp; row < g.steps; row += 32) {
       const int64_t n = row0 + row;
-      const int64_t logical = n * kLanes + (lane ^ (int)(n & 254));
+      const int64_t logical = n * kLanes + (lane ^ (int)(n & g.lane_mask));
       int byte = 0;
       if (logical < g.logical_numel) {
         byte = kPrecomputed ? (int)static_cast<const uint8_t*>(src)[logical]
@@ -377,6 +379,7 @@ static int check_encode_shape(int64_t size, int64_t logical_numel, int block_sym
   g->block_symbols = block_symbols;
   g->steps = steps;
   g->fixed_words = fixed_words;
+  g->lane_mask = lct::lane_mask_now();
   return 0;
 }
 

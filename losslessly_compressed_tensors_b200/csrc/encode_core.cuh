@@ -18,13 +18,13 @@ namespace lct {
 template <bool kCheckValid>
 __device__ __forceinline__ bool encode_tile_rows(const uint2* table, const uint8_t* tile_bytes,
                                                  uint32_t* payload_column, int64_t word_stride,
-                                                 int lane32,
+                                                 int lane32, int lane_mask,
                                                  int step0, int valid, int budget_bits, int& pos,
                                                  uint32_t& lo, int& extra_start) {
   LCT_ENCODE_UNROLL_PRAGMA
   for (int p = 0; p < kTilePairs; ++p) {
-    // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p.
-    const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ (2 * p)));
+    // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p & lane_mask.
+    const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ ((2 * p) & lane_mask)));
     uint2 c0 = table[e[0]];
     uint2 c1 = table[e[1]];
     if (kCheckValid) {  // padding carries no bits

@@ -114,7 +114,7 @@ update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other,
   // Same jittered position as the center estimate (one per equal slice of the tensor).
   const int64_t pos = sample_position(idx, n);
   const int64_t row = pos >> 8;
-  const int lane = (int)(pos & 255) ^ (int)(row & 254);
+  const int lane = (int)(pos & 255) ^ (int)(row & g.lane_mask);
   const int64_t block = row / g.steps;
   const int step = (int)(row - block * g.steps);
   const uint32_t* words = a.encoded + block * kLanes + lane;
@@ -183,7 +183,7 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
-  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel);
+  const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   const int tail_from = sh.overflow_start[tid];
   const int coded = min(valid, tail_from);
   const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
@@ -198,13 +198,14 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
   bool open = true;
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length);
+    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
+                     g.lane_mask);
     __syncwarp();
     // ---- row side: A (op) B, new side bytes out, new exponents back into the tile ----
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
-      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base);
+      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base, g.lane_mask);
       uint4* slot = reinterpret_cast<uint4*>(&tile[p * 32 + 8 * j4]);
       const uint4 words = *slot;
       uint32_t e_top03, e_top47, e_bot03, e_bot47;
@@ -237,19 +238,19 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
     // ---- lane side: encode the result exponents ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(encode_table, tile_bytes, out_column, g.streams, lane32, step0, valid,
+        open = encode_tile_rows<false>(encode_table, tile_bytes, out_column, g.streams, lane32, g.lane_mask, step0, valid,
                                        budget_bits, pos, lo, extra_start);
       else
-        open = encode_tile_rows<true>(encode_table, tile_bytes, out_column, g.streams, lane32, step0, valid,
+        open = encode_tile_rows<true>(encode_table, tile_bytes, out_column, g.streams, lane32, g.lane_mask, step0, valid,
                                       budget_bits, pos, lo, extra_start);
     }
     if (!open) {
       // Raw exponents of the overflowed lane, from its overflow step on, for the tail pass.
       const int from = extra_start > step0 ? (extra_start - step0) >> 1 : 0;
       const int64_t tile_row = row0 + step0;
-      const int group = warp ^ ((int)(tile_row >> 5) & 7);
+      const int group = warp ^ ((int)(tile_row & g.lane_mask) >> 5);
       for (int p = from; p < kTilePairs; ++p) {
-        const int column = lane32 ^ (2 * p);
+        const int column = lane32 ^ ((2 * p) & g.lane_mask);
         const int64_t logical = (tile_row + 2 * p) * kLanes + 32 * group + column;
         const uint8_t* e = tile_bytes + 2 * (p * 32 + column);
         if (logical < g.logical_numel) spill[logical] = e[0];

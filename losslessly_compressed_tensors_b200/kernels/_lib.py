@@ -62,6 +62,8 @@ _SIGNATURES = {
     "lct_compact_tails": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _p],
     "lct_decode": [ctypes.POINTER(Operand), _p, _i64, _i64, _i, _i, _i, _i, _p],
     "lct_decode_batch": [_p, _i, _i64, _i, _i, _i, _i, _p],
+    "lct_set_lane_mapping": [_i],
+    "lct_get_lane_mapping": [],
     "lct_compress": [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64,
                      _i, _i, _i, _p],
     "lct_compress_batch": [_p, _i, _i64, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p],

@@ -92,6 +92,16 @@ except AttributeError:  # pragma: no cover - older/newer torch without the priva
         return torch.cuda.current_stream(index).cuda_stream
 
 _functions: dict = {}
+_applied_lane_mapping = "swizzle"   # what the library was last told (its own default)
+
+
+def _apply_lane_mapping() -> None:
+    """Hand ``config.lane_mapping`` to the library when it changed since the last launch."""
+    global _applied_lane_mapping
+    config.check()
+    _lib.check(_lib.load().lct_set_lane_mapping(1 if config.lane_mapping == "linear" else 0),
+               "lct_set_lane_mapping")
+    _applied_lane_mapping = config.lane_mapping
 
 
 def _call(name: str, device: torch.device, *args, launches: int = 1) -> None:
@@ -99,6 +109,8 @@ def _call(name: str, device: torch.device, *args, launches: int = 1) -> None:
     function = _functions.get(name)
     if function is None:
         function = _functions[name] = getattr(_lib.load(), name)
+    if config.lane_mapping is not _applied_lane_mapping:
+        _apply_lane_mapping()
     index = device.index
     if index is None:
         index = torch.cuda.current_device()
