@@ -292,10 +292,15 @@ int lct_dual_scale_add(const lct_operand *a, const lct_operand *b /* host pointe
  *                       spill[logical offset], uint8[size], which is then the
  *                       `src` of lct_compact_tails(precomputed=1).
  * Results are bit-identical to lct_pointwise(compressed_output=1) followed by
- * lct_center_and_tables / lct_encode(precomputed=1). */
+ * lct_center_and_tables / lct_encode(precomputed=1).
+ * Optional sample-value cache: result_values (uint16[min(logical_numel, 4096)],
+ * may be NULL) receives the BF16 bits of the RESULT at the sample positions;
+ * handed back as known_values (may be NULL) when that result is the A of the
+ * next update, they replace the walk over A's bit streams. */
 int lct_update_sample(const lct_operand *a /* host pointer */, const void *other,
                       const float *alpha, const float *beta, int op, int alpha_is_one,
-                      int beta_is_one, uint8_t *samples, int64_t size, int64_t logical_numel,
+                      int beta_is_one, uint8_t *samples, const uint16_t *known_values,
+                      uint16_t *result_values, int64_t size, int64_t logical_numel,
                       int block_symbols, int steps, int fixed_words, int rare_length,
                       void *stream);
 int lct_update_fused(const lct_operand *a /* host pointer */, const void *other,
@@ -318,6 +323,7 @@ int lct_update_fused(const lct_operand *a /* host pointer */, const void *other,
 int lct_update(const lct_operand *a /* host pointer */, const void *other, const float *alpha,
                const float *beta, int op, int alpha_is_one, int beta_is_one,
                const int32_t *encode_table, const int32_t *decode_table, uint8_t *samples,
+               const uint16_t *known_values, uint16_t *result_values,
                int32_t *center, int32_t *shifted_encode, int32_t *shifted_decode,
                uint8_t *side_out, int32_t *encoded_out, uint8_t *extra_starts,
                int32_t *summaries, uint8_t *spill, int32_t *counts, int32_t *descriptor,

@@ -89,6 +89,9 @@ def _launch_pointwise_compressed_dense(data, other, operation, dense_output, *, 
 FUSED_UPDATE = True
 
 
+_SAMPLE_VALUES = "_b200_sample_values"   # attribute of a CompressedTensor made by a fused update
+
+
 def _fused_update(data, other, operation, result_distribution, buffer, *, alpha, beta,
                   alpha_is_one):
     scaled = operation.name == "scalar_mul_add"
@@ -105,7 +108,16 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
                 beta_is_one=not scaled or beta is None, rare_length=rare_length,
                 logical_numel=data.logical_numel, block_symbols=block_symbols, lanes=lanes,
                 steps=steps, fixed_words=fixed_words)
-    samples = torch.empty(min(data.logical_numel, 4096), dtype=torch.uint8, device=device)
+    count = min(data.logical_numel, 4096)
+    samples = torch.empty(count, dtype=torch.uint8, device=device)
+    # The BF16 results at the sample positions ride along with the result (outside the
+    # reference's field set and its memory_size()): when the result is updated again, they
+    # replace the walk over its bit streams in the sample pre-pass.
+    known = getattr(data, _SAMPLE_VALUES, None)
+    if known is not None and (known.numel() != count or known.device != device):
+        known = None
+    values = torch.empty(count, dtype=torch.int16, device=device)
+    meta_sample = dict(meta, known_values=known, result_values=values)
     side_out = torch.empty(data.size, dtype=torch.uint8, device=device)
     spill = torch.empty(data.size, dtype=torch.uint8, device=device)  # touched by overflow lanes only
     if buffer is not None and encode_module.SINGLE_CALL_PIPELINE:
@@ -127,8 +139,8 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
             operand, other, alpha, beta, encode_table, decode_table, samples, center,
             new(256, torch.int32), shifted_decode, side_out, encoded, new(streams, torch.uint8),
             new(4 * blocks, torch.int32), spill, counts, descriptor, blocks_out, buffer, data.size,
-            **meta)
-        return CompressedTensor(
+            **meta_sample)
+        result = CompressedTensor(
             encoded, data.size, side_out, fallback_starts=None, fallback_lanes=None,
             fallback_blocks=blocks_out, fallback_buffer=buffer.data,
             fallback_descriptor=descriptor, buffer=buffer, fallback_count=counts[:1],
@@ -136,16 +148,20 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
             decode_table=shifted_decode, shape=data.shape, layout=StorageLayout.COMPRESSED,
             stream_geometry=geometry(result_distribution),
         )
-    dispatch.update_sample(operand, other, samples, data.size, alpha, beta, **meta)
+        object.__setattr__(result, _SAMPLE_VALUES, values)
+        return result
+    dispatch.update_sample(operand, other, samples, data.size, alpha, beta, **meta_sample)
 
     def launch(shifted_encode, encoded, extra_starts, summaries):
         dispatch.update_fused(operand, other, shifted_encode, side_out, encoded, extra_starts,
                               summaries, spill, data.size, alpha, beta, **meta)
 
-    return compress_components(
+    result = compress_components(
         spill, side_out, data.size, result_distribution, buffer, data.shape, precomputed=True,
         logical_numel=data.logical_numel, center_samples=samples, launch_encode=launch,
     )
+    object.__setattr__(result, _SAMPLE_VALUES, values)
+    return result
 
 
 def _launch_scalar_mul_add_compressed_compressed(data, other, alpha, dense_output):

@@ -102,40 +102,48 @@ __device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, 
 // its shared column asynchronously while the overflow map is consulted.
 __global__ void __launch_bounds__(kThreads)
 update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, OpSpec spec,
-                     uint8_t* __restrict__ samples) {
+                     const uint16_t* __restrict__ known, uint8_t* __restrict__ samples,
+                     uint16_t* __restrict__ values) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cudaTriggerProgrammaticLaunchCompletion();  // the center kernel behind this one waits on its own
   const int tid = threadIdx.x;
-  uint32_t* column = reinterpret_cast<uint32_t*>(smem_raw) + tid;
   const int64_t n = g.logical_numel;
   const int64_t count = n < kSampleCount ? n : kSampleCount;
   const int64_t idx = (int64_t)blockIdx.x * kThreads + tid;
   if (idx >= count) return;
   // Same jittered position as the center estimate (one per equal slice of the tensor).
   const int64_t pos = sample_position(idx, n);
-  const int64_t row = pos >> 8;
-  const int lane = (int)(pos & 255) ^ (int)(row & g.lane_mask);
-  const int64_t block = row / g.steps;
-  const int step = (int)(row - block * g.steps);
-  const uint32_t* words = a.encoded + block * kLanes + lane;
-  for (int w = 0; w < g.fixed_words; ++w)
-    cp_async_4(column + w * kLanes, words + (int64_t)w * g.streams);
-  column[g.fixed_words * kLanes] = 0u;
-  column[(g.fixed_words + 1) * kLanes] = 0u;
-  column[(g.fixed_words + 2) * kLanes] = 0u;
   const uint32_t right = other[pos];
-  const uint32_t side = a.side[block * (int64_t)g.block_symbols + (int64_t)step * kLanes + lane];
-  const int center = *a.center;
-  const uint32_t* table = a.pair_table + (size_t)((center + 128) & 255) * kPairEntries;
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
-  const int tail = tail_exponent_at(a, g, block, step, lane);
-  cp_async_wait_all();
-  const uint32_t exponent = tail >= 0 ? (uint32_t)tail : walk_to(table, g, column, step, center);
-  const uint32_t left = (exponent << 7) | (side & 0x7Fu) | ((side & 0x80u) << 8);
+  uint32_t left;
+  if (known != nullptr) {
+    // A's values at the sample positions were kept when A was made: no stream to walk.
+    left = known[idx];
+  } else {
+    uint32_t* column = reinterpret_cast<uint32_t*>(smem_raw) + tid;
+    const int64_t row = pos >> 8;
+    const int lane = (int)(pos & 255) ^ (int)(row & g.lane_mask);
+    const int64_t block = row / g.steps;
+    const int step = (int)(row - block * g.steps);
+    const uint32_t* words = a.encoded + block * kLanes + lane;
+    for (int w = 0; w < g.fixed_words; ++w)
+      cp_async_4(column + w * kLanes, words + (int64_t)w * g.streams);
+    column[g.fixed_words * kLanes] = 0u;
+    column[(g.fixed_words + 1) * kLanes] = 0u;
+    column[(g.fixed_words + 2) * kLanes] = 0u;
+    const uint32_t side = a.side[block * (int64_t)g.block_symbols + (int64_t)step * kLanes + lane];
+    const int center = *a.center;
+    const uint32_t* table = a.pair_table + (size_t)((center + 128) & 255) * kPairEntries;
+    const int tail = tail_exponent_at(a, g, block, step, lane);
+    cp_async_wait_all();
+    const uint32_t exponent = tail >= 0 ? (uint32_t)tail : walk_to(table, g, column, step, center);
+    left = (exponent << 7) | (side & 0x7Fu) | ((side & 0x80u) << 8);
+  }
   const uint32_t result = apply_op(left, right, spec.op, spec.alpha_is_one != 0,
                                    spec.beta_is_one != 0, alpha, beta);
   samples[idx] = (uint8_t)((result >> 7) & 0xFFu);
+  if (values != nullptr) values[idx] = (uint16_t)result;
 }
 
 // Split one row of results (4 words, column order; padding already zeroed):
@@ -306,7 +314,8 @@ static int check_update_args(const lct_operand* a, const void* other, const floa
 
 static int launch_sample(const lct_operand* a, const void* other, const float* alpha,
                          const float* beta, int op, int alpha_is_one, int beta_is_one,
-                         uint8_t* samples, int64_t size, int64_t logical_numel, int block_symbols,
+                         uint8_t* samples, const uint16_t* known_values, uint16_t* result_values,
+                         int64_t size, int64_t logical_numel, int block_symbols,
                          int steps, int fixed_words, int rare_length, cudaStream_t stream) {
   lct::Shape g;
   lct::OperandView va;
@@ -319,8 +328,10 @@ static int launch_sample(const lct_operand* a, const void* other, const float* a
   const unsigned grid = (unsigned)((count + lct::kThreads - 1) / lct::kThreads);
   const size_t shared = lct::payload_image_bytes(fixed_words + 1);
   if ((rc = lct::opt_in_shared(lct::update_sample_kernel, shared)) != 0) return rc;
+  if ((reinterpret_cast<uintptr_t>(known_values) | reinterpret_cast<uintptr_t>(result_values)) & 1u)
+    return LCT_E_ALIGNMENT;
   lct::update_sample_kernel<<<grid, lct::kThreads, shared, stream>>>(
-      va, g, static_cast<const uint16_t*>(other), spec, samples);
+      va, g, static_cast<const uint16_t*>(other), spec, known_values, samples, result_values);
   return (int)cudaGetLastError();
 }
 
@@ -356,11 +367,12 @@ static int launch_fused(const lct_operand* a, const void* other, const float* al
 
 int lct_update_sample(const lct_operand* a, const void* other, const float* alpha,
                       const float* beta, int op, int alpha_is_one, int beta_is_one,
-                      uint8_t* samples, int64_t size, int64_t logical_numel, int block_symbols,
+                      uint8_t* samples, const uint16_t* known_values, uint16_t* result_values,
+                      int64_t size, int64_t logical_numel, int block_symbols,
                       int steps, int fixed_words, int rare_length, void* stream) {
-  return launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples, size,
-                       logical_numel, block_symbols, steps, fixed_words, rare_length,
-                       static_cast<cudaStream_t>(stream));
+  return launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples, known_values,
+                       result_values, size, logical_numel, block_symbols, steps, fixed_words,
+                       rare_length, static_cast<cudaStream_t>(stream));
 }
 
 int lct_update_fused(const lct_operand* a, const void* other, const float* alpha,
@@ -377,7 +389,8 @@ int lct_update_fused(const lct_operand* a, const void* other, const float* alpha
 
 int lct_update(const lct_operand* a, const void* other, const float* alpha, const float* beta,
                int op, int alpha_is_one, int beta_is_one, const int32_t* encode_table,
-               const int32_t* decode_table, uint8_t* samples, int32_t* center,
+               const int32_t* decode_table, uint8_t* samples, const uint16_t* known_values,
+               uint16_t* result_values, int32_t* center,
                int32_t* shifted_encode, int32_t* shifted_decode, uint8_t* side_out,
                int32_t* encoded_out, uint8_t* extra_starts, int32_t* summaries, uint8_t* spill,
                int32_t* counts, int32_t* descriptor, int32_t* blocks_out, void* arena_storage,
@@ -390,8 +403,9 @@ int lct_update(const lct_operand* a, const void* other, const float* alpha, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // 1. the sample pre-pass: an ordinary launch, so everything queued before this call is
   //    complete and visible before any of the five kernels starts.
-  int rc = launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples, size,
-                         logical_numel, block_symbols, steps, fixed_words, rare_length, st);
+  int rc = launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples,
+                         known_values, result_values, size, logical_numel, block_symbols, steps,
+                         fixed_words, rare_length, st);
   if (rc) return rc;
   // 2-5. each may be scheduled while its predecessor runs and waits for it on the device.
   const int64_t count = logical_numel < lct::kSampleCount ? logical_numel : lct::kSampleCount;

@@ -69,12 +69,12 @@ _SIGNATURES = {
     "lct_compress_batch": [_p, _i, _i64, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p],
     "lct_pointwise": [ctypes.POINTER(Operand), _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i64,
                       _i, _i, _i, _i, _p],
-    "lct_update_sample": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _i64, _i64, _i, _i,
-                          _i, _i, _p],
+    "lct_update_sample": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _i64, _i64,
+                          _i, _i, _i, _i, _p],
     "lct_update_fused": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p,
                          _i64, _i64, _i, _i, _i, _i, _p],
     "lct_update": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p,
-                   _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _p],
+                   _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _p],
     "lct_dual_scale_add": [ctypes.POINTER(Operand), ctypes.POINTER(Operand), _p, _p, _p, _i,
                            _i64, _i64, _i, _i, _i, _i, _p],
     "lct_buffer_reset": [_p, _i, _i32, _p],

@@ -323,16 +323,19 @@ def pointwise_dense(operand: Operand, other, output, auxiliary, n_elements, alph
 
 def update_sample(operand: Operand, other, samples, n_elements, alpha, beta, *, op, alpha_is_one,
                   beta_is_one, rare_length, logical_numel, block_symbols, lanes, steps,
-                  fixed_words):
-    """Exponent bytes of ``compA (op) other`` at the positions the center estimate samples."""
+                  fixed_words, known_values=None, result_values=None):
+    """Exponent bytes of ``compA (op) other`` at the positions the center estimate samples.
+    ``result_values`` (int16[samples]) receives the full BF16 results there; ``known_values`` are
+    such values of ``compA`` kept from the update that produced it (no stream walk then)."""
     device = _require_cuda(samples)
     _call(
         "lct_update_sample", device,
         ctypes.byref(operand), other.data_ptr(),
         alpha.data_ptr() if alpha is not None else None,
         beta.data_ptr() if beta is not None else None,
-        op, int(alpha_is_one), int(beta_is_one), samples.data_ptr(), n_elements, logical_numel,
-        block_symbols, steps, fixed_words, rare_length)
+        op, int(alpha_is_one), int(beta_is_one), samples.data_ptr(), _ptr(known_values),
+        _ptr(result_values), n_elements, logical_numel, block_symbols, steps, fixed_words,
+        rare_length)
 
 
 def update_fused(operand: Operand, other, shifted_encode, side_out, encoded_out, extra_starts,
@@ -354,7 +357,7 @@ def update_pipeline(operand: Operand, other, alpha, beta, encode_table, decode_t
                     center, shifted_encode, shifted_decode, side_out, encoded_out, extra_starts,
                     summaries, spill, counts, descriptor, blocks_out, buffer, n_elements, *, op,
                     alpha_is_one, beta_is_one, rare_length, logical_numel, block_symbols, lanes,
-                    steps, fixed_words):
+                    steps, fixed_words, known_values=None, result_values=None):
     """Sample, center, decode-op-encode, scan + reservation and tail compaction of a fused update
     as one call (five launches that overlap where their data allows)."""
     device = _require_cuda(side_out)
@@ -364,8 +367,9 @@ def update_pipeline(operand: Operand, other, alpha, beta, encode_table, decode_t
         alpha.data_ptr() if alpha is not None else None,
         beta.data_ptr() if beta is not None else None,
         op, int(alpha_is_one), int(beta_is_one), encode_table.data_ptr(), decode_table.data_ptr(),
-        samples.data_ptr(), center.data_ptr(), shifted_encode.data_ptr(),
-        shifted_decode.data_ptr(), side_out.data_ptr(), encoded_out.data_ptr(),
+        samples.data_ptr(), _ptr(known_values), _ptr(result_values), center.data_ptr(),
+        shifted_encode.data_ptr(), shifted_decode.data_ptr(), side_out.data_ptr(),
+        encoded_out.data_ptr(),
         extra_starts.data_ptr(), summaries.data_ptr(), spill.data_ptr(), counts.data_ptr(),
         descriptor.data_ptr(), blocks_out.data_ptr(), buffer._storage.data_ptr(),
         buffer.max_free_regions, n_elements, logical_numel, block_symbols, steps, fixed_words,
