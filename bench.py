@@ -539,9 +539,10 @@ def run_ours(args, rank: int, world: int, local: int):
     clocks = sampler.finish() if sampler else None   # sampled across both timed regions
 
     del host_out, dev_in, dev_out, x, flush
-    sharded = sharded_leg(rank, world) if not args.no_sharded else None
-    update = update_leg() if (rank == 0 and not args.no_sharded) else None
-    arena = arena_leg() if (rank == 0 and not args.no_sharded) else None
+    legs = set() if args.no_sharded else set(args.legs.split(","))
+    sharded = sharded_leg(rank, world) if "sharded" in legs else None
+    update = update_leg() if (rank == 0 and "update" in legs) else None
+    arena = arena_leg() if (rank == 0 and "arena" in legs) else None
     if rank != 0:
         return
     peak, peak_kind = peak_hbm_gbs()
@@ -593,7 +594,11 @@ def main():
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    parser.add_argument("--no-sharded", action="store_true", help="skip the sharded weight-set leg")
+    parser.add_argument("--no-sharded", action="store_true",
+                        help="skip the extra legs (configurations 3, 4 and 5)")
+    parser.add_argument("--legs", default="sharded,update,arena",
+                        help="extra legs to run after configuration 2: sharded (configuration 5), "
+                             "update (configuration 4), arena (configuration 3)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))

@@ -187,10 +187,29 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
       decode_tile_rows(reader_b, sh_b, tile_b, lane32, step0, b_coded, b_tail_from, b_tail,
                        g.rare_length, g.lane_mask);
     __syncwarp();
+    // All global loads of the tile's four rows first, so their latencies overlap.
+    UnitPlace place_of[2];
+    uint2 side_a[2][2], side_b[2][2];
+    uint32_t dense_in[2][2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      place_of[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base,
+                               g.lane_mask);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int64_t s_at = place_of[u].storage + half * kLanes;
+        side_a[u][half] = __ldcs(reinterpret_cast<const uint2*>(a.side + s_at));
+        if (kDual)
+          side_b[u][half] = __ldcs(reinterpret_cast<const uint2*>(b.side + s_at));
+        else
+          load_dense8(other, place_of[u].logical + half * kLanes, g.logical_numel, other_vector_ok,
+                      dense_in[u][half]);
+      }
+    }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
-      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base, g.lane_mask);
+      const UnitPlace place = place_of[u];
       const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
       uint4 words_b = make_uint4(0, 0, 0, 0);
       if (kDual) words_b = *reinterpret_cast<const uint4*>(&tile_b[p * 32 + 8 * j4]);
@@ -199,13 +218,12 @@ pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restri
         const int64_t s_at = place.storage + half * kLanes;
         const int64_t l_at = place.logical + half * kLanes;
         uint32_t left[4], right[4], result[4];
-        join_row(words, __ldcs(reinterpret_cast<const uint2*>(a.side + s_at)), place.q, half == 1,
-                 left);
+        join_row(words, side_a[u][half], place.q, half == 1, left);
         if (kDual) {
-          join_row(words_b, __ldcs(reinterpret_cast<const uint2*>(b.side + s_at)), place.q,
-                   half == 1, right);
+          join_row(words_b, side_b[u][half], place.q, half == 1, right);
         } else {
-          load_dense8(other, l_at, g.logical_numel, other_vector_ok, right);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) right[k] = dense_in[u][half][k];
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k)

@@ -210,10 +210,28 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
                      g.lane_mask);
     __syncwarp();
     // ---- row side: A (op) B, new side bytes out, new exponents back into the tile ----
+    // Side bytes of all four rows first (registers allow no more at four CTAs per SM); B's
+    // rows are requested two at a time, each pair ahead of the arithmetic that uses it.
+    UnitPlace place_of[2];
+    uint2 side_in[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      place_of[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base,
+                               g.lane_mask);
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        side_in[u][half] =
+            __ldcs(reinterpret_cast<const uint2*>(a.side + place_of[u].storage + half * kLanes));
+    }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
-      const UnitPlace place = place_unit(warp, p, j4, row0, step0, block_base, g.lane_mask);
+      const UnitPlace place = place_of[u];
+      uint32_t right_in[2][4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        load_dense8(other, place.logical + half * kLanes, g.logical_numel, other_vector_ok,
+                    right_in[half]);
       uint4* slot = reinterpret_cast<uint4*>(&tile[p * 32 + 8 * j4]);
       const uint4 words = *slot;
       uint32_t e_top03, e_top47, e_bot03, e_bot47;
@@ -221,10 +239,9 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, 
       for (int half = 0; half < 2; ++half) {
         const int64_t s_at = place.storage + half * kLanes;
         const int64_t l_at = place.logical + half * kLanes;
-        uint32_t left[4], right[4], result[4];
-        join_row(words, __ldcs(reinterpret_cast<const uint2*>(a.side + s_at)), place.q, half == 1,
-                 left);
-        load_dense8(other, l_at, g.logical_numel, other_vector_ok, right);
+        uint32_t left[4], result[4];
+        const uint32_t* right = right_in[half];
+        join_row(words, side_in[u][half], place.q, half == 1, left);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           result[k] = apply_op(left[k], right[k], spec.op, spec.alpha_is_one != 0,
