@@ -196,7 +196,7 @@ def run_reference(args, rank: int):
     }))
 
 
-def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
+def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2, with_peer: bool = False) -> dict:
     """BASELINE configuration 5: a GPT-2-small-shaped BF16 weight set (148 tensors, 124 475 904
     parameters, N(0, 0.02), LayerNorm weights 1, biases 0), EMPIRICAL codebook, row-shards of at
     most 4 Mi elements spread over the ranks; every rank encodes its shards into its wire
@@ -238,7 +238,8 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2) -> dict:
                 times[key].append(e[a].elapsed_time(e[b]))
     exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors, restored))
     ms = {k: max_over_ranks(statistics.mean(v), world) for k, v in times.items()}
-    peer = peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup) if world > 1 else None
+    peer = (peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup)
+            if world > 1 and with_peer else None)
     return {
         "workload": "config5: GPT-2-small-shaped weight set, 148 tensors, EMPIRICAL/CLEAN, "
                     "row-shards <= 4 Mi elements",
@@ -540,7 +541,7 @@ def run_ours(args, rank: int, world: int, local: int):
 
     del host_out, dev_in, dev_out, x, flush
     legs = set() if args.no_sharded else set(args.legs.split(","))
-    sharded = sharded_leg(rank, world) if "sharded" in legs else None
+    sharded = sharded_leg(rank, world, with_peer="peer" in legs) if "sharded" in legs else None
     update = update_leg() if (rank == 0 and "update" in legs) else None
     arena = arena_leg() if (rank == 0 and "arena" in legs) else None
     if rank != 0:
@@ -598,7 +599,8 @@ def main():
                         help="skip the extra legs (configurations 3, 4 and 5)")
     parser.add_argument("--legs", default="sharded,update,arena",
                         help="extra legs to run after configuration 2: sharded (configuration 5), "
-                             "update (configuration 4), arena (configuration 3)")
+                             "update (configuration 4), arena (configuration 3); add 'peer' to also "
+                             "time the peer-memory decode inside the sharded leg (N > 1)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))

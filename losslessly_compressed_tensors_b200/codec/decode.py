@@ -13,6 +13,9 @@ from ..kernels import dispatch
 from ..kernels.backends import FallbackStorage
 
 
+_OPERAND = "_b200_operand"   # per-object cache slot (not a field: outside equality and memory_size)
+
+
 def _buffered(data: CompressedTensor) -> bool:
     return data.fallback_descriptor is not None
 
@@ -45,7 +48,11 @@ def has_fallback(data: CompressedTensor) -> bool:
 
 
 def operand_of(data: CompressedTensor):
-    """The ``struct lct_operand`` describing ``data`` for the decoder and the fused operations."""
+    """The ``struct lct_operand`` describing ``data`` for the decoder and the fused operations.
+    A compressed tensor is immutable, so the struct is built once and kept with it."""
+    cached = data.__dict__.get(_OPERAND)
+    if cached is not None:
+        return cached
     device = data.data.device
     overflow = dispatch.fallback_tail_args(_storage(data) if has_fallback(data) else None)
     pair_table = dispatch.pair_table_for(data.distribution, device)
@@ -56,6 +63,7 @@ def operand_of(data: CompressedTensor):
     operand = dispatch.make_operand(data.data, data.sign_mantissa, shifted, data.center,
                                     pair_table, overflow)
     operand.keepalive = (shifted, pair_table)  # raw pointers inside: keep the tensors referenced
+    object.__setattr__(data, _OPERAND, operand)
     return operand
 
 
