@@ -74,3 +74,14 @@ def test_cpu_tensors_are_rejected():
     with pytest.raises(ValueError, match="CUDA device"):
         dispatch.shift_decoding_table(torch.zeros(1024, dtype=torch.int32),
                                       torch.zeros(1, dtype=torch.int32))
+
+
+def test_lane_mapping_switch_is_host_state_only():
+    """lct_set_lane_mapping touches no device: it can be exercised without a GPU."""
+    from losslessly_compressed_tensors_b200.kernels import _lib
+
+    lib = _lib.load()
+    assert lib.lct_get_lane_mapping() == 0            # "swizzle" is the default
+    assert lib.lct_set_lane_mapping(1) == 0 and lib.lct_get_lane_mapping() == 1
+    assert lib.lct_set_lane_mapping(2) != 0 and lib.lct_get_lane_mapping() == 1   # rejected, unchanged
+    assert lib.lct_set_lane_mapping(0) == 0 and lib.lct_get_lane_mapping() == 0
