@@ -471,6 +471,28 @@ def run_ours(args, rank: int, world: int, local: int):
     finally:
         encode_module.SINGLE_CALL_PIPELINE = True
     kernel_ms["lct_encode"] = statistics.mean(encode_trace.milliseconds("lct_encode"))
+    # The same step as one captured CUDA graph (compress + decompress + free, seven launches):
+    # what a caller with fixed shapes pays per step once the host is out of the loop.  Back to
+    # back, no L2 flush in between (the 128 MiB input and output are each larger than L2).
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        c = compress(x, dist_cfg, buffer)
+        graph_out = decompress(c)
+        c.free()
+    del c
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    replays = max(10, min(args.steps, 50))
+    a, b = event(), event()
+    a.record()
+    for _ in range(replays):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    graph_ms = a.elapsed_time(b) / replays
+    assert torch.equal(graph_out.view(torch.int16), x.view(torch.int16))
+    del graph, graph_out
     # Without a shared arena (the reference's other mode): exact-size private overflow tensors
     # need the two totals on the host, i.e. one synchronisation inside every compress.
     private_ms = []
@@ -577,6 +599,7 @@ def run_ours(args, rank: int, world: int, local: int):
                 "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
         "gpu_launches": launches, "clocks": clocks, "sharded": sharded, "update": update,
         "arena": arena, "encode_ms_without_arena": statistics.mean(private_ms),
+        "graph_replay_ms_per_step": graph_ms,
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)
