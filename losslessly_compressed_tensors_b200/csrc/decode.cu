@@ -46,9 +46,13 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
   BitReader reader;
   reader.open(payload + tid, g.fixed_words);
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
+  // Rows of this block that hold elements: tiles of pure padding (the tail of a ragged or tiny
+  // tensor) have nothing to decode and nothing to store.
+  const int rows_used =
+      full_block ? g.steps : (int)((g.logical_numel - block_base + kLanes - 1) / kLanes);
   uint16_t* tile = sh.tile[warp];
 
-  for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
+  for (int step0 = 0; step0 < rows_used; step0 += kTileRows) {
     // Side bytes of this thread's two row-phase units, requested before the lane phase.
     UnitPlace place[2];
     uint2 side_regs[2][2];

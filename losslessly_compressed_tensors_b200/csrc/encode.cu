@@ -148,7 +148,11 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   }
   __syncthreads();
 
-  for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
+  // Rows of this block that hold elements.  Tiles of pure padding (the tail of a ragged or tiny
+  // tensor) carry no bits; their side bytes are cleared in one sweep after the loop.
+  const int rows_used =
+      full_block ? g.steps : (int)((g.logical_numel - block_base + kLanes - 1) / kLanes);
+  for (int step0 = 0; step0 < rows_used; step0 += kTileRows) {
     // ---- row phase ----
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -185,7 +189,7 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
     }
     __syncwarp();
     // Request the next tile's source now; it arrives while the lanes encode.
-    if (step0 + kTileRows < g.steps) {
+    if (step0 + kTileRows < rows_used) {
 #pragma unroll
       for (int u = 0; u < 2; ++u)
         source[u] = load_unit<kPrecomputed>(src, logical_of(step0 + kTileRows + 2 * unit_p[u]),
@@ -201,6 +205,12 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
                                       budget_bits, pos, lo, extra_start);
     }
     __syncwarp();
+  }
+  if (!kPrecomputed && !full_block) {
+    const int first_untouched = (rows_used + kTileRows - 1) / kTileRows * kTileRows;
+    uint4* rest = reinterpret_cast<uint4*>(side + block_base + (int64_t)first_untouched * kLanes);
+    for (int i = tid; i < (g.steps - first_untouched) * (kLanes / 16); i += kThreads)
+      __stcs(rest + i, make_uint4(0u, 0u, 0u, 0u));
   }
   if (open && (pos & 31) != 0) payload_column[(pos >> 5) * kLanes] = lo;
   extra_starts[block * kLanes + tid] = extra_start < 0 ? (uint8_t)255 : (uint8_t)extra_start;
