@@ -1,8 +1,10 @@
-"""``LCTTensor``: a tensor wrapper that keeps its values compressed.
+"""``LCTTensor``: a ``torch.Tensor`` wrapper subclass whose values live compressed.
 
-Interface of the reference's ``LCT/LCTensor.py:12-111``: construction compresses, the
-in-place updates replace the compressed value through the fused kernels and release the
-previous value's arena region.
+Interface of the reference's ``LCT/LCTensor.py:12-111`` (constructor, ``x``, ``nbytes``,
+``dense_nbytes``, ``layout``, ``add_``, ``mul_add_``, ``add_comp_``, ``decompress``,
+``decompress_free``, ``free``; ``.T``/``permute``/``mm`` decode first).  Every in-place update
+builds the new compressed value with one fused call on the old one, in the old value's codebook
+and arena, and then returns the old value's arena region.
 """
 from __future__ import annotations
 
@@ -11,12 +13,12 @@ import math
 import torch
 from torch import Tensor
 
+from . import operations as ops
 from .comp_format import Distribution
 from .comp_tensor import CompressedTensor
-from .operations import (
-    a_compA_add_B, a_compA_add_b_B, a_compA_add_compB, compA_add_B, compress, decompress,
-)
 from .tensor_buffer import TensorBuffer
+
+_aten = torch.ops.aten
 
 
 class LCTTensor(Tensor):
@@ -27,22 +29,28 @@ class LCTTensor(Tensor):
     def __new__(cls, x, buffer: TensorBuffer | None, dist: Distribution):
         assert x.dtype == torch.bfloat16
         assert x.device.type == "cuda", f"x.device={x.device}"
-        return torch.Tensor._make_wrapper_subclass(
-            cls, x.shape, dtype=x.dtype, device=x.device, requires_grad=x.requires_grad)
+        # shape / dtype / device / requires_grad of the wrapper follow the dense source
+        return Tensor._make_wrapper_subclass(cls, x.shape, dtype=x.dtype, device=x.device,
+                                             requires_grad=x.requires_grad)
 
     def __init__(self, x: Tensor, buffer: TensorBuffer | None, dist: Distribution):
-        self.x = compress(x, buffer=buffer, distribution=dist)
+        self.x = ops.compress(x, buffer=buffer, distribution=dist)
+
+    # ---- the few aten ops the wrapper answers itself (by decoding) ------------------------
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
         def dense(value):
-            return decompress(value.x) if isinstance(value, LCTTensor) else value
+            return ops.decompress(value.x) if isinstance(value, LCTTensor) else value
 
-        if func in (torch.ops.aten.t.default, torch.ops.aten.permute.default):
+        if func in (_aten.t.default, _aten.permute.default):
             return dense(args[0]).T
-        if func is torch.ops.aten.mm.default:
-            return dense(args[0]) @ dense(args[1])
+        if func is _aten.mm.default:
+            left, right = args
+            return dense(left) @ dense(right)
         raise NotImplementedError(f"{func} not implemented for LCTTensor")
+
+    # ---- sizes ---------------------------------------------------------------------------
 
     @property
     def nbytes(self):
@@ -50,7 +58,7 @@ class LCTTensor(Tensor):
 
     @property
     def dense_nbytes(self):
-        return math.prod(self.x.shape) * 2
+        return 2 * math.prod(self.x.shape)
 
     @property
     def layout(self):
@@ -59,40 +67,44 @@ class LCTTensor(Tensor):
     def __repr__(self):
         return f"LCTTensor({self.x})"
 
-    def _replace(self, new: CompressedTensor) -> None:
-        previous, self.x = self.x, new
-        previous.free()
+    # ---- in-place updates ----------------------------------------------------------------
+
+    def _become(self, make) -> None:
+        """``make(old, home)`` builds the new value (``home``: compressed result in the old
+        value's codebook and arena); the old value's region is released afterwards."""
+        old = self.x
+        home = dict(dense_output=False, distribution=old.distribution, buffer=old.buffer)
+        self.x = make(old, home)
+        old.free()
 
     def add_(self, update: Tensor):
         """``x <- x + update``."""
-        prev = self.x
-        self._replace(compA_add_B(prev, update, dense_output=False,
-                                  distribution=prev.distribution, buffer=prev.buffer))
+        self._become(lambda old, home: ops.compA_add_B(old, update, **home))
 
     def mul_add_(self, alpha: Tensor, update: Tensor, beta: Tensor | None = None, *,
                  alpha_is_one: bool = False):
-        """``x <- alpha * x + beta * update`` (``beta`` defaults to 1)."""
-        prev = self.x
-        common = dict(alpha_is_one=alpha_is_one, dense_output=False,
-                      distribution=prev.distribution, buffer=prev.buffer)
+        """``x <- alpha * x + beta * update`` (``beta`` defaults to 1; ``alpha_is_one`` treats
+        alpha as 1 without reading it)."""
         if beta is None:
-            self._replace(a_compA_add_B(prev, alpha, update, **common))
+            self._become(lambda old, home: ops.a_compA_add_B(
+                old, alpha, update, alpha_is_one=alpha_is_one, **home))
         else:
-            self._replace(a_compA_add_b_B(prev, alpha, update, beta, **common))
+            self._become(lambda old, home: ops.a_compA_add_b_B(
+                old, alpha, update, beta, alpha_is_one=alpha_is_one, **home))
 
     def add_comp_(self, update_comp: "LCTTensor", alpha: Tensor):
-        """``x <- x + alpha * update_comp`` with both sides compressed."""
-        prev = self.x
-        self._replace(a_compA_add_compB(update_comp.x, alpha, prev, dense_output=False,
-                                        buffer=prev.buffer, distribution=prev.distribution))
+        """``x <- x + alpha * update_comp``, both sides compressed."""
+        self._become(lambda old, home: ops.a_compA_add_compB(update_comp.x, alpha, old, **home))
+
+    # ---- leaving the compressed form -------------------------------------------------------
 
     def decompress(self) -> Tensor:
-        return decompress(self.x)
+        return ops.decompress(self.x)
 
     def decompress_free(self) -> Tensor:
-        """Decode, then release the compressed value's arena region."""
+        """The dense values; the compressed form's arena region is returned."""
         dense = self.decompress()
-        self.x.free()
+        self.free()
         return dense
 
     def free(self):

@@ -1,100 +1,122 @@
 """Public functional API: lossless BF16 compression, decompression and fused updates.
 
-Same names, arguments and error behaviour as the reference's ``LCT/operations.py:18-136``.
+Drop-in for the reference's ``LCT/operations.py:18-136``: same function names, argument names,
+defaults and exceptions.  Everything here is routing; the work happens in ``codec/`` and, below
+that, in the CUDA library.
+
+    fused forms (A compressed, result dense or compressed):
+        compA_add_B       A + B                      bf16 add
+        compA_mul_B       A * B                      bf16 multiply
+        a_compA_add_B     a*A + B                    fp32 fma, one rounding
+        a_compA_add_b_B   a*A + b*B                  fp32 (B*b), fma, one rounding
+        a_compA_add_compB a*A + B, both compressed   fp32 fma, one rounding
 """
 from __future__ import annotations
 
 import torch
 from torch import Tensor
 
-from .codec.decode import decode as decode_dense
-from .codec.encode import encode as compress_dense
-from .codec.pointwise import (
-    ADD, MULTIPLY, SCALAR_MUL_ADD, pointwise_compressed_dense, pointwise_scale_add_compressed,
-)
+from .codec import decode as _decode, encode as _encode, pointwise as _pointwise
 from .comp_format import Distribution, StorageLayout
 from .comp_tensor import CompressedTensor
 from .tensor_buffer import TensorBuffer
 
 
+def _need_tensor(value, name: str) -> None:
+    if not isinstance(value, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+
+
+def _need_device_scalar(value, name: str, device: torch.device) -> None:
+    _need_tensor(value, name)
+    if value.numel() != 1 or value.dtype != torch.float32 or value.device != device:
+        raise ValueError(f"{name} must be a float32 scalar on the compressed tensor's device")
+
+
+def _need_matching_inner(A: Tensor, inner: int) -> None:
+    if A.ndim != 2 or A.shape[1] != inner:
+        raise ValueError("activation and weight inner dimensions must match")
+
+
+def _dense_operand(A_comp, B, operation, where, **scalars):
+    """All ``compA (op) dense B`` forms: ``where`` carries dense_output / buffer / distribution."""
+    return _pointwise.pointwise_compressed_dense(A_comp, B, operation, **scalars, **where)
+
+
+# ---- codec -------------------------------------------------------------------------------
+
 @torch.compiler.disable
 def compress(data: Tensor, distribution: Distribution | None = None,
              buffer: TensorBuffer | None = None, allow_raw: bool = False) -> CompressedTensor:
-    """Losslessly encode the exponent bytes of a CUDA bfloat16 tensor."""
-    if distribution is None:
-        distribution = Distribution()
-    return compress_dense(data.detach(), distribution, buffer, allow_raw=allow_raw)
+    """Losslessly encode the exponent bytes of a CUDA bfloat16 tensor (any shape).  With a
+    ``buffer`` the overflow tails share its arena and nothing synchronises the host."""
+    return _encode.encode(data.detach(), distribution if distribution is not None else Distribution(),
+                          buffer, allow_raw=allow_raw)
 
 
 @torch.compiler.disable
 def decompress(data: CompressedTensor) -> Tensor:
-    """Decode a tensor produced by :func:`compress` (bit-exact)."""
-    if data.layout == StorageLayout.COMPRESSED:
-        return decode_dense(data)
-    return data.data.reshape(data.shape)
+    """The original tensor, bit for bit."""
+    if data.layout != StorageLayout.COMPRESSED:      # RAW: the dense source was kept
+        return data.data.reshape(data.shape)
+    return _decode.decode(data)
+
+
+# ---- matrix products through a decoded weight ----------------------------------------------
+
+def A_compB(A: Tensor, B_comp: CompressedTensor) -> Tensor:
+    """``A @ B_comp``."""
+    _need_matching_inner(A, B_comp.shape[0])
+    return A.contiguous() @ decompress(B_comp)
 
 
 def A_compBT(A: Tensor, B_comp: CompressedTensor) -> Tensor:
     """``A @ B_comp.T``."""
-    if A.ndim != 2 or A.shape[1] != B_comp.shape[1]:
-        raise ValueError("activation and weight inner dimensions must match")
+    _need_matching_inner(A, B_comp.shape[1])
     return A.contiguous() @ decompress(B_comp).T
 
 
-def A_compB(A: Tensor, B_comp: CompressedTensor) -> Tensor:
-    """``A @ B_comp``."""
-    if A.ndim != 2 or A.shape[1] != B_comp.shape[0]:
-        raise ValueError("activation and weight inner dimensions must match")
-    return A.contiguous() @ decompress(B_comp)
-
+# ---- fused operations ------------------------------------------------------------------------
 
 def compA_add_B(A_comp: CompressedTensor, B: Tensor, *, dense_output: bool = True,
                 buffer: TensorBuffer | None = None, distribution=None):
-    """``A + B`` with A compressed."""
-    return pointwise_compressed_dense(A_comp, B, ADD, dense_output=dense_output, buffer=buffer,
-                                      distribution=distribution)
+    where = dict(dense_output=dense_output, buffer=buffer, distribution=distribution)
+    return _dense_operand(A_comp, B, _pointwise.ADD, where)
 
 
 def compA_mul_B(A_comp: CompressedTensor, B: Tensor, *, dense_output: bool = True,
                 buffer: TensorBuffer | None = None, distribution=None):
-    """``A * B`` elementwise with A compressed."""
-    return pointwise_compressed_dense(A_comp, B, MULTIPLY, dense_output=dense_output,
-                                      buffer=buffer, distribution=distribution)
+    where = dict(dense_output=dense_output, buffer=buffer, distribution=distribution)
+    return _dense_operand(A_comp, B, _pointwise.MULTIPLY, where)
 
 
 def a_compA_add_B(A_comp: CompressedTensor, a: Tensor, B: Tensor, *, alpha_is_one: bool = False,
                   dense_output: bool = True, buffer: TensorBuffer | None = None,
                   distribution=None):
-    """``a * A + B`` (float32 fma, one rounding to BF16).  ``alpha_is_one`` skips reading ``a``."""
-    if not isinstance(a, torch.Tensor):
-        raise TypeError("alpha must be a torch.Tensor")
-    return pointwise_compressed_dense(
-        A_comp, B, SCALAR_MUL_ADD, alpha=a, alpha_is_one=alpha_is_one, dense_output=dense_output,
-        buffer=buffer, distribution=distribution)
+    """``alpha_is_one`` makes it ``A + B`` in fp32 without reading ``a``."""
+    _need_tensor(a, "alpha")
+    where = dict(dense_output=dense_output, buffer=buffer, distribution=distribution)
+    return _dense_operand(A_comp, B, _pointwise.SCALAR_MUL_ADD, where, alpha=a,
+                          alpha_is_one=alpha_is_one)
 
 
 def a_compA_add_b_B(A_comp: CompressedTensor, a: Tensor, B: Tensor, b: Tensor, *,
                     alpha_is_one: bool = False, dense_output: bool = True,
                     buffer: TensorBuffer | None = None, distribution=None):
-    """``a * A + b * B``: ``B * b`` rounded to float32, then ``fma(A, a, .)``, then BF16.
-    With ``alpha_is_one`` the result is ``fma(B, b, A)``."""
-    for name, scalar in (("alpha", a), ("beta", b)):
-        if not isinstance(scalar, torch.Tensor):
-            raise TypeError(f"{name} must be a torch.Tensor")
-        if (scalar.numel() != 1 or scalar.dtype != torch.float32
-                or scalar.device != A_comp.data.device):
-            raise ValueError(
-                f"{name} must be a float32 scalar on the compressed tensor's device")
-    return pointwise_compressed_dense(
-        A_comp, B, SCALAR_MUL_ADD, alpha=a, beta=b, alpha_is_one=alpha_is_one,
-        dense_output=dense_output, buffer=buffer, distribution=distribution)
+    """``B*b`` is rounded to fp32 first, then ``fma(A, a, .)``; with ``alpha_is_one`` the result
+    is ``fma(B, b, A)``."""
+    device = A_comp.data.device
+    _need_device_scalar(a, "alpha", device)
+    _need_device_scalar(b, "beta", device)
+    where = dict(dense_output=dense_output, buffer=buffer, distribution=distribution)
+    return _dense_operand(A_comp, B, _pointwise.SCALAR_MUL_ADD, where, alpha=a, beta=b,
+                          alpha_is_one=alpha_is_one)
 
 
 def a_compA_add_compB(A_comp: CompressedTensor, a: Tensor, B_comp: CompressedTensor, *,
                       dense_output: bool = True, buffer: TensorBuffer | None = None,
                       distribution=None):
-    """``a * A + B`` with both operands compressed, decoded and combined in one launch."""
-    if not isinstance(a, torch.Tensor):
-        raise TypeError("alpha must be a torch.Tensor")
-    return pointwise_scale_add_compressed(A_comp, B_comp, a, dense_output=dense_output,
-                                          buffer=buffer, distribution=distribution)
+    """Both operands decoded and combined in one launch."""
+    _need_tensor(a, "alpha")
+    return _pointwise.pointwise_scale_add_compressed(
+        A_comp, B_comp, a, dense_output=dense_output, buffer=buffer, distribution=distribution)

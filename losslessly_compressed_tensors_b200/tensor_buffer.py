@@ -19,26 +19,25 @@ _ALIGNMENT = 16
 
 @dataclass(frozen=True)
 class Allocation:
-    """A device ``[offset, aligned_size, status, generation]`` descriptor and its arena."""
+    """A device ``[offset, aligned_size, status, generation]`` descriptor and its arena.
+    ``offset``, ``size``, ``status`` and ``generation`` are 0-dim views of the four words
+    (reading their values synchronises; handing them to kernels does not)."""
 
     descriptor: torch.Tensor
     owner: object
 
-    @property
-    def offset(self) -> torch.Tensor:
-        return self.descriptor[0]
 
-    @property
-    def size(self) -> torch.Tensor:
-        return self.descriptor[1]
+def _descriptor_word(index: int, name: str) -> property:
+    def read(self: Allocation) -> torch.Tensor:
+        return self.descriptor[index]
 
-    @property
-    def status(self) -> torch.Tensor:
-        return self.descriptor[2]
+    read.__name__ = name
+    return property(read)
 
-    @property
-    def generation(self) -> torch.Tensor:
-        return self.descriptor[3]
+
+for _index, _name in enumerate(("offset", "size", "status", "generation")):
+    setattr(Allocation, _name, _descriptor_word(_index, _name))
+del _index, _name
 
 
 @torch.library.custom_op("lct::tensor_buffer_free", mutates_args=("storage", "descriptor"))
@@ -163,41 +162,44 @@ def _free_regions_snapshot(buffer: TensorBuffer) -> list[tuple[int, int]]:
 
 
 def verify_buffer(buffer: TensorBuffer) -> None:
-    """Synchronise and check the free list: sorted, in range, non-empty, coalesced."""
-    end_of_previous = 0
-    free_bytes = 0
-    for start, size in _free_regions_snapshot(buffer):
-        if size <= 0 or start < end_of_previous or start + size > buffer.capacity_bytes:
-            raise RuntimeError(f"invalid free region: [{start}, {start + size})")
-        if start == end_of_previous and end_of_previous != 0:
+    """Synchronise and check the free list: regions sorted, inside the payload, non-empty, and
+    no two of them touching (a free must have merged them)."""
+    regions = _free_regions_snapshot(buffer)
+    cursor = 0
+    for index, (start, size) in enumerate(regions):
+        stop = start + size
+        if size <= 0 or start < cursor or stop > buffer.capacity_bytes:
+            raise RuntimeError(f"invalid free region: [{start}, {stop})")
+        if index and start == cursor:
             raise RuntimeError("adjacent free regions were not coalesced")
-        end_of_previous = start + size
-        free_bytes += size
-    if free_bytes > buffer.capacity_bytes:
+        cursor = stop
+    if sum(size for _, size in regions) > buffer.capacity_bytes:
         raise RuntimeError("free regions exceed payload capacity")
 
 
 def visualize_buffer(buffer: TensorBuffer | None, width: int = 80) -> str:
-    """Synchronise and draw the payload as ``#`` (used) and ``.`` (free) cells."""
+    """Synchronise and draw the payload as a strip of ``width`` cells: ``#`` where bytes are in
+    use, ``.`` where a cell touches a free region, followed by the free list."""
     if buffer is None:
         return ""
     if width < 8:
         raise ValueError("width must be at least 8")
     capacity = buffer.capacity_bytes
     free = _free_regions_snapshot(buffer)
-    used = capacity - sum(size for _, size in free)
-    cells = ["#"] * width
+    strip = bytearray(b"#" * width)
     for start, size in free:
         first = start * width // capacity
-        last = ((start + size) * width + capacity - 1) // capacity
-        for cell in range(first, min(width, max(first + 1, last))):
-            cells[cell] = "."
-    spans = [f"[{start}, {start + size})" for start, size in free]
-    if len(spans) > 8:
-        spans = spans[:4] + ["..."] + spans[-4:]
+        past = -(-(start + size) * width // capacity)          # ceiling
+        for cell in range(first, min(width, max(first + 1, past))):
+            strip[cell] = ord(".")
+    in_use = capacity - sum(size for _, size in free)
+    listed = [f"[{start}, {start + size})" for start, size in free]
+    if len(listed) > 8:
+        listed[4:-4] = ["..."]
     return "\n".join((
-        f"payload: {used}/{capacity} B used ({used / capacity:.1%}); {len(free)} free region(s)",
-        f"0 [{''.join(cells)}] {capacity}",
-        "# used  . free",
-        f"free: {', '.join(spans) or 'none'}",
+        f"arena payload {in_use} of {capacity} B in use ({in_use / capacity:.1%}), "
+        f"{len(free)} free region(s)",
+        f"0 |{strip.decode()}| {capacity}",
+        "legend: # in use, . free",
+        "free regions: " + (", ".join(listed) if listed else "none"),
     ))
