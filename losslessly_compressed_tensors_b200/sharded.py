@@ -389,7 +389,10 @@ class PeerWire:
     allocation per rank, mapped into every peer over NVLink), each rank encodes into its own,
     and ``decode_all(plan, peer.buffers, ..., interleave_from=rank + 1)`` decodes every shard
     by plain loads from the owner's memory - the transfer is the decoder's own input stream, so
-    it overlaps the decoding instead of preceding it, and no gathered copy exists.  ``fence()``
+    it overlaps the decoding instead of preceding it, and no gathered copy exists.  Measured on
+    B200s: faster than all-gather + decode between two GPUs (0.28 ms against 0.38 ms for a
+    124 M-parameter set), slower across eight (0.55 ms against 0.43 ms: the decoder's 32-byte
+    side-byte requests use NVLink at half the rate of NCCL's bulk copies).  ``fence()``
     orders the ranks on their streams (a one-element all-reduce): call it after encoding and
     before decoding, and again before the buffers are written the next time.
 
