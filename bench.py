@@ -266,32 +266,40 @@ def peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup) -> dict:
     except Exception as error:  # symmetric memory not available on this box / build
         return {"unavailable": f"{type(error).__name__}: {error}"[:200]}
     restored = [torch.empty(s, dtype=torch.bfloat16, device="cuda") for _, s in shapes]
-    encode, decode = [], []
-    for it in range(warmup + steps):
-        barrier(world)
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record()
-        sharded.encode_rank(plan, rank, tensors, wire=peer.local)
-        e[1].record()
-        peer.fence()                       # every rank's wire is complete
-        sharded.decode_all(plan, peer.buffers, [s for _, s in shapes], outputs=restored,
-                           interleave_from=rank + 1)
-        e[2].record()
-        peer.fence()                       # nobody still reads what the next step overwrites
-        torch.cuda.synchronize()
-        if it >= warmup:
-            encode.append(e[0].elapsed_time(e[1]))
-            decode.append(e[1].elapsed_time(e[2]))
-    exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors, restored))
     dense_bytes = 2 * sum(t.numel() for t in tensors)
-    decode_ms = max_over_ranks(statistics.mean(decode), world)
-    return {
-        "bit_exact": bool(exact), "multicast_bound": peer.multicast,
-        "encode_ms": max_over_ranks(statistics.mean(encode), world),
-        "fence_and_decode_all_ms": decode_ms,
-        "decode_gbps_aggregate": world * dense_bytes / decode_ms / 1e6,
-        "note": "replaces all_gather_ms + decode_all_ms above",
-    }
+    result = {"multicast_bound": peer.multicast, "note": "replaces all_gather_ms + decode_all_ms above"}
+    # Direct: the decoder's own loads cross NVLink.  Staged: every CTA first copies its block's
+    # side bytes into local scratch with 16-byte requests and decodes from the copy.
+    for name, stage_for in (("direct", None), ("staged", rank)):
+        encode, decode = [], []
+        for it in range(warmup + steps):
+            barrier(world)
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            sharded.encode_rank(plan, rank, tensors, wire=peer.local)
+            e[1].record()
+            peer.fence()                       # every rank's wire is complete
+            sharded.decode_all(plan, peer.buffers, [s for _, s in shapes], outputs=restored,
+                               interleave_from=rank + 1, stage_remote_for=stage_for)
+            e[2].record()
+            peer.fence()                       # nobody still reads what the next step overwrites
+            torch.cuda.synchronize()
+            if it >= warmup:
+                encode.append(e[0].elapsed_time(e[1]))
+                decode.append(e[1].elapsed_time(e[2]))
+        exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16))
+                    for a, b in zip(tensors, restored))
+        decode_ms = max_over_ranks(statistics.mean(decode), world)
+        leg = {"bit_exact": bool(exact), "encode_ms": max_over_ranks(statistics.mean(encode), world),
+               "fence_and_decode_all_ms": decode_ms,
+               "decode_gbps_aggregate": world * dense_bytes / decode_ms / 1e6}
+        if name == "direct":
+            result.update(leg)
+        else:
+            result["side_bytes_staged"] = leg
+        for t in restored:
+            t.zero_()
+    return result
 
 
 def arena_leg(batches: int = 3) -> dict:

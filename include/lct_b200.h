@@ -242,6 +242,11 @@ typedef struct lct_decode_job {
   int64_t size;          /* padded element count */
   int64_t logical_numel;
   int64_t first_block;   /* sum of the earlier jobs' block counts */
+  uint8_t *side_stage;   /* NULL, or uint8[size] scratch in THIS GPU's memory (16-byte aligned):
+                            every CTA first copies its block's side bytes there with 16-byte
+                            accesses and decodes from the copy.  For operands that live in a
+                            peer GPU's memory: the decoder's own side-byte loads are 32 bytes
+                            per warp and row, which uses NVLink at half the rate of full lines. */
 } lct_decode_job;
 
 int lct_decode_batch(const lct_decode_job *jobs /* device */, int n_jobs, int64_t total_blocks,

@@ -129,6 +129,23 @@ __device__ __forceinline__ int find_job(const Job* jobs, int n_jobs, int64_t blo
   return lo;
 }
 
+// Operand in a peer GPU's memory: bring one block's side bytes over in full 16-byte requests
+// (four in flight per thread) so that the decoder reads a local copy.  `chunks` (2048 or 4096)
+// is a multiple of 4 * kThreads.  Not inlined: its registers are dead before the decoder starts.
+static __device__ __noinline__ void stage_side_bytes(const uint8_t* __restrict__ from_bytes,
+                                                     uint8_t* __restrict__ to_bytes, int chunks) {
+  const uint4* from = reinterpret_cast<const uint4*>(from_bytes);
+  uint4* to = reinterpret_cast<uint4*>(to_bytes);
+  for (int i = threadIdx.x; i < chunks; i += 4 * kThreads) {
+    uint4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = __ldcs(from + i + k * kThreads);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) to[i + k * kThreads] = v[k];
+  }
+  __syncthreads();  // the copy is read by other threads of this CTA only
+}
+
 __global__ void __launch_bounds__(kThreads, LCT_DECODE_MIN_CTAS)
 decode_batch_kernel(const lct_decode_job* __restrict__ jobs, int n_jobs, Shape common) {
   const int64_t block = blockIdx.x;
@@ -138,8 +155,14 @@ decode_batch_kernel(const lct_decode_job* __restrict__ jobs, int n_jobs, Shape c
   g.logical_numel = job.logical_numel;
   g.n_blocks = job.size / common.block_symbols;
   g.streams = g.n_blocks * kLanes;
-  decode_block(view_of_job(job.operand), g, reinterpret_cast<uint16_t*>(job.out),
-               block - job.first_block);
+  OperandView view = view_of_job(job.operand);
+  const int64_t local_block = block - job.first_block;
+  if (job.side_stage != nullptr) {
+    const int64_t base = local_block * (int64_t)g.block_symbols;
+    stage_side_bytes(view.side + base, job.side_stage + base, g.block_symbols / 16);
+    view.side = job.side_stage;
+  }
+  decode_block(view, g, reinterpret_cast<uint16_t*>(job.out), local_block);
 }
 
 // ---------------------------------------------------------------------------

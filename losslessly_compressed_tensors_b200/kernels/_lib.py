@@ -41,7 +41,7 @@ class DecodeJob(ctypes.Structure):
     """``struct lct_decode_job``."""
 
     _fields_ = [("operand", Operand), ("out", _p), ("size", _i64), ("logical_numel", _i64),
-                ("first_block", _i64)]
+                ("first_block", _i64), ("side_stage", _p)]
 
 
 class EncodeJob(ctypes.Structure):

@@ -449,15 +449,24 @@ def compress_batch(jobs: list[dict], encode_table, decode_table, buffer, **geome
 
 class DecodeBatch:
     """A prepared multi-tensor decode (one launch per ``run``).  Each job is
-    ``(operand, output int16 tensor, size, logical_numel)``."""
+    ``(operand, output int16 tensor, size, logical_numel)`` with an optional fifth element: a
+    local uint8 tensor of ``size`` bytes through which the job's side bytes are staged (for
+    operands in a peer GPU's memory)."""
 
     def __init__(self, jobs: list[tuple], *, block_symbols, lanes, steps, fixed_words, rare_length):
         self.device = _require_cuda(jobs[0][1])
         records = (DecodeJob * len(jobs))()
         first = 0
-        for record, (operand, output, size, logical_numel) in zip(records, jobs):
+        for record, job in zip(records, jobs):
+            operand, output, size, logical_numel = job[:4]
+            stage = job[4] if len(job) > 4 else None
             if output.data_ptr() % 16:
                 raise ValueError("batched decode needs 16-byte aligned outputs")
+            if stage is not None:
+                if stage.numel() < size or stage.data_ptr() % 16 or stage.device != output.device:
+                    raise ValueError("side-byte stage must be a local, 16-byte aligned tensor of "
+                                     "at least `size` bytes")
+                record.side_stage = stage.data_ptr()
             record.operand = operand
             record.out = output.data_ptr()
             record.size = size

@@ -308,6 +308,10 @@ def views_of(plan: Plan, gathered) -> list[tuple[Shard, CompressedTensor]]:
     """Rebuild a ``CompressedTensor`` for every shard of every rank as views of the wire bytes:
     ``gathered`` is the all-gathered buffer, or a list with every rank's wire buffer (which may
     live in peer GPUs' memory, see ``PeerWire``).  Rank-major order."""
+    return [(shard, compressed) for _, shard, compressed in _views_with_rank(plan, gathered)]
+
+
+def _views_with_rank(plan: Plan, gathered) -> list[tuple[int, Shard, CompressedTensor]]:
     from .tensor_buffer import TensorBuffer
 
     metadata = TensorBuffer.storage_bytes(0, plan.max_free_regions)
@@ -316,7 +320,7 @@ def views_of(plan: Plan, gathered) -> list[tuple[Shard, CompressedTensor]]:
         arena_start = plan.arena_offset[rank] + metadata
         arena_payload = wire[arena_start:arena_start + plan.arena_capacity]
         for shard, slots in zip(plan.shards[rank], plan.offsets[rank]):
-            result.append((shard, _compressed_view(plan, wire, shard, slots, arena_payload)))
+            result.append((rank, shard, _compressed_view(plan, wire, shard, slots, arena_payload)))
     return result
 
 
@@ -337,13 +341,16 @@ def _interleaved(plan: Plan, views: list, first_rank: int) -> list:
 
 
 def decode_all(plan: Plan, gathered, shapes: list[tuple[int, ...]], *, batched: bool = True,
-               outputs: list[torch.Tensor] | None = None, interleave_from: int | None = None):
+               outputs: list[torch.Tensor] | None = None, interleave_from: int | None = None,
+               stage_remote_for: int | None = None):
     """Decode every shard from the wire bytes and reassemble the weight set.  ``gathered``: the
     all-gathered buffer, or a list of per-rank wire buffers (``PeerWire.buffers``: the decoder
     then reads the other ranks' bytes straight from their memory, no collective).  ``batched``
     decodes all shards with one launch, straight into their rows of the output tensors;
     ``outputs`` reuses existing BF16 tensors of the given shapes; ``interleave_from`` orders the
-    launch's jobs round-robin over the source ranks starting at that rank."""
+    launch's jobs round-robin over the source ranks starting at that rank; ``stage_remote_for``
+    (this rank's number, with peer buffers) makes every CTA copy the side bytes of a shard that
+    another rank owns into local scratch with full-width requests before it decodes them."""
     from .codec.decode import operand_of
     from .compression.huffman_tables import get_distribution_tables
     from .kernels import dispatch
@@ -353,22 +360,30 @@ def decode_all(plan: Plan, gathered, shapes: list[tuple[int, ...]], *, batched: 
     device = wires[0].device
     if outputs is None:
         outputs = [torch.empty(shape, dtype=torch.bfloat16, device=device) for shape in shapes]
-    key = ("decode", batched, interleave_from, tuple(w.data_ptr() for w in wires),
-           tuple(t.data_ptr() for t in outputs))
+    key = ("decode", batched, interleave_from, stage_remote_for,
+           tuple(w.data_ptr() for w in wires), tuple(t.data_ptr() for t in outputs))
     hit = plan.prepared.get(key)
     if hit is not None:
         hit.run()
         return outputs
-    views = views_of(plan, wires)
+    views = _views_with_rank(plan, wires)
     if interleave_from is not None:
         views = _interleaved(plan, views, interleave_from % plan.world)
+    stage, stage_at = None, 0
+    if stage_remote_for is not None and batched:
+        remote_bytes = sum(c.size for rank, _, c in views if rank != stage_remote_for)
+        stage = torch.empty(max(remote_bytes, 16), dtype=torch.uint8, device=device)
     jobs, direct = [], True
-    for shard, compressed in views:
+    for rank, shard, compressed in views:
         target = outputs[shard.index]
         rows = target.reshape(()) if target.dim() == 0 else target[shard.row_start:shard.row_stop]
         flat = rows.view(-1).view(torch.int16) if rows.dim() else rows.reshape(1).view(torch.int16)
         if batched and flat.numel() and flat.data_ptr() % 16 == 0:
-            jobs.append((operand_of(compressed), flat, compressed.size, flat.numel()))
+            job = (operand_of(compressed), flat, compressed.size, flat.numel())
+            if stage is not None and rank != stage_remote_for:
+                job += (stage[stage_at:stage_at + compressed.size],)   # sizes are block multiples
+                stage_at += compressed.size
+            jobs.append(job)
         elif flat.numel():
             direct = False
             rows.copy_(decompress(compressed).reshape(rows.shape))
@@ -391,8 +406,9 @@ class PeerWire:
     by plain loads from the owner's memory - the transfer is the decoder's own input stream, so
     it overlaps the decoding instead of preceding it, and no gathered copy exists.  Measured on
     B200s: faster than all-gather + decode between two GPUs (0.28 ms against 0.38 ms for a
-    124 M-parameter set), slower across eight (0.55 ms against 0.43 ms: the decoder's 32-byte
-    side-byte requests use NVLink at half the rate of NCCL's bulk copies).  ``fence()``
+    124 M-parameter set); across eight 0.56 ms against 0.43 ms as it is (the decoder's 32-byte
+    side-byte requests use NVLink at half the rate of NCCL's bulk copies) and 0.40 ms with
+    ``stage_remote_for=rank``, which is the form to use from four ranks on.  ``fence()``
     orders the ranks on their streams (a one-element all-reduce): call it after encoding and
     before decoding, and again before the buffers are written the next time.
 

@@ -41,11 +41,14 @@ def main():
         sharded.encode_rank(plan, rank, tensors, wire=peer.local)
         peer.fence()
         from_peers = sharded.decode_all(plan, peer.buffers, shapes, interleave_from=rank + 1)
+        staged = sharded.decode_all(plan, peer.buffers, shapes, interleave_from=rank + 1,
+                                    stage_remote_for=rank)   # side bytes through local scratch
         gathered = sharded.all_gather_wire(peer.local.clone(), plan)
         from_gather = sharded.decode_all(plan, gathered, shapes)
         peer.fence()
-        for want, a, b in zip(tensors, from_peers, from_gather):
+        for want, a, b, c in zip(tensors, from_peers, from_gather, staged):
             assert torch.equal(a.view(torch.int16), want.view(torch.int16)), (rank, step)
+            assert torch.equal(c.view(torch.int16), want.view(torch.int16)), (rank, step)
             assert torch.equal(b.view(torch.int16), want.view(torch.int16)), (rank, step)
     torch.cuda.synchronize()
     dist.barrier()

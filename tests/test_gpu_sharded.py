@@ -106,6 +106,11 @@ def test_decode_from_per_rank_buffers_matches_the_gathered_path(world, row_shard
         restored = sharded.decode_all(plan, wires, shapes, interleave_from=interleave)
         for want, got in zip(host, restored):
             assert np.array_equal(bits_of(got), bits_of(want))
+    # side bytes of the shards that rank `start % world` does not own go through local scratch
+    staged = sharded.decode_all(plan, wires, shapes, interleave_from=start,
+                                stage_remote_for=start % world)
+    for want, got in zip(host, staged):
+        assert np.array_equal(bits_of(got), bits_of(want))
     # same launch prepared once per set of buffers, reused on the second call
     before = len(plan.prepared)
     sharded.decode_all(plan, wires, shapes, outputs=restored, interleave_from=start)
