@@ -38,9 +38,10 @@ constexpr int kFirstMask = 1023;        // the codebook's first-level table cove
 constexpr int kSampleCount = 4096;     // positions the exponent center is estimated from
 
 // Two-symbol table entry: byte0 = first symbol, byte1 = second symbol,
-// byte2 = bits consumed by the symbols present, byte3 = length of the first
-// symbol | flags.  kSlow marks every entry that is not two directly coded
-// symbols (the sign bit, so one signed compare finds it).
+// byte2 = length of the first symbol (of prefix + literal for an escape), byte3 = bits consumed by both symbols
+// (so that "position += entry >> 24" is one shift-and-add instruction), or the
+// flags of an entry that is not two directly coded symbols: kSlow (the sign
+// bit, so one signed compare finds it) and kEscape.
 constexpr uint32_t kSlow = 0x80000000u;
 constexpr uint32_t kEscape = 0x40000000u;
 

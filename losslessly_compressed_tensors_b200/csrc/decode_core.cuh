@@ -132,21 +132,27 @@ __device__ __forceinline__ uint32_t symbol_of(uint32_t entry, uint32_t bits, con
     *length = rare_length + 8;
     return sh.index_to_byte[(bits >> rare_length) & 255u];
   }
-  *length = (int)((entry >> 24) & 15u);
+  *length = (int)((entry >> 16) & 15u);
   return entry & 255u;
 }
 
 // Pair whose table entry is not "two direct symbols": take the first symbol
 // from the entry already in hand, look the second one up on its own.
-// Returns the pair in table-entry form (bytes: first, second, bits consumed).
+// Returns the pair in table-entry form (bytes: first, second, -, bits consumed).
 template <typename Reader>
 __device__ __forceinline__ uint32_t slow_pair(const Reader& r, uint32_t entry, uint32_t bits,
                                               const DecodeShared& sh, int rare_length) {
-  int l0, l1;
-  const uint32_t e0 = symbol_of(entry, bits, sh, rare_length, &l0);
-  const uint32_t bits1 = r.peek(l0);
-  const uint32_t e1 = symbol_of(sh.table[table_slot(bits1)], bits1, sh, rare_length, &l1);
-  return e0 | (e1 << 8) | ((uint32_t)(l0 + l1) << 16);
+  // Every entry carries the length of its first symbol, escapes included, so the second
+  // lookup does not wait for an escape test; literals are patched in afterwards.
+  const uint32_t l0 = (entry >> 16) & 31u;
+  const uint32_t bits1 = r.peek((int)l0);
+  const uint32_t second = sh.table[table_slot(bits1)];
+  uint32_t e0 = entry & 255u, e1 = second & 255u;
+  if ((entry | second) & kEscape) {
+    if (entry & kEscape) e0 = sh.index_to_byte[(bits >> rare_length) & 255u];
+    if (second & kEscape) e1 = sh.index_to_byte[(bits1 >> rare_length) & 255u];
+  }
+  return e0 | (e1 << 8) | ((l0 + ((second >> 16) & 31u)) << 24);
 }
 
 // Lane phase for one tile.  `coded` = number of leading steps of this lane that
@@ -166,7 +172,7 @@ __device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& 
       uint32_t entry = sh.table[table_slot(bits)];
       if ((int32_t)entry < 0) entry = slow_pair(r, entry, bits, sh, rare_length);
       tile[p * 32 + (lane32 ^ ((2 * p) & lane_mask))] = (uint16_t)entry;
-      r.advance((int)prmt(entry, 0, 0x4442));
+      r.advance((int)(entry >> 24));
     }
     return;
   }
@@ -177,7 +183,7 @@ __device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& 
       const uint32_t bits = r.peek0();
       pair = sh.table[table_slot(bits)];
       if ((int32_t)pair < 0) pair = slow_pair(r, pair, bits, sh, rare_length);
-      r.advance((int)prmt(pair, 0, 0x4442));
+      r.advance((int)(pair >> 24));
     } else if (step >= tail_from) {
       const uint32_t t0 = tail_bytes[step - tail_from], t1 = tail_bytes[step + 1 - tail_from];
       pair = ((t0 + 127u) & 255u) | (((t1 + 127u) & 255u) << 8);

@@ -96,14 +96,18 @@ __device__ __forceinline__ UnitSource load_unit(const void* src, int64_t at, int
 
 // One codec block.  extra_starts and summaries are the tensor's own arrays
 // (summaries holds g.n_blocks entries per row).
-template <bool kPrecomputed>
+// kLaneMask: the lane mapping as a compile-time constant (254, the default mapping), or -1 to
+// take it from the shape at run time.
+template <bool kPrecomputed, int kLaneMask>
 __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool src_vector_ok,
                                              uint8_t* __restrict__ side,
                                              uint32_t* __restrict__ encoded,
                                              const int32_t* __restrict__ shifted_encode,
                                              uint8_t* __restrict__ extra_starts,
-                                             int32_t* __restrict__ summaries, const EncodeShape& g,
+                                             int32_t* __restrict__ summaries, const EncodeShape& g_in,
                                              int64_t block) {
+  EncodeShape g = g_in;
+  if (kLaneMask >= 0) g.lane_mask = kLaneMask;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   EncodeSharedHead& sh = *reinterpret_cast<EncodeSharedHead*>(smem_raw);
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw + sizeof(EncodeSharedHead));
@@ -240,13 +244,13 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   }
 }
 
-template <bool kPrecomputed>
+template <bool kPrecomputed, int kLaneMask>
 __global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
 encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
               uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
               uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
-  encode_block<kPrecomputed>(src, src_vector_ok, side, encoded, shifted_encode, extra_starts,
-                             summaries, g, blockIdx.x);
+  encode_block<kPrecomputed, kLaneMask>(src, src_vector_ok, side, encoded, shifted_encode,
+                                        extra_starts, summaries, g, blockIdx.x);
 }
 
 // Shape of one job of a batch (all jobs share the geometry in `common`).
@@ -269,6 +273,7 @@ __device__ __forceinline__ int find_encode_job(const lct_encode_job* jobs, int n
   return lo;
 }
 
+template <int kLaneMask>
 __global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
 encode_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs,
                     const int32_t* __restrict__ shifted_encode, uint8_t* __restrict__ extra_starts,
@@ -278,9 +283,11 @@ encode_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs,
   const lct_encode_job& job = jobs[j];
   const EncodeShape g = shape_of_job(job, common);
   const bool vector_ok = (reinterpret_cast<uintptr_t>(job.src) & 15u) == 0;
-  encode_block<false>(job.src, vector_ok, job.side, reinterpret_cast<uint32_t*>(job.encoded),
-                      shifted_encode + 256 * (int64_t)j, extra_starts + job.first_block * kLanes,
-                      summaries + 4 * job.first_block, g, block - job.first_block);
+  encode_block<false, kLaneMask>(job.src, vector_ok, job.side,
+                                 reinterpret_cast<uint32_t*>(job.encoded),
+                                 shifted_encode + 256 * (int64_t)j,
+                                 extra_starts + job.first_block * kLanes,
+                                 summaries + 4 * job.first_block, g, block - job.first_block);
 }
 
 // Compact overflow metadata and raw exponent tails of one block.  Lanes are
@@ -417,7 +424,9 @@ static int launch_encode(const void* src, uint8_t* side, int32_t* encoded,
   const bool vector_ok = (s & (precomputed ? 7u : 15u)) == 0;
   const size_t shared = sizeof(lct::EncodeSharedHead) + (size_t)fixed_words * lct::kLanes * 4;
   uint32_t* words = reinterpret_cast<uint32_t*>(encoded);
-  auto kernel = precomputed ? lct::encode_kernel<true> : lct::encode_kernel<false>;
+  const bool swizzled = g.lane_mask == 254;
+  auto kernel = precomputed ? (swizzled ? lct::encode_kernel<true, 254> : lct::encode_kernel<true, -1>)
+                            : (swizzled ? lct::encode_kernel<false, 254> : lct::encode_kernel<false, -1>);
   rc = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   if (rc) return rc;
   if (overlapped)
@@ -534,12 +543,12 @@ int lct_compress_batch(const lct_encode_job* jobs, int n_jobs, int64_t total_blo
   if ((rc = lct::launch_center_batch(jobs, n_jobs, encode_table, decode_table, shifted_encode, st)))
     return rc;
   const size_t shared = sizeof(lct::EncodeSharedHead) + (size_t)fixed_words * lct::kLanes * 4;
-  rc = (int)cudaFuncSetAttribute(lct::encode_batch_kernel,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+  auto encode_all = g.lane_mask == 254 ? lct::encode_batch_kernel<254> : lct::encode_batch_kernel<-1>;
+  rc = (int)cudaFuncSetAttribute(encode_all, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   if (rc) return rc;
   // Centers first (ordinary launch); the three kernels behind it may each be scheduled while
   // their predecessor still runs and wait for it on the device.
-  if ((rc = lct::launch_overlapped(lct::encode_batch_kernel, (unsigned)total_blocks, lct::kThreads,
+  if ((rc = lct::launch_overlapped(encode_all, (unsigned)total_blocks, lct::kThreads,
                                    shared, st, jobs, n_jobs, shifted_encode, extra_starts,
                                    summaries, g)))
     return rc;

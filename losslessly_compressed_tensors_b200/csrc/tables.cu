@@ -147,7 +147,8 @@ shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __re
 // second symbol is present only when both codes are direct and fit in the 12
 // bits together.  The entry for stream window i is stored at table_slot(i).
 __global__ void __launch_bounds__(kTableThreads)
-pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pair_table) {
+pair_table_kernel(const int32_t* __restrict__ decode, int rare_length,
+                  uint32_t* __restrict__ pair_table) {
   const int center = (int)blockIdx.x - 128;
   uint32_t* table = pair_table + (size_t)blockIdx.x * kPairEntries;
   for (int slot = threadIdx.x; slot < kPairEntries; slot += blockDim.x) {
@@ -155,18 +156,18 @@ pair_table_kernel(const int32_t* __restrict__ decode, uint32_t* __restrict__ pai
     const int32_t first = decode[i & kFirstMask];
     uint32_t entry;
     if (first == 0) {
-      entry = kSlow | kEscape;
+      entry = kSlow | kEscape | ((uint32_t)(rare_length + 8) << 16);  // prefix + 8-bit literal
     } else {
       const uint32_t len0 = (uint32_t)first & 255u;
       const uint32_t byte0 = index_to_exponent_byte(((uint32_t)first >> 8) & 255u, center);
-      entry = byte0 | (len0 << 24);
+      entry = byte0 | (len0 << 16);
       const int32_t second = decode[(i >> len0) & kFirstMask];
       const uint32_t len1 = (uint32_t)second & 255u;
       if (second != 0 && len0 + len1 <= (uint32_t)kPairBits) {
         const uint32_t byte1 = index_to_exponent_byte(((uint32_t)second >> 8) & 255u, center);
-        entry |= byte1 << 8 | (len0 + len1) << 16;
+        entry |= byte1 << 8 | (len0 + len1) << 24;
       } else {
-        entry |= kSlow | (len0 << 16);
+        entry |= kSlow;
       }
     }
     table[slot] = entry;
@@ -202,7 +203,8 @@ int lct_build_pair_table(const int32_t* decode_table, int rare_length, uint32_t*
   if (decode_table == nullptr || pair_table == nullptr) return LCT_E_NULL_POINTER;
   if (rare_length < 0 || rare_length > 8) return LCT_E_BAD_ARGUMENT;
   lct::pair_table_kernel<<<lct::kCenterValues, lct::kTableThreads, 0,
-                           static_cast<cudaStream_t>(stream)>>>(decode_table, pair_table);
+                           static_cast<cudaStream_t>(stream)>>>(decode_table, rare_length,
+                                                                pair_table);
   return (int)cudaGetLastError();
 }
 

@@ -43,7 +43,7 @@ __device__ __forceinline__ uint32_t byte_of(uint32_t entry, uint32_t bits, int r
     *length = rare_length + 8;
     return index_to_exponent_byte((bits >> rare_length) & 255u, center);
   }
-  *length = (int)((entry >> 24) & 15u);
+  *length = (int)((entry >> 16) & 15u);
   return entry & 255u;
 }
 
@@ -89,7 +89,7 @@ __device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, 
     } else {
       first = entry & 255u;
       second = (entry >> 8) & 255u;
-      consumed = (int)((entry >> 16) & 255u);
+      consumed = (int)(entry >> 24);
     }
     r.advance(consumed);
   }
