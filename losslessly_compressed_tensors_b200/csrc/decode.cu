@@ -177,12 +177,14 @@ decode_batch_kernel(const lct_decode_job* __restrict__ jobs, int n_jobs, Shape c
 // Fused pointwise operations
 // ---------------------------------------------------------------------------
 
-template <bool kDual>
+template <bool kDual, int kLaneMask>
 __global__ void __launch_bounds__(kThreads)
-pointwise_kernel(OperandView a, OperandView b, Shape g, const uint16_t* __restrict__ other,
+pointwise_kernel(OperandView a, OperandView b, Shape g_in, const uint16_t* __restrict__ other,
                  bool other_vector_ok, void* output, uint8_t* auxiliary, OpSpec spec,
                  bool compressed) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  Shape g = g_in;
+  if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // see decode_block
   const size_t image = (size_t)(g.fixed_words + 2) * kLanes * 4;
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
   uint32_t* payload_b = reinterpret_cast<uint32_t*>(smem_raw + (kDual ? image : 0));
@@ -331,9 +333,9 @@ int lct_pointwise(const lct_operand* a, const void* other, void* output, uint8_t
   if ((reinterpret_cast<uintptr_t>(other) & 1u) != 0) return LCT_E_ALIGNMENT;
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
   const size_t shared = lct::operand_shared_bytes(fixed_words);
-  if ((rc = lct::opt_in_shared(lct::pointwise_kernel<false>, shared)) != 0) return rc;
-  lct::pointwise_kernel<false><<<(unsigned)g.n_blocks, lct::kThreads, shared,
-                                 static_cast<cudaStream_t>(stream)>>>(
+  auto kernel = g.lane_mask == 254 ? lct::pointwise_kernel<false, 254> : lct::pointwise_kernel<false, -1>;
+  if ((rc = lct::opt_in_shared(kernel, shared)) != 0) return rc;
+  kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, static_cast<cudaStream_t>(stream)>>>(
       va, va, g, static_cast<const uint16_t*>(other), lct::aligned16(other), output, auxiliary,
       spec, compressed_output != 0);
   return (int)cudaGetLastError();
@@ -356,9 +358,9 @@ int lct_dual_scale_add(const lct_operand* a, const lct_operand* b, void* output,
   // fma(a, alpha, b): the scaled operation with beta == 1.
   const lct::OpSpec spec{alpha, nullptr, LCT_OP_SCALAR_MUL_ADD, 0, 1};
   const size_t one = lct::operand_shared_bytes(fixed_words);
-  if ((rc = lct::opt_in_shared(lct::pointwise_kernel<true>, 2 * one)) != 0) return rc;
-  lct::pointwise_kernel<true><<<(unsigned)g.n_blocks, lct::kThreads, 2 * one,
-                                static_cast<cudaStream_t>(stream)>>>(
+  auto kernel = g.lane_mask == 254 ? lct::pointwise_kernel<true, 254> : lct::pointwise_kernel<true, -1>;
+  if ((rc = lct::opt_in_shared(kernel, 2 * one)) != 0) return rc;
+  kernel<<<(unsigned)g.n_blocks, lct::kThreads, 2 * one, static_cast<cudaStream_t>(stream)>>>(
       va, vb, g, nullptr, false, output, auxiliary, spec, compressed_output != 0);
   return (int)cudaGetLastError();
 }

@@ -162,13 +162,16 @@ __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint3
 // Shared memory: [input payload image | DecodeShared | encode table].  Finished output
 // words go straight to global memory (a warp's lanes write neighbouring words of the same
 // payload rows; L2 merges the sectors), which keeps four CTAs resident per SM.
+template <int kLaneMask>
 __global__ void __launch_bounds__(kThreads, 4)
-update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, bool other_vector_ok,
+update_fused_kernel(OperandView a, Shape g_in, const uint16_t* __restrict__ other, bool other_vector_ok,
                     OpSpec spec, const int32_t* __restrict__ shifted_encode,
                     uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
                     uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
                     uint8_t* __restrict__ spill) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  Shape g = g_in;
+  if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // compile-time lane mapping, see decode_block
   const size_t image = (size_t)(g.fixed_words + 2) * kLanes * 4;
   uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + image);
@@ -369,14 +372,15 @@ static int launch_fused(const lct_operand* a, const void* other, const float* al
   if (!lct::aligned16(side_out) || !lct::aligned16(encoded_out)) return LCT_E_ALIGNMENT;
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
   const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
-  if ((rc = lct::opt_in_shared(lct::update_fused_kernel, shared)) != 0) return rc;
+  auto kernel = g.lane_mask == 254 ? lct::update_fused_kernel<254> : lct::update_fused_kernel<-1>;
+  if ((rc = lct::opt_in_shared(kernel, shared)) != 0) return rc;
   const uint16_t* dense = static_cast<const uint16_t*>(other);
   uint32_t* words = reinterpret_cast<uint32_t*>(encoded_out);
   if (overlapped)
-    return lct::launch_overlapped(lct::update_fused_kernel, (unsigned)g.n_blocks, lct::kThreads,
+    return lct::launch_overlapped(kernel, (unsigned)g.n_blocks, lct::kThreads,
                                   shared, stream, va, g, dense, lct::aligned16(other), spec,
                                   shifted_encode, side_out, words, extra_starts, summaries, spill);
-  lct::update_fused_kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, stream>>>(
+  kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, stream>>>(
       va, g, dense, lct::aligned16(other), spec, shifted_encode, side_out, words, extra_starts,
       summaries, spill);
   return (int)cudaGetLastError();
