@@ -336,6 +336,45 @@ int lct_update(const lct_operand *a /* host pointer */, const void *other, const
                int64_t logical_numel, int block_symbols, int steps, int fixed_words,
                int rare_length, void *stream);
 
+/* Many compressed tensors of ONE geometry updated by one call (an optimizer
+ * step over all its parameters): the five kernels of lct_update, each launched
+ * once over all jobs - samples (16 CTAs per job), centers (one CTA per job),
+ * the fused decode -> op -> re-encode (one CTA per block of every job), the
+ * scans and arena reservations (in job order, so the arena ends up exactly as
+ * after one lct_update per job), the tail compaction.  Same bytes in the same
+ * output tensors as n_jobs calls of lct_update.  `jobs` is a DEVICE array
+ * sorted by first_block; alpha, beta, op and the codebook are common to all
+ * jobs.  Work buffers: samples uint8[4096 * n_jobs], shifted_encode
+ * int32[256 * n_jobs], extra_starts uint8[256 * total_blocks], summaries
+ * int32[4 * total_blocks] (job j uses the 4 * blocks_j ints from
+ * 4 * first_block).  No counterpart in the reference, whose optimizers update
+ * one tensor per call (LCT/components/sparse_utils.py:30-61). */
+typedef struct lct_update_job {
+  lct_operand a;                 /* the state to update */
+  const void *other;             /* dense BF16 operand, int16[logical_numel] */
+  const uint16_t *known_values;  /* NULL, or A's BF16 bits at the sample positions */
+  uint16_t *result_values;       /* NULL, or uint16[min(logical_numel, 4096)] */
+  uint8_t *side_out;             /* uint8[size] */
+  int32_t *encoded_out;          /* int32[streams*fixed_words + 4] */
+  uint8_t *spill;                /* uint8[size] work buffer */
+  int32_t *center;               /* int32[1] */
+  int32_t *shifted_decode;       /* int32[1024] */
+  int32_t *counts;               /* int32[4] */
+  int32_t *descriptor;           /* int32[4] */
+  int32_t *blocks_out;           /* int32[3*blocks] */
+  int64_t size;
+  int64_t logical_numel;
+  int64_t first_block;
+} lct_update_job;
+
+int lct_update_batch(const lct_update_job *jobs /* device */, int n_jobs, int64_t total_blocks,
+                     const float *alpha, const float *beta, int op, int alpha_is_one,
+                     int beta_is_one, const int32_t *encode_table, const int32_t *decode_table,
+                     void *arena_storage, int max_free_regions, uint8_t *samples,
+                     int32_t *shifted_encode, uint8_t *extra_starts, int32_t *summaries,
+                     int block_symbols, int steps, int fixed_words, int rare_length,
+                     void *stream);
+
 /* ---- shared overflow arena (TensorBuffer) ---------------------------------- */
 /* storage layout: int32 free_starts[R] | free_sizes[R] | free_count | lock |
  * generation | pad to 16 bytes | payload[capacity]  (LCT/tensor_buffer.py:58-82).

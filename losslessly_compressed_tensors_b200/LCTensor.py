@@ -92,6 +92,20 @@ class LCTTensor(Tensor):
             self._become(lambda old, home: ops.a_compA_add_b_B(
                 old, alpha, update, beta, alpha_is_one=alpha_is_one, **home))
 
+    @staticmethod
+    def mul_add_many_(tensors: "list[LCTTensor]", alpha: Tensor, updates: "list[Tensor]",
+                      beta: Tensor | None = None, *, alpha_is_one: bool = False) -> None:
+        """``mul_add_`` of every tensor of the list with its own update, as one call of five
+        launches for the whole list (all tensors must share the first one's codebook, geometry
+        and arena).  Same values as calling ``mul_add_`` on each; the old values' arena regions
+        are released after all new ones have been reserved."""
+        old = [tensor.x for tensor in tensors]
+        new = ops.a_compA_add_b_B_many(old, alpha, updates, beta, alpha_is_one=alpha_is_one,
+                                       buffer=old[0].buffer, distribution=old[0].distribution)
+        for tensor, value, previous in zip(tensors, new, old):
+            tensor.x = value
+            previous.free()
+
     def add_comp_(self, update_comp: "LCTTensor", alpha: Tensor):
         """``x <- x + alpha * update_comp``, both sides compressed."""
         self._become(lambda old, home: ops.a_compA_add_compB(update_comp.x, alpha, old, **home))

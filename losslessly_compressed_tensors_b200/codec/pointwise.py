@@ -164,6 +164,86 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
     return result
 
 
+def fused_update_many(datas, others, operation, result_distribution, buffer, *, alpha=None,
+                      beta=None, alpha_is_one=False):
+    """``_fused_update`` of many compressed tensors in five launches in all: every tensor of
+    ``datas`` (one codebook, one geometry, one device, none RAW or empty) is combined with its
+    dense partner in ``others`` and re-encoded into ``buffer``'s arena.  Each result holds the
+    bytes the one-tensor call gives it; the arena reservations are made in list order."""
+    if not datas or len(datas) != len(others):
+        raise ValueError("fused_update_many needs as many dense operands as compressed tensors")
+    if buffer is None or buffer.capacity_bytes % 4:
+        raise ValueError("fused_update_many needs a TensorBuffer whose capacity is divisible by 4")
+    first = datas[0]
+    device = first.data.device
+    scaled = operation.name == "scalar_mul_add"
+    if scaled and alpha is None:
+        raise ValueError("scalar_mul_add requires an alpha argument")
+    result_distribution = result_distribution or first.distribution
+    block_symbols, lanes, steps, fixed_words = first.codec_geometry
+    if geometry(result_distribution) != first.codec_geometry:
+        raise ValueError("matrix compressed output must preserve the input stream geometry")
+    alpha = _scalar(alpha, device) if scaled and not alpha_is_one else None
+    beta = _scalar(beta, device) if scaled else None
+    encode_table, decode_table, rare_length = get_distribution_tables(result_distribution, device)
+    flat = []
+    for data, other in zip(datas, others):
+        if (data.layout != StorageLayout.COMPRESSED or data.distribution != first.distribution
+                or data.codec_geometry != first.codec_geometry or data.data.device != device
+                or not data.logical_numel):
+            raise ValueError("fused_update_many needs non-empty compressed tensors of one codebook, "
+                             "geometry and device")
+        if tuple(other.shape) != data.shape:
+            raise ValueError(f"{operation.name} expects tensors with the same shape")
+        other = other.contiguous().view(-1)
+        if other.dtype != torch.bfloat16:
+            raise TypeError("the dense operand must be bfloat16")
+        flat.append(other)
+    # Every result owns its tensors (memory_size() counts storages); only the spill arrays,
+    # which nothing reads after the call, share one allocation (sizes are multiples of the
+    # 32768-element block, so every slice starts on a 16-byte boundary).
+    def new(count, dtype):
+        return torch.empty(count, dtype=dtype, device=device)
+
+    spill_pool = new(sum(d.size for d in datas), torch.uint8)
+    jobs, results = [], []
+    at = 0
+    for data, other in zip(datas, flat):
+        blocks = data.size // block_symbols
+        count = min(data.logical_numel, 4096)
+        center, counts, descriptor = new(1, torch.int32), new(4, torch.int32), new(4, torch.int32)
+        shifted_decode = new(decode_table.numel(), torch.int32)
+        blocks_out = new(3 * blocks, torch.int32)
+        side_out = new(data.size, torch.uint8)
+        encoded = new(blocks * lanes * fixed_words + 4, torch.int32)
+        values = new(count, torch.int16)
+        known = getattr(data, _SAMPLE_VALUES, None)
+        if known is not None and (known.numel() != count or known.device != device):
+            known = None
+        jobs.append(dict(operand=operand_of(data), other=other, known_values=known,
+                         result_values=values, side_out=side_out, encoded_out=encoded,
+                         spill=spill_pool[at:at + data.size], center=center,
+                         decode_table=shifted_decode, counts=counts, descriptor=descriptor,
+                         blocks=blocks_out, size=data.size, logical_numel=data.logical_numel))
+        result = CompressedTensor(
+            encoded, data.size, side_out, fallback_starts=None, fallback_lanes=None,
+            fallback_blocks=blocks_out, fallback_buffer=buffer.data,
+            fallback_descriptor=descriptor, buffer=buffer, fallback_count=counts[:1],
+            fallback_used=counts[1:2], distribution=result_distribution, center=center,
+            decode_table=shifted_decode, shape=data.shape, layout=StorageLayout.COMPRESSED,
+            stream_geometry=geometry(result_distribution),
+        )
+        object.__setattr__(result, _SAMPLE_VALUES, values)
+        results.append(result)
+        at += data.size
+    dispatch.update_batch(
+        jobs, alpha, beta, encode_table, decode_table, buffer, op=operation.code,
+        alpha_is_one=not scaled or alpha_is_one, beta_is_one=not scaled or beta is None,
+        rare_length=rare_length, block_symbols=block_symbols, lanes=lanes, steps=steps,
+        fixed_words=fixed_words)
+    return results
+
+
 def _launch_scalar_mul_add_compressed_compressed(data, other, alpha, dense_output):
     device = data.data.device
     _, _, rare_a = get_distribution_tables(data.distribution, device)

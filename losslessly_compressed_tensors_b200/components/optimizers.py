@@ -101,10 +101,20 @@ class SparseSGDM(_Base):
             torch.add(grad, state, alpha=0.9, out=state)   # the reference's dense branch (literal 0.9)
         return state
 
+    def _advance_all(self) -> bool:
+        """From the second step on, with a shared arena: every momentum advanced by one call of
+        five launches for the whole parameter list (same values as one ``mul_add_`` each)."""
+        if not (self.compressed and self.buffer is not None and len(self.params) > 1
+                and all(isinstance(m, LCTTensor) for m in self.momentums)):
+            return False
+        LCTTensor.mul_add_many_(self.momentums, self.momentum, [p.grad for p in self.params])
+        return True
+
     @torch.no_grad()
     def step(self):
+        advanced = self._advance_all()
         for index, p in enumerate(self.params):
-            state = self._advance_momentum(index, p.grad)
+            state = self.momentums[index] if advanced else self._advance_momentum(index, p.grad)
             if not self.compressed:
                 p.add_(state * self.neg_lr)
             elif isinstance(p, LCTTensor):

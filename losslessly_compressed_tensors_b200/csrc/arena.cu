@@ -162,8 +162,9 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
 // "empty request" descriptor, which is what the allocator would have written.
 constexpr int kListSlots = 1024;
 
+template <typename Job>  // lct_encode_job or lct_update_job: size, first_block, counts, descriptor
 __global__ void __launch_bounds__(kScanThreads)
-scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* summaries,
+scan_batch_kernel(const Job* __restrict__ jobs, int n_jobs, int32_t* summaries,
                   void* arena_storage, int regions, int block_symbols) {
   __shared__ int alloc_scratch[2];
   __shared__ int32_t list_starts[kListSlots], list_sizes[kListSlots];
@@ -174,7 +175,7 @@ scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* 
   cudaTriggerProgrammaticLaunchCompletion();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   for (int j = warp; j < n_jobs; j += warps) {
-    const lct_encode_job& job = jobs[j];
+    const Job& job = jobs[j];
     const int64_t blocks = job.size / block_symbols;
     int32_t* rows = summaries + 4 * job.first_block;
     int running_count = 0, running_bytes = 0;
@@ -207,7 +208,7 @@ scan_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, int32_t* 
   const Arena arena = arena_of(arena_storage, regions);
   if (regions > kListSlots) {
     for (int j = 0; j < n_jobs; ++j) {
-      const lct_encode_job& job = jobs[j];
+      const Job& job = jobs[j];
       const int32_t request = job.counts[1] + 2 * job.counts[0];  // uniform across the CTA
       if (request > 0) {
         arena_allocate(arena, regions, request, job.descriptor, alloc_scratch);
@@ -300,8 +301,15 @@ int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descripto
 int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries,
                       void* arena_storage, int max_free_regions, int block_symbols,
                       cudaStream_t stream) {
-  return launch_overlapped(scan_batch_kernel, 1, kScanThreads, 0, stream, jobs, n_jobs, summaries,
-                           arena_storage, max_free_regions, block_symbols);
+  return launch_overlapped(scan_batch_kernel<lct_encode_job>, 1, kScanThreads, 0, stream, jobs,
+                           n_jobs, summaries, arena_storage, max_free_regions, block_symbols);
+}
+
+int launch_scan_batch(const lct_update_job* jobs, int n_jobs, int32_t* summaries,
+                      void* arena_storage, int max_free_regions, int block_symbols,
+                      cudaStream_t stream) {
+  return launch_overlapped(scan_batch_kernel<lct_update_job>, 1, kScanThreads, 0, stream, jobs,
+                           n_jobs, summaries, arena_storage, max_free_regions, block_symbols);
 }
 
 }  // namespace lct

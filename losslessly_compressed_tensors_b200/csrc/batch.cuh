@@ -18,6 +18,20 @@ int launch_scan_batch(const lct_encode_job* jobs, int n_jobs, int32_t* summaries
                       void* arena_storage, int max_free_regions, int block_symbols,
                       cudaStream_t stream);
 
+// The same three steps for the jobs of a batched update (lct_update_batch in update.cu).
+// tables.cu: job j's center from its sampled result exponents, samples + 4096 * j.
+int launch_center_batch(const lct_update_job* jobs, int n_jobs, const int32_t* encode_table,
+                        const int32_t* decode_table, const uint8_t* samples,
+                        int32_t* shifted_encode, cudaStream_t stream);
+int launch_scan_batch(const lct_update_job* jobs, int n_jobs, int32_t* summaries,
+                      void* arena_storage, int max_free_regions, int block_symbols,
+                      cudaStream_t stream);
+// encode.cu: tails of all jobs from their spill arrays (raw result exponents).
+int launch_compact_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
+                         uint8_t* arena_payload, const uint8_t* extra_starts,
+                         const int32_t* summaries, int block_symbols, int steps, int fixed_words,
+                         cudaStream_t stream);
+
 // tables.cu: center sample + shifted tables of one tensor.
 int launch_center(const void* src, int64_t logical_numel, bool precomputed,
                   const int32_t* encode_table, const int32_t* decode_table, int32_t* center,

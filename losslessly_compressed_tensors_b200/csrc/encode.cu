@@ -254,8 +254,8 @@ encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restr
 }
 
 // Shape of one job of a batch (all jobs share the geometry in `common`).
-__device__ __forceinline__ EncodeShape shape_of_job(const lct_encode_job& job,
-                                                    const EncodeShape& common) {
+template <typename Job>
+__device__ __forceinline__ EncodeShape shape_of_job(const Job& job, const EncodeShape& common) {
   EncodeShape g = common;
   g.size = job.size;
   g.logical_numel = job.logical_numel;
@@ -264,7 +264,8 @@ __device__ __forceinline__ EncodeShape shape_of_job(const lct_encode_job& job,
   return g;
 }
 
-__device__ __forceinline__ int find_encode_job(const lct_encode_job* jobs, int n_jobs, int64_t block) {
+template <typename Job>
+__device__ __forceinline__ int find_encode_job(const Job* jobs, int n_jobs, int64_t block) {
   int lo = 0, hi = n_jobs - 1;
   while (lo < hi) {  // last job with first_block <= block
     const int mid = (lo + hi + 1) >> 1;
@@ -367,17 +368,24 @@ compact_tails_kernel(const void* __restrict__ src, uint8_t* lanes, uint8_t* star
                               extra_starts, summaries, g, blockIdx.x);
 }
 
+// Where the tail pass finds a job's exponents: the BF16 source of an encode job, the raw
+// result exponents a fused update left for its overflowing lanes.
+__device__ __forceinline__ const void* tail_source(const lct_encode_job& job) { return job.src; }
+__device__ __forceinline__ const void* tail_source(const lct_update_job& job) { return job.spill; }
+
+template <typename Job, bool kPrecomputed>
 __global__ void __launch_bounds__(kThreads)
-compact_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs, uint8_t* arena_payload,
+compact_batch_kernel(const Job* __restrict__ jobs, int n_jobs, uint8_t* arena_payload,
                      const uint8_t* __restrict__ extra_starts, const int32_t* __restrict__ summaries,
                      EncodeShape common) {
   cudaGridDependencySynchronize();  // prefixes and reservations come from the scan in front
   const int64_t block = blockIdx.x;
-  const lct_encode_job& job = jobs[find_encode_job(jobs, n_jobs, block)];
+  const Job& job = jobs[find_encode_job(jobs, n_jobs, block)];
   const EncodeShape g = shape_of_job(job, common);
-  compact_block<false>(job.src, arena_payload, arena_payload, arena_payload, job.descriptor,
-                       job.counts, job.blocks_out, extra_starts + job.first_block * kLanes,
-                       summaries + 4 * job.first_block, g, block - job.first_block);
+  compact_block<kPrecomputed>(tail_source(job), arena_payload, arena_payload, arena_payload,
+                              job.descriptor, job.counts, job.blocks_out,
+                              extra_starts + job.first_block * kLanes,
+                              summaries + 4 * job.first_block, g, block - job.first_block);
 }
 
 static int check_encode_shape(int64_t size, int64_t logical_numel, int block_symbols, int steps,
@@ -441,6 +449,18 @@ static int launch_encode(const void* src, uint8_t* side, int32_t* encoded,
 }  // extern "C"
 
 namespace lct {
+
+int launch_compact_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
+                         uint8_t* arena_payload, const uint8_t* extra_starts,
+                         const int32_t* summaries, int block_symbols, int steps, int fixed_words,
+                         cudaStream_t stream) {
+  EncodeShape g;
+  const int rc = check_encode_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words, &g);
+  if (rc) return rc;
+  return launch_overlapped(compact_batch_kernel<lct_update_job, true>, (unsigned)total_blocks,
+                           kThreads, 0, stream, jobs, n_jobs, arena_payload, extra_starts,
+                           summaries, g);
+}
 
 int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* tail,
                           const int32_t* descriptor, const int32_t* counts, int32_t* blocks_out,
@@ -557,9 +577,10 @@ int lct_compress_batch(const lct_encode_job* jobs, int n_jobs, int64_t total_blo
     return rc;
   // The arena payload starts after the allocator words, padded to 16 bytes.
   const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
-  return lct::launch_overlapped(lct::compact_batch_kernel, (unsigned)total_blocks, lct::kThreads, 0,
-                                st, jobs, n_jobs, static_cast<uint8_t*>(arena_storage) + metadata,
-                                extra_starts, summaries, g);
+  return lct::launch_overlapped(lct::compact_batch_kernel<lct_encode_job, false>,
+                                (unsigned)total_blocks, lct::kThreads, 0, st, jobs, n_jobs,
+                                static_cast<uint8_t*>(arena_storage) + metadata, extra_starts,
+                                summaries, g);
 }
 
 }  // extern "C"

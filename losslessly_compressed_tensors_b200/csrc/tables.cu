@@ -135,6 +135,22 @@ center_batch_kernel(const lct_encode_job* __restrict__ jobs, const int32_t* __re
 }
 
 __global__ void __launch_bounds__(kTableThreads)
+center_update_batch_kernel(const lct_update_job* __restrict__ jobs,
+                           const int32_t* __restrict__ base_encode,
+                           const int32_t* __restrict__ base_decode,
+                           const uint8_t* __restrict__ samples, int32_t* shifted_encode) {
+  // The samples come from the kernel in front; the fused kernel behind may start its
+  // table-independent prologue right away.
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
+  const lct_update_job& job = jobs[blockIdx.x];
+  const int64_t count = job.logical_numel < kSampleCount ? job.logical_numel : kSampleCount;
+  center_and_tables<true>(samples + (int64_t)kSampleCount * blockIdx.x, count, base_encode,
+                          base_decode, job.center, shifted_encode + 256 * (int64_t)blockIdx.x,
+                          job.shifted_decode);
+}
+
+__global__ void __launch_bounds__(kTableThreads)
 shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __restrict__ base_decode,
                     const int32_t* __restrict__ center, int32_t* shifted_encode,
                     int32_t* shifted_decode) {
@@ -192,6 +208,13 @@ int launch_center_batch(const lct_encode_job* jobs, int n_jobs, const int32_t* e
   center_batch_kernel<<<n_jobs, kTableThreads, 0, stream>>>(jobs, encode_table, decode_table,
                                                             shifted_encode);
   return (int)cudaGetLastError();
+}
+
+int launch_center_batch(const lct_update_job* jobs, int n_jobs, const int32_t* encode_table,
+                        const int32_t* decode_table, const uint8_t* samples,
+                        int32_t* shifted_encode, cudaStream_t stream) {
+  return launch_overlapped(center_update_batch_kernel, (unsigned)n_jobs, kTableThreads, 0, stream,
+                           jobs, encode_table, decode_table, samples, shifted_encode);
 }
 
 }  // namespace lct

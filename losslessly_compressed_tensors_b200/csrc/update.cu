@@ -100,16 +100,18 @@ __device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, 
 // The kernel is a chain of memory latencies in front of a serial bit-stream
 // walk, so everything independent starts first: the lane's payload words go to
 // its shared column asynchronously while the overflow map is consulted.
-__global__ void __launch_bounds__(kThreads)
-update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, OpSpec spec,
-                     const uint16_t* __restrict__ known, uint8_t* __restrict__ samples,
-                     uint16_t* __restrict__ values) {
+// `chunk`: which 256 of the (up to) 4096 samples this CTA computes.
+__device__ __forceinline__ void update_sample_chunk(const OperandView& a, const Shape& g,
+                                                    const uint16_t* __restrict__ other,
+                                                    const OpSpec& spec,
+                                                    const uint16_t* __restrict__ known,
+                                                    uint8_t* __restrict__ samples,
+                                                    uint16_t* __restrict__ values, int chunk) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  cudaTriggerProgrammaticLaunchCompletion();  // the center kernel behind this one waits on its own
   const int tid = threadIdx.x;
   const int64_t n = g.logical_numel;
   const int64_t count = n < kSampleCount ? n : kSampleCount;
-  const int64_t idx = (int64_t)blockIdx.x * kThreads + tid;
+  const int64_t idx = (int64_t)chunk * kThreads + tid;
   if (idx >= count) return;
   // Same jittered position as the center estimate (one per equal slice of the tensor).
   const int64_t pos = sample_position(idx, n);
@@ -146,6 +148,54 @@ update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other,
   if (values != nullptr) values[idx] = (uint16_t)result;
 }
 
+__global__ void __launch_bounds__(kThreads)
+update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, OpSpec spec,
+                     const uint16_t* __restrict__ known, uint8_t* __restrict__ samples,
+                     uint16_t* __restrict__ values) {
+  cudaTriggerProgrammaticLaunchCompletion();  // the center kernel behind this one waits on its own
+  update_sample_chunk(a, g, other, spec, known, samples, values, (int)blockIdx.x);
+}
+
+// Geometry of one job of a batched update (all jobs share `common`).
+__device__ __forceinline__ Shape shape_of_update(const lct_update_job& job, const Shape& common) {
+  Shape g = common;
+  g.size = job.size;
+  g.logical_numel = job.logical_numel;
+  g.n_blocks = job.size / common.block_symbols;
+  g.streams = g.n_blocks * kLanes;
+  return g;
+}
+
+__device__ __forceinline__ OperandView view_of_update(const lct_operand& in) {
+  OperandView v;
+  v.encoded = reinterpret_cast<const uint32_t*>(in.encoded);
+  v.side = in.side;
+  v.center = in.center;
+  v.pair_table = in.pair_table;
+  v.lanes = in.overflow.lanes;
+  v.starts = in.overflow.starts;
+  v.tail = in.overflow.tail;
+  v.descriptor = in.overflow.descriptor;
+  v.count = in.overflow.count;
+  v.blocks = in.overflow.blocks;
+  v.base = in.overflow.base;
+  v.mode = in.overflow.mode;
+  return v;
+}
+
+// Sample pre-pass of every job of a batch: grid (16, n_jobs); job j's samples go to
+// samples + 4096 * j.
+__global__ void __launch_bounds__(kThreads)
+update_sample_batch_kernel(const lct_update_job* __restrict__ jobs, Shape common, OpSpec spec,
+                           uint8_t* __restrict__ samples) {
+  cudaTriggerProgrammaticLaunchCompletion();
+  const lct_update_job& job = jobs[blockIdx.y];
+  update_sample_chunk(view_of_update(job.a), shape_of_update(job, common),
+                      static_cast<const uint16_t*>(job.other), spec, job.known_values,
+                      samples + (int64_t)kSampleCount * blockIdx.y, job.result_values,
+                      (int)blockIdx.x);
+}
+
 // Split one row of results (4 words, column order; padding already zeroed):
 // exponent bytes stay in column order, side bytes go to lane order.
 __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint32_t* e03,
@@ -162,13 +212,14 @@ __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint3
 // Shared memory: [input payload image | DecodeShared | encode table].  Finished output
 // words go straight to global memory (a warp's lanes write neighbouring words of the same
 // payload rows; L2 merges the sectors), which keeps four CTAs resident per SM.
+// One codec block.  extra_starts and summaries are the tensor's own arrays.
 template <int kLaneMask>
-__global__ void __launch_bounds__(kThreads, 4)
-update_fused_kernel(OperandView a, Shape g_in, const uint16_t* __restrict__ other, bool other_vector_ok,
-                    OpSpec spec, const int32_t* __restrict__ shifted_encode,
-                    uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
-                    uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
-                    uint8_t* __restrict__ spill) {
+__device__ __forceinline__ void update_fused_block(
+    const OperandView& a, const Shape& g_in, const uint16_t* __restrict__ other,
+    bool other_vector_ok, const OpSpec& spec, const int32_t* __restrict__ shifted_encode,
+    uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
+    uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
+    uint8_t* __restrict__ spill, int64_t block) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Shape g = g_in;
   if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // compile-time lane mapping, see decode_block
@@ -177,7 +228,6 @@ update_fused_kernel(OperandView a, Shape g_in, const uint16_t* __restrict__ othe
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + image);
   uint2* encode_table = reinterpret_cast<uint2*>(smem_raw + image + sizeof(DecodeShared));
 
-  const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
@@ -309,6 +359,40 @@ update_fused_kernel(OperandView a, Shape g_in, const uint16_t* __restrict__ othe
     summaries[block] = total_bad;
     summaries[g.n_blocks + block] = total_bytes;
   }
+}
+
+template <int kLaneMask>
+__global__ void __launch_bounds__(kThreads, 4)
+update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, bool other_vector_ok,
+                    OpSpec spec, const int32_t* __restrict__ shifted_encode,
+                    uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
+                    uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
+                    uint8_t* __restrict__ spill) {
+  update_fused_block<kLaneMask>(a, g, other, other_vector_ok, spec, shifted_encode, side_out,
+                                encoded_out, extra_starts, summaries, spill, blockIdx.x);
+}
+
+// Every block of every job of a batch: CTA b serves the job whose block range contains b.
+template <int kLaneMask>
+__global__ void __launch_bounds__(kThreads, 4)
+update_fused_batch_kernel(const lct_update_job* __restrict__ jobs, int n_jobs, Shape common,
+                          OpSpec spec, const int32_t* __restrict__ shifted_encode,
+                          uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries) {
+  const int64_t block = blockIdx.x;
+  int lo = 0, hi = n_jobs - 1;
+  while (lo < hi) {  // last job with first_block <= block
+    const int mid = (lo + hi + 1) >> 1;
+    if (jobs[mid].first_block <= block) lo = mid; else hi = mid - 1;
+  }
+  const lct_update_job& job = jobs[lo];
+  const bool vector_ok = (reinterpret_cast<uintptr_t>(job.other) & 15u) == 0;
+  update_fused_block<kLaneMask>(view_of_update(job.a), shape_of_update(job, common),
+                                static_cast<const uint16_t*>(job.other), vector_ok, spec,
+                                shifted_encode + 256 * (int64_t)lo, job.side_out,
+                                reinterpret_cast<uint32_t*>(job.encoded_out),
+                                extra_starts + job.first_block * kLanes,
+                                summaries + 4 * job.first_block, job.spill,
+                                block - job.first_block);
 }
 
 }  // namespace lct
@@ -446,5 +530,60 @@ int lct_update(const lct_operand* a, const void* other, const float* alpha, cons
                              extra_starts, summaries, size, logical_numel, block_symbols, steps, 1,
                              true, st);
 }
+
+int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
+                     const float* alpha, const float* beta, int op, int alpha_is_one,
+                     int beta_is_one, const int32_t* encode_table, const int32_t* decode_table,
+                     void* arena_storage, int max_free_regions, uint8_t* samples,
+                     int32_t* shifted_encode, uint8_t* extra_starts, int32_t* summaries,
+                     int block_symbols, int steps, int fixed_words, int rare_length,
+                     void* stream) {
+  if (jobs == nullptr || encode_table == nullptr || decode_table == nullptr ||
+      arena_storage == nullptr || samples == nullptr || shifted_encode == nullptr ||
+      extra_starts == nullptr || summaries == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (n_jobs <= 0 || n_jobs > 65535 || total_blocks <= 0 || total_blocks > 0x7FFFFFFFLL)
+    return LCT_E_BAD_ARGUMENT;
+  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
+  if (op < LCT_OP_ADD || op > LCT_OP_SCALAR_MUL_ADD) return LCT_E_BAD_ARGUMENT;
+  if (op == LCT_OP_SCALAR_MUL_ADD) {
+    if (!alpha_is_one && alpha == nullptr) return LCT_E_NULL_POINTER;
+    if (!beta_is_one && beta == nullptr) return LCT_E_NULL_POINTER;
+  } else {
+    alpha_is_one = beta_is_one = 1;
+  }
+  lct::Shape g;
+  int rc = lct::check_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words,
+                            rare_length, &g);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
+  // 1. samples of all jobs: an ordinary launch, so everything queued before this call is
+  //    complete and visible before any of the five kernels starts.
+  const size_t sample_shared = lct::payload_image_bytes(fixed_words + 1);
+  if ((rc = lct::opt_in_shared(lct::update_sample_batch_kernel, sample_shared)) != 0) return rc;
+  lct::update_sample_batch_kernel<<<dim3(lct::kSampleCount / lct::kThreads, (unsigned)n_jobs),
+                                    lct::kThreads, sample_shared, st>>>(jobs, g, spec, samples);
+  if ((rc = (int)cudaGetLastError()) != 0) return rc;
+  // 2-5. each may be scheduled while its predecessor runs and waits for it on the device.
+  if ((rc = lct::launch_center_batch(jobs, n_jobs, encode_table, decode_table, samples,
+                                     shifted_encode, st)))
+    return rc;
+  const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
+  auto kernel = g.lane_mask == 254 ? lct::update_fused_batch_kernel<254>
+                                   : lct::update_fused_batch_kernel<-1>;
+  if ((rc = lct::opt_in_shared(kernel, shared)) != 0) return rc;
+  if ((rc = lct::launch_overlapped(kernel, (unsigned)total_blocks, lct::kThreads, shared, st, jobs,
+                                   n_jobs, g, spec, shifted_encode, extra_starts, summaries)))
+    return rc;
+  if ((rc = lct::launch_scan_batch(jobs, n_jobs, summaries, arena_storage, max_free_regions,
+                                   block_symbols, st)))
+    return rc;
+  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
+  return lct::launch_compact_batch(jobs, n_jobs, total_blocks,
+                                   static_cast<uint8_t*>(arena_storage) + metadata, extra_starts,
+                                   summaries, block_symbols, steps, fixed_words, st);
+}
+
 
 }  // extern "C"

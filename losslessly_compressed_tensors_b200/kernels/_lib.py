@@ -44,6 +44,15 @@ class DecodeJob(ctypes.Structure):
                 ("first_block", _i64), ("side_stage", _p)]
 
 
+class UpdateJob(ctypes.Structure):
+    """``struct lct_update_job``."""
+
+    _fields_ = [("a", Operand), ("other", _p), ("known_values", _p), ("result_values", _p),
+                ("side_out", _p), ("encoded_out", _p), ("spill", _p), ("center", _p),
+                ("shifted_decode", _p), ("counts", _p), ("descriptor", _p), ("blocks_out", _p),
+                ("size", _i64), ("logical_numel", _i64), ("first_block", _i64)]
+
+
 class EncodeJob(ctypes.Structure):
     """``struct lct_encode_job``."""
 
@@ -75,6 +84,8 @@ _SIGNATURES = {
                          _i64, _i64, _i, _i, _i, _i, _p],
     "lct_update": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p,
                    _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _p],
+    "lct_update_batch": [_p, _i, _i64, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i,
+                         _i, _i, _p],
     "lct_dual_scale_add": [ctypes.POINTER(Operand), ctypes.POINTER(Operand), _p, _p, _p, _i,
                            _i64, _i64, _i, _i, _i, _i, _p],
     "lct_buffer_reset": [_p, _i, _i32, _p],

@@ -23,7 +23,7 @@ import torch
 from .. import config
 from ..compression.huffman_tables import FIRST_BITS, get_distribution_tables
 from . import _lib
-from ._lib import DecodeJob, EncodeJob, Operand, Overflow
+from ._lib import DecodeJob, EncodeJob, Operand, Overflow, UpdateJob
 from .backends import FallbackStorage
 
 OP_ADD, OP_MULTIPLY, OP_SCALAR_MUL_ADD = 0, 1, 2
@@ -445,6 +445,51 @@ def compress_batch(jobs: list[dict], encode_table, decode_table, buffer, **geome
     batch = CompressBatch(jobs, encode_table, decode_table, buffer, **geometry_kw)
     batch.run()
     return batch
+
+
+def update_batch(jobs: list[dict], alpha, beta, encode_table, decode_table, buffer, *, op,
+                 alpha_is_one, beta_is_one, rare_length, block_symbols, lanes, steps, fixed_words):
+    """Fused update of many compressed tensors of one codebook and geometry into ``buffer``'s
+    arena with five launches in all (instead of five per tensor).  Each job is a dict: ``operand``
+    (the state), ``other`` (dense BF16), ``known_values`` / ``result_values`` (or None),
+    ``side_out``, ``encoded_out``, ``spill``, ``center``, ``decode_table``, ``counts``,
+    ``descriptor``, ``blocks`` plus ``size`` and ``logical_numel``.  Returns the work tensors,
+    which must stay referenced until the launches have run."""
+    device = _require_cuda(encode_table)
+    records = (UpdateJob * len(jobs))()
+    first = 0
+    for record, job in zip(records, jobs):
+        record.a = job["operand"]
+        record.other = job["other"].data_ptr()
+        record.known_values = _ptr(job.get("known_values"))
+        record.result_values = _ptr(job.get("result_values"))
+        record.side_out = job["side_out"].data_ptr()
+        record.encoded_out = job["encoded_out"].data_ptr()
+        record.spill = job["spill"].data_ptr()
+        record.center = job["center"].data_ptr()
+        record.shifted_decode = job["decode_table"].data_ptr()
+        record.counts = job["counts"].data_ptr()
+        record.descriptor = job["descriptor"].data_ptr()
+        record.blocks_out = job["blocks"].data_ptr()
+        record.size = job["size"]
+        record.logical_numel = job["logical_numel"]
+        record.first_block = first
+        first += job["size"] // block_symbols
+    table = _to_device(records, device)
+    work = torch.empty(4096 * len(jobs) + first * lanes + 16, dtype=torch.uint8, device=device)
+    samples, extra_starts = work[:4096 * len(jobs)], work[4096 * len(jobs):]
+    ints = torch.empty(4 * first + 256 * len(jobs), dtype=torch.int32, device=device)
+    summaries, shifted_encode = ints[:4 * first], ints[4 * first:]
+    _call(
+        "lct_update_batch", device,
+        table.data_ptr(), len(jobs), first,
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        op, int(alpha_is_one), int(beta_is_one), encode_table.data_ptr(), decode_table.data_ptr(),
+        buffer._storage.data_ptr(), buffer.max_free_regions, samples.data_ptr(),
+        shifted_encode.data_ptr(), extra_starts.data_ptr(), summaries.data_ptr(), block_symbols,
+        steps, fixed_words, rare_length, launches=5)
+    return table, work, ints
 
 
 class DecodeBatch:

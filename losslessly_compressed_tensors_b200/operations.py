@@ -113,6 +113,24 @@ def a_compA_add_b_B(A_comp: CompressedTensor, a: Tensor, B: Tensor, b: Tensor, *
                           alpha_is_one=alpha_is_one)
 
 
+def a_compA_add_b_B_many(A_comps: list[CompressedTensor], a: Tensor, Bs: list[Tensor],
+                         b: Tensor | None = None, *, alpha_is_one: bool = False,
+                         buffer: TensorBuffer, distribution=None) -> list[CompressedTensor]:
+    """``a * A + b * B`` (``b`` defaults to 1) for a whole list of compressed tensors of one
+    codebook and geometry, results compressed into ``buffer``'s arena: five launches for the
+    list instead of five per tensor, with the bytes ``a_compA_add_B`` / ``a_compA_add_b_B``
+    (``dense_output=False``) give each tensor.  An optimizer's step over all its states.  No
+    counterpart in the reference (``LCT/operations.py`` updates one tensor per call)."""
+    device = A_comps[0].data.device
+    if b is None:
+        _need_tensor(a, "alpha")
+    else:
+        _need_device_scalar(a, "alpha", device)
+        _need_device_scalar(b, "beta", device)
+    return _pointwise.fused_update_many(A_comps, Bs, _pointwise.SCALAR_MUL_ADD, distribution,
+                                        buffer, alpha=a, beta=b, alpha_is_one=alpha_is_one)
+
+
 def a_compA_add_compB(A_comp: CompressedTensor, a: Tensor, B_comp: CompressedTensor, *,
                       dense_output: bool = True, buffer: TensorBuffer | None = None,
                       distribution=None):
