@@ -389,19 +389,41 @@ def update_leg(steps: int = 10, warmup: int = 3) -> dict:
         out[label + "_ms_per_tensor_step"] = statistics.mean(times)
         out[label + "_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
     pointwise_module.FUSED_UPDATE = True
-    # All twelve states in one call (five launches per step instead of sixty).
-    times = []
+    # The twelve states through the many-tensor call: five launches per group of tensors
+    # (groups of 4: the host prepares the next group while the GPU works; one group of 12).
+    for label, group in (("many", 4), ("many_one_call", None)):
+        times = []
+        for it in range(warmup + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            updates = [grads[(it + k) % len(grads)] for k in range(n_tensors)]
+            a.record()
+            LCTTensor.mul_add_many_(states, alpha, updates, group=group)
+            b.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(a.elapsed_time(b) / n_tensors)
+        out[label + "_ms_per_tensor_step"] = statistics.mean(times)
+        out[label + "_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
+    # The same with everything but the launches prepared once (two alternating value sets, job
+    # tables, work buffers): six launches per step for all twelve states.
+    from losslessly_compressed_tensors_b200.update_plan import UpdatePlan
+
+    plan = UpdatePlan(states, alpha)
+    times, walls = [], []
     for it in range(warmup + steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         updates = [grads[(it + k) % len(grads)] for k in range(n_tensors)]
+        t0 = time.perf_counter()
         a.record()
-        LCTTensor.mul_add_many_(states, alpha, updates)
+        plan.step(updates)
         b.record()
+        walls.append((time.perf_counter() - t0) / n_tensors)
         torch.cuda.synchronize()
         if it >= warmup:
             times.append(a.elapsed_time(b) / n_tensors)
-    out["many_ms_per_tensor_step"] = statistics.mean(times)
-    out["many_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
+    out["plan_ms_per_tensor_step"] = statistics.mean(times)
+    out["plan_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
+    out["plan_host_ms_per_tensor_step"] = statistics.mean(walls[warmup:]) * 1e3
     # the compressed state still decodes to what the dense recurrence gives
     check = LCTTensor(torch.zeros(shape, dtype=torch.bfloat16, device="cuda"), buffer, dist_cfg)
     dense = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")

@@ -393,6 +393,11 @@ int lct_buffer_allocate(void *storage, const int32_t *requested_bytes,
 /* Replaces the lct::tensor_buffer_free op, LCT/kernels/tensor_buffer_ops.py:5-15. */
 int lct_buffer_free(void *storage, int32_t *descriptor, int32_t *status, int max_free_regions,
                     void *stream);
+/* n regions returned under one lock, in list order: `descriptors` is a DEVICE
+ * array of n descriptor pointers, status int32[n].  Same free list as n calls of
+ * lct_buffer_free.  No counterpart in the reference. */
+int lct_buffer_free_many(void *storage, int32_t *const *descriptors /* device */, int n,
+                         int32_t *status, int max_free_regions, void *stream);
 
 #ifdef __cplusplus
 }

@@ -94,17 +94,24 @@ class LCTTensor(Tensor):
 
     @staticmethod
     def mul_add_many_(tensors: "list[LCTTensor]", alpha: Tensor, updates: "list[Tensor]",
-                      beta: Tensor | None = None, *, alpha_is_one: bool = False) -> None:
-        """``mul_add_`` of every tensor of the list with its own update, as one call of five
-        launches for the whole list (all tensors must share the first one's codebook, geometry
-        and arena).  Same values as calling ``mul_add_`` on each; the old values' arena regions
-        are released after all new ones have been reserved."""
-        old = [tensor.x for tensor in tensors]
-        new = ops.a_compA_add_b_B_many(old, alpha, updates, beta, alpha_is_one=alpha_is_one,
-                                       buffer=old[0].buffer, distribution=old[0].distribution)
-        for tensor, value, previous in zip(tensors, new, old):
-            tensor.x = value
-            previous.free()
+                      beta: Tensor | None = None, *, alpha_is_one: bool = False,
+                      group: int | None = 4) -> None:
+        """``mul_add_`` of every tensor of the list with its own update, five launches per
+        ``group`` tensors instead of five per tensor (all tensors must share the first one's
+        codebook, geometry and arena).  Same values as calling ``mul_add_`` on each.  A group's
+        old arena regions are released after all of its new ones have been reserved.  Groups
+        let the host prepare the next call while the GPU works on the previous one;
+        ``group=None`` puts the whole list into one call."""
+        size = len(tensors) if not group else group
+        for at in range(0, len(tensors), size):
+            part = tensors[at:at + size]
+            old = [tensor.x for tensor in part]
+            new = ops.a_compA_add_b_B_many(old, alpha, updates[at:at + size], beta,
+                                           alpha_is_one=alpha_is_one, buffer=old[0].buffer,
+                                           distribution=old[0].distribution)
+            for tensor, value, previous in zip(part, new, old):
+                tensor.x = value
+                previous.free()
 
     def add_comp_(self, update_comp: "LCTTensor", alpha: Tensor):
         """``x <- x + alpha * update_comp``, both sides compressed."""

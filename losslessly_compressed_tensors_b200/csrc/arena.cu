@@ -35,15 +35,10 @@ arena_allocate_kernel(void* storage, const int32_t* requested_bytes, const int32
   arena_allocate(arena_of(storage, regions), regions, request, descriptor, scratch);
 }
 
-// Return a region to the sorted free list, merging with its neighbours.
-__global__ void __launch_bounds__(kArenaThreads)
-arena_free_kernel(void* storage, int32_t* descriptor, int32_t* status_out, int regions) {
-  __shared__ int scratch[2];
-  const Arena a = arena_of(storage, regions);
-  if (!arena_lock(a, scratch)) {
-    if (threadIdx.x == 0) *status_out = kStatusLockTimeout;
-    return;
-  }
+// Return a region to the sorted free list, merging with its neighbours.  The caller holds
+// the arena lock; `scratch` needs 2 ints.  Ends with every thread past a block barrier.
+__device__ __forceinline__ void arena_free_locked(const Arena& a, int regions, int32_t* descriptor,
+                                                  int32_t* status_out, int* scratch) {
   const int32_t offset = descriptor[0], size = descriptor[1];
   const bool valid = descriptor[2] == 0 && descriptor[3] == *a.generation && offset >= 0 && size > 0;
   const int count = *a.count;
@@ -111,6 +106,32 @@ arena_free_kernel(void* storage, int32_t* descriptor, int32_t* status_out, int r
     if (status == 0) descriptor[2] = 5;
     *status_out = status;
   }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kArenaThreads)
+arena_free_kernel(void* storage, int32_t* descriptor, int32_t* status_out, int regions) {
+  __shared__ int scratch[2];
+  const Arena a = arena_of(storage, regions);
+  if (!arena_lock(a, scratch)) {
+    if (threadIdx.x == 0) *status_out = kStatusLockTimeout;
+    return;
+  }
+  arena_free_locked(a, regions, descriptor, status_out, scratch);
+  arena_unlock(a);
+}
+
+// Many regions under one lock, in list order (the free list ends up as after one call each).
+__global__ void __launch_bounds__(kArenaThreads)
+arena_free_many_kernel(void* storage, int32_t* const* descriptors, int n, int32_t* status_out,
+                       int regions) {
+  __shared__ int scratch[2];
+  const Arena a = arena_of(storage, regions);
+  if (!arena_lock(a, scratch)) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) status_out[i] = kStatusLockTimeout;
+    return;
+  }
+  for (int i = 0; i < n; ++i) arena_free_locked(a, regions, descriptors[i], status_out + i, scratch);
   arena_unlock(a);
 }
 
@@ -343,6 +364,15 @@ int lct_buffer_free(void* storage, int32_t* descriptor, int32_t* status, int max
   if (!power_of_two(max_free_regions)) return LCT_E_BAD_ARGUMENT;
   lct::arena_free_kernel<<<1, lct::kArenaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       storage, descriptor, status, max_free_regions);
+  return (int)cudaGetLastError();
+}
+
+int lct_buffer_free_many(void* storage, int32_t* const* descriptors, int n, int32_t* status,
+                         int max_free_regions, void* stream) {
+  if (storage == nullptr || descriptors == nullptr || status == nullptr) return LCT_E_NULL_POINTER;
+  if (!power_of_two(max_free_regions) || n <= 0) return LCT_E_BAD_ARGUMENT;
+  lct::arena_free_many_kernel<<<1, lct::kArenaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      storage, descriptors, n, status, max_free_regions);
   return (int)cudaGetLastError();
 }
 

@@ -91,6 +91,7 @@ _SIGNATURES = {
     "lct_buffer_reset": [_p, _i, _i32, _p],
     "lct_buffer_allocate": [_p, _p, _p, _i, _p, _i, _p],
     "lct_buffer_free": [_p, _p, _p, _i, _p],
+    "lct_buffer_free_many": [_p, _p, _i, _p, _i, _p],
 }
 
 EXPORTS = tuple(_SIGNATURES) + ("lct_version", "lct_error_string")

@@ -10,7 +10,9 @@ from losslessly_compressed_tensors_b200.LCTensor import LCTTensor
 from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType, NoiseLevel
 from losslessly_compressed_tensors_b200.operations import (
     a_compA_add_B, a_compA_add_b_B, a_compA_add_b_B_many, compress, decompress)
-from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
+from losslessly_compressed_tensors_b200.tensor_buffer import (
+    TensorBuffer, _free_regions_snapshot, verify_buffer)
+from losslessly_compressed_tensors_b200.update_plan import UpdatePlan
 from synth import synth_bf16
 
 pytestmark = pytest.mark.gpu
@@ -112,3 +114,68 @@ def test_many_rejects_mixed_lists():
         a_compA_add_b_B_many([a], alpha, [x[:-1]], buffer=arena)
     with pytest.raises(ValueError):
         a_compA_add_b_B_many([a], alpha, [x], buffer=None)
+
+
+@pytest.mark.parametrize("dist,kind,sizes", [
+    (MEDIUM, "normal", [32768 * 3, 5, 40000, 70001]),
+    (CLEAN, "wide", [32768 * 2 + 17, 50000, 300]),                  # overflow tails in the arena
+], ids=["medium", "overflowing"])
+def test_prepared_plan_equals_the_unprepared_call(dist, kind, sizes):
+    """UpdatePlan (storage, job tables and work buffers prepared once, two value sets that
+    alternate) against mul_add_many_ on a twin arena: same components, same arena, five steps;
+    the updates change address at step 3 (the job table is rebuilt) and stay put otherwise."""
+    arenas = [TensorBuffer(4 << 20), TensorBuffer(4 << 20)]
+    inputs = _inputs(sizes, kind, 300)
+    planned = [LCTTensor(x, arenas[0], dist) for x in inputs]
+    plain = [LCTTensor(x, arenas[1], dist) for x in inputs]
+    alpha = _scalar(0.95)
+    plan = UpdatePlan(planned, alpha)
+    updates = _inputs(sizes, kind, 400)
+    for step in range(5):
+        if step == 3:
+            updates = [u.clone() for u in _inputs(sizes, kind, 500)]
+        elif step:
+            for u, fresh in zip(updates, _inputs(sizes, kind, 400 + step)):
+                u.copy_(fresh)
+        plan.step(updates)
+        LCTTensor.mul_add_many_(plain, alpha, updates, group=None)
+        for i, (a, b) in enumerate(zip(planned, plain)):
+            _same(a.x, b.x, f"step {step} tensor {i}")
+            assert a.nbytes == b.nbytes
+            assert np.array_equal(bits_of(a.decompress()), bits_of(b.decompress()))
+        assert np.array_equal(host(arenas[0]._storage), host(arenas[1]._storage)), f"arena, step {step}"
+    assert len(plan.tables) == 3          # own -> 0, 0 -> 1, 1 -> 0
+    assert set(host(plan.status).tolist()) <= {0, 4}     # 4: a tensor without tails had no region
+    # a tensor replaced behind the plan's back
+    planned[0].x, planned[1].x = planned[0].x, planned[0].x
+    with pytest.raises(ValueError):
+        plan.step(updates)
+    with pytest.raises(ValueError):
+        plan.step(updates[:-1])
+    for t in plain:
+        t.free()
+    for value in plan.values[1 - plan.which]:
+        value.free()
+    for arena in arenas:
+        verify_buffer(arena)
+        assert _free_regions_snapshot(arena) == [(0, 4 << 20)]
+
+
+def test_prepared_plan_with_beta_matches_pytorch():
+    shapes = [(128, 512), (300, 301)]
+    gen = torch.Generator().manual_seed(11)
+    dense = [(torch.randn(s, generator=gen) * 1e-3).to(torch.bfloat16).cuda() for s in shapes]
+    arena = TensorBuffer(1 << 20)
+    states = [LCTTensor(x, arena, MEDIUM) for x in dense]
+    alpha, beta = _scalar(0.5), _scalar(2.0)
+    plan = UpdatePlan(states, alpha, beta)
+    for _ in range(4):
+        grads = [(torch.randn(s, generator=gen) * 1e-3).to(torch.bfloat16).cuda() for s in shapes]
+        plan.step(grads)
+        dense = [(m.float() * alpha + g.float() * beta).to(torch.bfloat16) for m, g in zip(dense, grads)]
+        for m, want in zip(states, dense):
+            assert np.array_equal(bits_of(m.decompress()), bits_of(want))
+    with pytest.raises(ValueError):
+        UpdatePlan([], alpha)
+    with pytest.raises(ValueError):
+        UpdatePlan([LCTTensor(dense[0], None, MEDIUM)], alpha)
