@@ -25,6 +25,7 @@ from torch import Tensor
 from ..LCTensor import LCTTensor
 from ..operations import a_compA_add_B
 from ..tensor_buffer import TensorBuffer
+from ..update_plan import UpdatePlan
 from .dist_configs import momentum_dist, momentum_first_dist
 
 
@@ -89,6 +90,7 @@ class SparseSGDM(_Base):
         self.momentum = torch.tensor(momentum, dtype=torch.float32, device=anchor.device)
         self.neg_lr = _scalar(-lr, anchor)
         self.momentums: list[Tensor | LCTTensor | None] = [None] * len(self.params)
+        self._plan: UpdatePlan | None = None
 
     def _advance_momentum(self, index: int, grad: Tensor):
         state = self.momentums[index]
@@ -102,12 +104,16 @@ class SparseSGDM(_Base):
         return state
 
     def _advance_all(self) -> bool:
-        """From the second step on, with a shared arena: every momentum advanced by one call of
-        five launches for the whole parameter list (same values as one ``mul_add_`` each)."""
+        """From the second step on, with a shared arena: every momentum advanced by one prepared
+        call for the whole parameter list (``UpdatePlan``: six launches per step, same values
+        as one ``mul_add_`` each).  The momentum values alternate between the plan's two sets,
+        so a reference to ``momentums[i].x`` is good for one more step only."""
         if not (self.compressed and self.buffer is not None and len(self.params) > 1
                 and all(isinstance(m, LCTTensor) for m in self.momentums)):
             return False
-        LCTTensor.mul_add_many_(self.momentums, self.momentum, [p.grad for p in self.params])
+        if self._plan is None:
+            self._plan = UpdatePlan(self.momentums, self.momentum)
+        self._plan.step([p.grad for p in self.params])
         return True
 
     @torch.no_grad()
