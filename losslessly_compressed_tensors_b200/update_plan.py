@@ -78,7 +78,7 @@ class UpdatePlan:
             torch.tensor([v.fallback_descriptor.data_ptr() for v in values], dtype=torch.int64)
             .to(self.device) for values in self.values]
         self.which = 0            # the set the next step writes
-        self.tables: dict = {}    # (source set or "own", target set) -> [records, device table, others]
+        self.tables: dict = {}    # (source set, target set) -> [records, device table, others]
 
     def _new_value(self, like: CompressedTensor, new) -> CompressedTensor:
         block_symbols, lanes, _, fixed_words = self.geometry
@@ -103,7 +103,7 @@ class UpdatePlan:
         ``others`` (pointers); rebuilt only when a pointer in it changed."""
         key = (source_key, self.which)
         entry = self.tables.get(key)
-        if entry is not None and entry[2] == others and (source_key != "own" or entry[3] == [id(s) for s in sources]):
+        if entry is not None and entry[2] == others:
             return entry[1]
         block_symbols = self.geometry[0]
         records = (UpdateJob * len(sources))()
@@ -131,9 +131,10 @@ class UpdatePlan:
             first += source.size // block_symbols
             at += source.size
         table = dispatch._to_device(records, self.device)
-        # "own" sources are whatever the tensors held when the plan first saw them: keep them
-        # referenced, and remember which objects they were.
-        self.tables[key] = [records, table, others, [id(s) for s in sources], list(sources)]
+        if source_key != "own":
+            # Values of the plan never move, so the table stays good while the updates do.  A
+            # table that reads the tensors' own first values is built for that one step only.
+            self.tables[key] = [records, table, others]
         return table
 
     def step(self, updates) -> None:

@@ -144,7 +144,7 @@ def test_prepared_plan_equals_the_unprepared_call(dist, kind, sizes):
             assert a.nbytes == b.nbytes
             assert np.array_equal(bits_of(a.decompress()), bits_of(b.decompress()))
         assert np.array_equal(host(arenas[0]._storage), host(arenas[1]._storage)), f"arena, step {step}"
-    assert len(plan.tables) == 3          # own -> 0, 0 -> 1, 1 -> 0
+    assert len(plan.tables) == 2          # 0 -> 1 and 1 -> 0; the first step's table is not kept
     assert set(host(plan.status).tolist()) <= {0, 4}     # 4: a tensor without tails had no region
     # a tensor replaced behind the plan's back
     planned[0].x, planned[1].x = planned[0].x, planned[0].x
