@@ -8,16 +8,17 @@
 // mask's bits 5..7 move a warp's 32 lanes to another aligned group of 32
 // columns and its bits 1..4 permute them inside that group, so in every row
 // one warp's lanes cover exactly one 64-byte segment of the BF16 row.  That
-// makes the whole pipeline warp-private: a warp (32 lanes of a block) passes
-// its data through its own shared-memory tile, 32 rows at a time, kept in
-// COLUMN (logical) order:
+// makes the pipeline warp-private: a warp (32 lanes of a block) passes its
+// data through its own shared-memory tile, 32 rows at a time:
 //
-//     tile[pair p][column c in the warp's group] = e(row 2p, c) | e(row 2p+1, c) << 8
+//     tile[pair p][x] = e(row 2p) | e(row 2p+1) << 8  of lane  x ^ (2p & lane_mask & 6)
 //
-// One side of each kernel works lane-wise (a thread owns a lane and walks its
-// bit stream, touching tile[p][lane ^ mask]); the other side works row-wise
-// (a thread owns 8 adjacent columns of a row pair: 128-bit global accesses,
-// four threads per 64-byte segment).  Only __syncwarp() separates the two.
+// i.e. column order inside every aligned group of 8, lane order between the
+// groups (decode_core.cuh: tile_slot_xor).  One side of each kernel works
+// lane-wise (a thread owns a lane and walks its bit stream); the other side
+// works row-wise (a thread owns 8 adjacent columns of a row pair: 128-bit
+// global accesses).  __syncwarp(), or a barrier of two warps where they share
+// rows, separates the two.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -37,37 +38,46 @@ constexpr int kCenterValues = 256;     // centers -128..127: one two-symbol tabl
 constexpr int kFirstMask = 1023;        // the codebook's first-level table covers 10 bits
 constexpr int kSampleCount = 4096;     // positions the exponent center is estimated from
 
-// Two-symbol table entry: byte0 = first symbol, byte1 = second symbol,
-// byte2 = length of the first symbol (of prefix + literal for an escape), byte3 = bits consumed by both symbols
-// (so that "position += entry >> 24" is one shift-and-add instruction), or the
-// flags of an entry that is not two directly coded symbols: kSlow (the sign
-// bit, so one signed compare finds it) and kEscape.
+// Two-symbol table entry (one per 12-bit stream window):
+//
+//   bits 0..4    bits to consume: both code lengths of a full pair (two directly coded
+//                symbols that fit the window together), else the first symbol's length
+//                (an escape: prefix + 8-bit literal).  A funnel shift takes its amount from
+//                the low five bits of a register, so the entry itself is the shift operand.
+//   bits 5..7    first code length - 1 of a full pair (for a reader that wants one symbol)
+//   byte 1       first symbol as an exponent byte (undefined for an escape)
+//   byte 2       second symbol of a full pair
+//   bits 24..28  copy of bits 0..4 for a full pair, else 0: one byte dot product subtracts it
+//                from a bit counter
+//   bit 30       kEscape: the first symbol is an escape
+//   bit 31       kSlow: not a full pair (the sign bit, so one signed compare finds it)
 constexpr uint32_t kSlow = 0x80000000u;
 constexpr uint32_t kEscape = 0x40000000u;
 
-// Slot of the two-symbol table that holds the entry for a 12-bit stream window
-// (the window is the low kPairBits bits of `stream_bits`; higher bits are
-// ignored).  Indexing by the raw window would put the first code's bits into
-// the shared-memory bank number: a handful of values, i.e. heavy bank
-// conflicts.  LCT_TABLE_INDEX picks the mapping (both ends must agree):
-//   0 raw window, 1 bit-reversed window, 2 window with its top five bits
-//   folded onto the bank bits.  Measured on B200 the three are within 3 % of
-//   each other (random 32-lane gathers cost ~3.5 wavefronts whatever the
-//   mapping); 2 is the fastest by a small margin.
-#ifndef LCT_TABLE_INDEX
-#define LCT_TABLE_INDEX 2
-#endif
-__device__ __forceinline__ uint32_t table_slot(uint32_t stream_bits) {
-#if LCT_TABLE_INDEX == 0
-  return stream_bits & (kPairEntries - 1);
-#elif LCT_TABLE_INDEX == 1
-  return __brev(stream_bits) >> (32 - kPairBits);
-#else
-  return (stream_bits & (kPairEntries - 1)) ^ ((stream_bits >> 7) & 31u);
-#endif
+__host__ __device__ __forceinline__ uint32_t make_pair_entry(uint32_t len0, uint32_t byte0,
+                                                             uint32_t len1, uint32_t byte1) {
+  const uint32_t total = len0 + len1;
+  return total | ((len0 - 1u) << 5) | (byte0 << 8) | (byte1 << 16) | (total << 24);
 }
-// Inverse of table_slot on 12-bit values (all three mappings are involutions).
-__device__ __forceinline__ uint32_t table_window(uint32_t slot) { return table_slot(slot); }
+__host__ __device__ __forceinline__ uint32_t make_single_entry(uint32_t len0, uint32_t byte0,
+                                                               bool escape) {
+  return kSlow | (escape ? kEscape : 0u) | len0 | (byte0 << 8);
+}
+// Length of the entry's first symbol.
+__device__ __forceinline__ uint32_t entry_first_length(uint32_t entry) {
+  return (int32_t)entry < 0 ? (entry & 31u) : ((entry >> 5) & 7u) + 1u;
+}
+__device__ __forceinline__ uint32_t entry_first_symbol(uint32_t entry) { return (entry >> 8) & 255u; }
+__device__ __forceinline__ uint32_t entry_second_symbol(uint32_t entry) { return (entry >> 16) & 255u; }
+
+// Slot of the two-symbol table that holds the entry for a 12-bit stream window (the window is
+// the low kPairBits bits of `stream_bits`; higher bits are ignored): the window itself.
+// Folding the window's top bits onto the shared-memory bank bits was measured too: it removes
+// a tenth of the bank conflicts and costs two instructions on every lookup's dependent chain,
+// for no change in the decoder's time.
+__device__ __forceinline__ uint32_t table_slot(uint32_t stream_bits) {
+  return stream_bits & (kPairEntries - 1);
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
   return __byte_perm(a, b, selector);

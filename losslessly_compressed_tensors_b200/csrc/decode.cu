@@ -1,24 +1,26 @@
 // Table-driven decoder and the fused decode -> pointwise operation kernels.
 //
-// One CTA (256 threads) per codec block; after a short block-wide prologue
-// every warp runs on its own (see common.cuh: a warp's 32 lanes own one
-// 64-byte segment of every row).
+// One CTA (256 threads) per codec block.
 //
 // Prologue: the block's payload tile (fixed_words rows of 256 words) and the
 // 16 KB two-symbol table of this tensor's center are copied into shared memory
 // with cp.async while the block's overflow map is expanded.
 //
-// Per 32-row tile, per warp:
-//   lane phase - thread = lane: a 96-bit register window over the lane's column
-//                of the payload image; 12 bits of it index the two-symbol table
-//                (two exponent bytes + bits consumed per lookup); the window is
-//                refilled from the image one word at a time, off the lookup's
-//                dependency chain.  The only divergent path is the rare "not two
-//                direct symbols" entry, decoded one symbol at a time;
-//   row phase  - thread = 8 columns of a row pair: 128-bit read of the tile,
-//                64-bit side-byte loads (issued before the lane phase), four
-//                bytes at a time rebuilt into BF16 low/high bytes, optional
-//                arithmetic, 128-bit streaming stores.
+// Then, software pipelined over half tiles of 16 rows:
+//   lane side - thread = lane: the next 94 bits of its stream in three registers,
+//               pre-shifted so that 12 of them index the two-symbol table (two
+//               exponent bytes + bits consumed per lookup); consuming is three
+//               funnel shifts by the table entry itself, refills from the shared
+//               image are off the lookup chain (decode_core.cuh: ShiftCursor).
+//               The only divergent path is the rare entry that is not a full
+//               pair, decoded one symbol at a time;
+//   row side  - thread = 8 columns of a row pair of the PREVIOUS half tile:
+//               128-bit read of the tile, 64-bit side-byte loads (requested a
+//               half tile earlier), four bytes at a time rebuilt into BF16,
+//               optional arithmetic, 128-bit streaming stores.  In the plain
+//               decoder its instructions are issued between the lane side's
+//               lookups, and two neighbouring warps share their rows out so
+//               that every store instruction writes full 128-byte lines.
 // Overflow lanes switch from the bit stream to their raw tail bytes at their
 // recorded start step, inside the same launch.
 #include "decode_core.cuh"
@@ -32,6 +34,48 @@ namespace lct {
 // kLaneMask: the lane mapping as a compile-time constant (254, the default mapping: the masked
 // tile and row addresses fold into constants, 80 instead of 82 us per 64 Mi elements), or -1 to
 // take it from the shape at run time (the linear mapping).
+// Row side of one half tile (16 rows) for one thread: 8 columns of one row pair.  Cut into
+// slices that the lane phase of the NEXT half tile issues between its pairs.
+struct DecodeRowSlices {
+  const uint16_t* tile;
+  uint16_t* out;
+  SideSelectors selectors;
+  int64_t logical_numel;
+  bool full_block;
+  // the half tile being finished:
+  UnitPlace place;
+  uint2 side[2];
+  uint4 words;
+  uint32_t top[4], bottom[4];
+
+  __device__ __forceinline__ void store(const uint32_t (&row)[4], int64_t at) {
+    if (full_block || at + 8 <= logical_numel) {
+      __stcs(reinterpret_cast<uint4*>(out + at), make_uint4(row[0], row[1], row[2], row[3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (at + i < logical_numel) out[at + i] = (uint16_t)(row[i >> 1] >> (16 * (i & 1)));
+    }
+  }
+  template <int k>
+  __device__ __forceinline__ void slice() {
+    if (k == 0) words = *reinterpret_cast<const uint4*>(&tile[place.tile_index]);
+    if (k == 1) join_row(words, side[0], selectors, false, top);
+    if (k == 2) store(top, place.logical);
+    if (k == 3) join_row(words, side[1], selectors, true, bottom);
+    if (k == 4) store(bottom, place.logical + kLanes);
+  }
+  __device__ __forceinline__ void rest() {
+    slice<0>(); slice<1>(); slice<2>(); slice<3>(); slice<4>();
+  }
+};
+
+// One codec block.  The work is software pipelined over half tiles of 16 rows: while a warp's
+// lanes decode half tile h into one half of the warp's tile buffer, the row side of half tile
+// h - 1 (join with the side bytes, 128-bit stores) is issued between the lookups from the other
+// half of the buffer, and the side bytes of half tile h were requested one iteration earlier.
+// kLaneMask: the lane mapping as a compile-time constant (254, the default mapping), or -1 to
+// take it from the shape at run time (the linear mapping).
 template <int kLaneMask>
 __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& g_in,
                                              uint16_t* __restrict__ out, int64_t block) {
@@ -41,68 +85,89 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + (size_t)(g.fixed_words + 2) * kLanes * 4);
-  prepare_block(sh, payload, a, g, block);
+  const OperandShared sh = carve_operand(smem_raw, 0, 1, g.fixed_words);
+  prepare_block(sh, a, g, block);
 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
-  const int tail_from = sh.overflow_start[tid];
-  const int coded = min(valid, tail_from);
-  const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  BitReader reader;
-  reader.open(payload + tid, g.fixed_words);
+  LaneState lane = open_lane(sh, a, g, valid);
   const bool full_block = block_base + g.block_symbols <= g.logical_numel;
-  // Rows of this block that hold elements: tiles of pure padding (the tail of a ragged or tiny
-  // tensor) have nothing to decode and nothing to store.
+  // Rows of this block that hold elements: half tiles of pure padding (the tail of a ragged or
+  // tiny tensor) have nothing to decode and nothing to store.
   const int rows_used =
       full_block ? g.steps : (int)((g.logical_numel - block_base + kLanes - 1) / kLanes);
-  uint16_t* tile = sh.tile[warp];
+  const int halves = (rows_used + kTileRows / 2 - 1) / (kTileRows / 2);
 
-  for (int step0 = 0; step0 < rows_used; step0 += kTileRows) {
-    // Side bytes of this thread's two row-phase units, requested before the lane phase.
-    UnitPlace place[2];
-    uint2 side_regs[2][2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      place[u] = place_unit(warp, (lane32 >> 2) + 8 * u, lane32 & 3, row0, step0, block_base, g.lane_mask);
-      const uint8_t* s = a.side + place[u].storage;
-      side_regs[u][0] = __ldcs(reinterpret_cast<const uint2*>(s));
-      side_regs[u][1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
+  // Row side: kRowWarps neighbouring warps work as one group.  Their lanes cover one aligned
+  // segment of 32 * kRowWarps columns in every row (the lane mapping's bits 5..7 move whole
+  // aligned groups), and the group's threads share that segment out so that 4 * kRowWarps
+  // neighbouring threads cover one row: 128-bit stores of full 128-byte lines from two warps on.
+  constexpr int kRowWarps = 2, kRowShift = 1;  // measured: 1 -> 76.8 us, 2 -> 75.9, 4 -> 78.0 (64 Mi elements)
+  const int group = warp >> kRowShift;
+  const int in_group = ((warp & (kRowWarps - 1)) << 5) + lane32;
+  const int column8 = in_group & (4 * kRowWarps - 1);  // which 8 columns of the segment
+  const int pair8 = in_group >> (2 + kRowShift);        // which row pair of a half tile, 0..7
+  auto group_barrier = [&] {
+    if (kRowWarps == 1) __syncwarp();
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(32 * kRowWarps) : "memory");
+  };
+
+  DecodeRowSlices rows;
+  rows.out = out;
+  // Every row-side unit of a thread has the same pair permutation (its pair index mod 4).
+  rows.selectors = side_selectors((uint32_t)(((2 * pair8) & g.lane_mask) >> 1) & 3u);
+  rows.logical_numel = g.logical_numel;
+  rows.full_block = full_block;
+
+  // Side bytes of half tile h for this thread's unit (row pair 8 * (h & 1) + pair8 of tile h / 2).
+  UnitPlace next_place;
+  const uint16_t* next_tile;
+  uint2 next_side[2];
+  auto request = [&](int h) {
+    const int step0 = kTileRows * (h >> 1);
+    // The warp of the group whose lanes hold these columns in this tile.
+    const int moved = (int)((row0 + step0) & g.lane_mask) >> 5;
+    const int owner = (group << kRowShift) + ((column8 >> 2) ^ (moved & (kRowWarps - 1)));
+    next_place = place_unit(owner, kHalfPairs * (h & 1) + pair8, column8 & 3, row0, step0,
+                            block_base, g.lane_mask);
+    next_tile = sh.head->tile[owner];
+    const uint8_t* s = a.side + next_place.storage;
+    next_side[0] = __ldcs(reinterpret_cast<const uint2*>(s));
+    next_side[1] = __ldcs(reinterpret_cast<const uint2*>(s + kLanes));
+  };
+  auto hand_over = [&] {
+    rows.place = next_place;
+    rows.tile = next_tile;
+    rows.side[0] = next_side[0];
+    rows.side[1] = next_side[1];
+  };
+  NoSlices nothing;
+  request(0);
+  // Half tile 0: nothing to finish yet.
+  decode_half_rows<kLaneMask, 0>(lane.reader, lane.tables, 0, lane.coded, lane.tail_from,
+                                 lane.tail_bytes, g.rare_length, g.lane_mask, nothing);
+  hand_over();
+  group_barrier();
+  for (int h = 1; h < halves; h += 2) {
+    request(h);
+    decode_half_rows<kLaneMask, 1>(lane.reader, lane.tables, kTileRows * (h >> 1), lane.coded,
+                                   lane.tail_from, lane.tail_bytes, g.rare_length, g.lane_mask, rows);
+    hand_over();
+    group_barrier();
+    if (h + 1 < halves) {
+      request(h + 1);
+      decode_half_rows<kLaneMask, 0>(lane.reader, lane.tables, kTileRows * ((h + 1) >> 1), lane.coded,
+                                     lane.tail_from, lane.tail_bytes, g.rare_length, g.lane_mask, rows);
+      hand_over();
+      group_barrier();
     }
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
-                     g.lane_mask);
-    __syncwarp();
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
-      const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
-      uint32_t top[4], bottom[4];
-      join_row(words, side_regs[u][0], place[u].q, false, top);
-      join_row(words, side_regs[u][1], place[u].q, true, bottom);
-      const int64_t at = place[u].logical;
-      if (full_block || at + kLanes + 8 <= g.logical_numel) {
-        __stcs(reinterpret_cast<uint4*>(out + at), make_uint4(top[0], top[1], top[2], top[3]));
-        __stcs(reinterpret_cast<uint4*>(out + at + kLanes),
-               make_uint4(bottom[0], bottom[1], bottom[2], bottom[3]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t t = top[i >> 1] >> (16 * (i & 1));
-          const uint32_t b = bottom[i >> 1] >> (16 * (i & 1));
-          if (at + i < g.logical_numel) out[at + i] = (uint16_t)t;
-          if (at + kLanes + i < g.logical_numel) out[at + kLanes + i] = (uint16_t)b;
-        }
-      }
-    }
-    __syncwarp();
   }
+  rows.rest();  // the last half tile
 }
 
-#ifndef LCT_DECODE_MIN_CTAS
-#define LCT_DECODE_MIN_CTAS 4
-#endif
+// Resident CTAs per SM the decoder is compiled for (shared memory allows no more; three cost 8 %).
+constexpr int kDecodeMinCtas = 4;
 template <int kLaneMask>
-__global__ void __launch_bounds__(kThreads, LCT_DECODE_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kDecodeMinCtas)
 decode_kernel(OperandView a, Shape g, uint16_t* __restrict__ out) {
   decode_block<kLaneMask>(a, g, out, blockIdx.x);
 }
@@ -154,7 +219,7 @@ static __device__ __noinline__ void stage_side_bytes(const uint8_t* __restrict__
 }
 
 template <int kLaneMask>
-__global__ void __launch_bounds__(kThreads, LCT_DECODE_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kDecodeMinCtas)
 decode_batch_kernel(const lct_decode_job* __restrict__ jobs, int n_jobs, Shape common) {
   const int64_t block = blockIdx.x;
   const lct_decode_job& job = jobs[find_job(jobs, n_jobs, block)];
@@ -185,44 +250,31 @@ pointwise_kernel(OperandView a, OperandView b, Shape g_in, const uint16_t* __res
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Shape g = g_in;
   if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // see decode_block
-  const size_t image = (size_t)(g.fixed_words + 2) * kLanes * 4;
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
-  uint32_t* payload_b = reinterpret_cast<uint32_t*>(smem_raw + (kDual ? image : 0));
-  unsigned char* tables = smem_raw + (kDual ? 2 : 1) * image;
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(tables);
-  DecodeShared& sh_b = *reinterpret_cast<DecodeShared*>(tables + (kDual ? sizeof(DecodeShared) : 0));
+  const OperandShared sh = carve_operand(smem_raw, 0, kDual ? 2 : 1, g.fixed_words);
+  const OperandShared sh_b = carve_operand(smem_raw, kDual ? 1 : 0, kDual ? 2 : 1, g.fixed_words);
   const int64_t block = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
   const int64_t block_base = block * (int64_t)g.block_symbols;
-  prepare_block(sh, payload, a, g, block);
-  if (kDual) prepare_block(sh_b, payload_b, b, g, block);
+  prepare_block(sh, a, g, block);
+  if (kDual) prepare_block(sh_b, b, g, block);
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
-  const int a_tail_from = sh.overflow_start[tid];
-  const int a_coded = min(valid, a_tail_from);
-  const uint8_t* a_tail = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  BitReader reader_a, reader_b;
-  reader_a.open(payload + tid, g.fixed_words);
-  reader_b.open(payload_b + tid, g.fixed_words);
-  int b_tail_from = g.steps, b_coded = 0;
-  const uint8_t* b_tail = nullptr;
-  if (kDual) {
-    b_tail_from = sh_b.overflow_start[tid];
-    b_coded = min(valid, b_tail_from);
-    b_tail = b.mode ? tail_origin(b) + sh_b.overflow_offset[tid] : nullptr;
-  }
-  uint16_t* tile = sh.tile[warp];
-  uint16_t* tile_b = sh_b.tile[warp];
+  LaneState lane_a = open_lane(sh, a, g, valid);
+  LaneState lane_b = lane_a;
+  if (kDual) lane_b = open_lane(sh_b, b, g, valid);
+  const uint16_t* tile = sh.head->tile[warp];
+  const uint16_t* tile_b = sh_b.head->tile[warp];
+  const SideSelectors selectors = side_selectors((uint32_t)(((2 * (lane32 >> 2)) & g.lane_mask) >> 1) & 3u);
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader_a, sh, tile, lane32, step0, a_coded, a_tail_from, a_tail,
-                     g.rare_length, g.lane_mask);
+    decode_tile_rows<kLaneMask>(lane_a.reader, lane_a.tables, step0, lane_a.coded, lane_a.tail_from,
+                                lane_a.tail_bytes, g.rare_length, g.lane_mask);
     if (kDual)
-      decode_tile_rows(reader_b, sh_b, tile_b, lane32, step0, b_coded, b_tail_from, b_tail,
-                       g.rare_length, g.lane_mask);
+      decode_tile_rows<kLaneMask>(lane_b.reader, lane_b.tables, step0, lane_b.coded,
+                                  lane_b.tail_from, lane_b.tail_bytes, g.rare_length, g.lane_mask);
     __syncwarp();
     // All global loads of the tile's four rows first, so their latencies overlap.
     UnitPlace place_of[2];
@@ -245,19 +297,18 @@ pointwise_kernel(OperandView a, OperandView b, Shape g_in, const uint16_t* __res
     }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
       const UnitPlace place = place_of[u];
-      const uint4 words = *reinterpret_cast<const uint4*>(&tile[p * 32 + 8 * j4]);
+      const uint4 words = *reinterpret_cast<const uint4*>(&tile[place.tile_index]);
       uint4 words_b = make_uint4(0, 0, 0, 0);
-      if (kDual) words_b = *reinterpret_cast<const uint4*>(&tile_b[p * 32 + 8 * j4]);
+      if (kDual) words_b = *reinterpret_cast<const uint4*>(&tile_b[place.tile_index]);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int64_t s_at = place.storage + half * kLanes;
         const int64_t l_at = place.logical + half * kLanes;
         uint32_t left[4], right[4], result[4];
-        join_row(words, side_a[u][half], place.q, half == 1, left);
+        join_row(words, side_a[u][half], selectors, half == 1, left);
         if (kDual) {
-          join_row(words_b, side_b[u][half], place.q, half == 1, right);
+          join_row(words_b, side_b[u][half], selectors, half == 1, right);
         } else {
 #pragma unroll
           for (int k = 0; k < 4; ++k) right[k] = dense_in[u][half][k];

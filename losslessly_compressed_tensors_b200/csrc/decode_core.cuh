@@ -1,8 +1,8 @@
 // Device building blocks shared by the decoder, the fused pointwise kernels and
 // the fused update kernel: operand views, the per-CTA prologue (staging of the
-// payload and of the center's two-symbol table, overflow map), the lane-side bit reader and
-// tile decoder, the row-side BF16 join/split, the arithmetic of the fused
-// operations, and the host-side argument checks.
+// payload and of the center's two-symbol table, overflow map), the lane-side
+// stream cursor and tile decoder, the row-side BF16 join/split, the arithmetic
+// of the fused operations, and the host-side argument checks.
 #pragma once
 
 #include "common.cuh"
@@ -37,25 +37,62 @@ struct Shape {
   int lane_mask;  // 254: lane ^ (row & 254) ("swizzle"); 0: "linear"
 };
 
-// Shared memory of a CTA: the payload image(s) first (fixed_words + 2 rows of
-// 256 words each, the last two zero), then one DecodeShared per operand.  A
-// lane's refill pointer is clamped to the image once per tile; inside a tile a
-// corrupt stream can run at most 16 rows past it, which still lands in the
-// tables below (garbage in, garbage out, but never an out-of-range access).
-struct __align__(16) DecodeShared {
-  uint32_t table[kPairEntries];
+// Shared memory of a decoding CTA with n operands (n = 2 only for the fused operation on two
+// compressed tensors):
+//
+//   table 0 .. n-1   the 4096-entry two-symbol table of each operand's center, 16 KB each.  They
+//                    come first so that their shared addresses do not depend on the geometry:
+//                    a lookup is then one load at (window & 0x3FFC) + a constant.
+//   (the fused update keeps its 2 KB encode table here, for the same reason)
+//   then per operand:
+//   image            the block's payload: fixed_words rows of 256 words,
+//                    then two zero rows                                          (fixed_words + 2) KB
+//   DecodeHead       warp tiles, byte table, overflow map, scan scratch         kHeadBytes
+//
+// A lane opens its stream with the image row in FRONT of its first word (see ShiftCursor), so
+// the kilobyte before the image must be readable: it is the end of the tables or of the
+// previous operand's head.  A well-formed stream is never read past the image's second zero
+// row; a lane's fetch address is pulled back to that row once per half tile and can run at
+// most 8 rows further inside one, which is the head (garbage in, garbage out, but never an
+// out-of-range access).
+struct __align__(16) DecodeHead {
   uint16_t tile[kWarps][kTilePairs * 32];
   uint8_t index_to_byte[256];
   uint16_t overflow_start[kLanes];
   int32_t overflow_offset[kLanes];
   int scan[36];
 };
+constexpr size_t kHeadBytes = 10240;
+constexpr size_t kTableBytes = (size_t)kPairEntries * 4;
+static_assert(sizeof(DecodeHead) <= kHeadBytes, "head must fit its slot");
+static_assert(kHeadBytes % 1024 == 0 && kHeadBytes >= 9 * 1024,
+              "a lane may fetch up to 9 rows past the image");
 
-static inline size_t payload_image_bytes(int fixed_words) {
+struct OperandShared {
+  DecodeHead* head;
+  uint32_t* image;
+  uint32_t* table;
+};
+
+static inline __host__ __device__ size_t payload_image_bytes(int fixed_words) {
   return (size_t)(fixed_words + 2) * kLanes * 4;
 }
-static inline size_t operand_shared_bytes(int fixed_words) {
-  return sizeof(DecodeShared) + payload_image_bytes(fixed_words);
+// Shared memory per operand (its table included).
+static inline __host__ __device__ size_t operand_shared_bytes(int fixed_words) {
+  return kTableBytes + kHeadBytes + payload_image_bytes(fixed_words);
+}
+// Operand `index` of `count` in the CTA's dynamic shared memory.  `extra_bytes` (a multiple of
+// 16) are left free between the tables and the first operand's head for the caller's own
+// fixed-address data.
+__device__ __forceinline__ OperandShared carve_operand(unsigned char* base, int index, int count,
+                                                       int fixed_words, size_t extra_bytes = 0) {
+  const size_t rest = kHeadBytes + payload_image_bytes(fixed_words);
+  unsigned char* own = base + (size_t)count * kTableBytes + extra_bytes + (size_t)index * rest;
+  OperandShared s;
+  s.table = reinterpret_cast<uint32_t*>(base + (size_t)index * kTableBytes);
+  s.image = reinterpret_cast<uint32_t*>(own);
+  s.head = reinterpret_cast<DecodeHead*>(own + payload_image_bytes(fixed_words));
+  return s;
 }
 
 __device__ __forceinline__ void cp_async_16(void* shared_dst, const void* global_src) {
@@ -71,130 +108,276 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
-// Read position of one lane: a 96-bit register window over the shared payload
-// image (the word under the position and the two after it) plus the bit
-// offset inside the first word.  Lookups take their bits from registers; the
-// only shared-memory access is the refill of the third word, which is not on
-// the lookup's dependency chain.
-struct BitReader {
-  const uint32_t* next_row;  // image word that enters the window at the next refill
-  const uint32_t* last_row;  // the image's second zero row
-  uint32_t cur, n1, n2;
-  int shift;                 // 0..31 between pairs
+// ---- shared memory by 32-bit address (lane phases) -------------------------
+// The lane phases address shared memory with 32-bit window addresses and constant
+// byte offsets, so that a lookup is one load with an immediate and no 64-bit
+// pointer arithmetic.
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+template <int kByteOffset = 0>
+__device__ __forceinline__ uint32_t load_shared_u32(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(address), "n"(kByteOffset));
+  return v;
+}
+__device__ __forceinline__ uint32_t load_shared_u8(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+template <int kByteOffset = 0>
+__device__ __forceinline__ uint32_t load_shared_u16(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(address), "n"(kByteOffset));
+  return v;
+}
+template <int kByteOffset = 0>
+__device__ __forceinline__ void store_shared_u16(uint32_t address, uint32_t value) {
+  asm volatile("st.shared.u16 [%0+%1], %2;" ::"r"(address), "n"(kByteOffset),
+               "h"((unsigned short)value)
+               : "memory");
+}
+__device__ __forceinline__ void store_shared_u16_at(uint32_t address, uint32_t value) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(address), "h"((unsigned short)value) : "memory");
+}
 
-  // `column`: this lane's column of an image of fixed_words + 2 rows.
-  __device__ __forceinline__ void open(const uint32_t* column, int fixed_words) {
-    cur = column[0];
-    n1 = column[kLanes];
-    n2 = column[2 * kLanes];
-    next_row = column + 3 * kLanes;
-    last_row = column + (fixed_words + 1) * kLanes;
-    shift = 0;
+__device__ __forceinline__ uint32_t funnel_right(uint32_t low, uint32_t high, uint32_t amount) {
+  return __funnelshift_r(low, high, amount);  // the amount is taken modulo 32
+}
+// a + sum over the four bytes of e (unsigned) * w (signed): with w = -1 in one byte this
+// subtracts that byte of e from a.
+__device__ __forceinline__ int dot_bytes(uint32_t e, int w, int a) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(e), "r"(w), "r"(a));
+  return d;
+}
+
+// Shared address of the table entry for the window at bits 2..13 of `bits4` (the two low bits
+// are ignored).  The tables sit at fixed offsets of the CTA's shared memory, so `table` is a
+// constant that folds into the load's immediate.
+__device__ __forceinline__ uint32_t entry_address(uint32_t bits4, uint32_t table) {
+  return (bits4 & 0x3FFCu) + table;
+}
+
+// Read position of one lane: the next 94 stream bits in three registers, already shifted so
+// that the bit under the position is bit 2 of `lo` (bits 0..1 are the two bits before it).
+// A lookup is then  entry = table[lo & 0x3FFC]  and consuming n bits is three funnel shifts
+// whose amount is the low five bits of a register, i.e. the table entry itself, so the
+// dependent chain from one lookup to the next is  mask -> shared load -> shift.
+// `valid` counts the loaded bits of the 96 (at least 64 at every check): when fewer than 64
+// are left, the next word of the lane's column is inserted above them.  Refills are off the
+// lookup chain.  Up to 31 bits may be consumed between two checks.
+struct ShiftCursor {
+  uint32_t lo, mid, hi;
+  int valid;
+  uint32_t next;  // shared address of the next unread word of this lane
+  uint32_t last;  // shared address of this lane's word in the image's second zero row
+
+  __device__ __forceinline__ void open(const uint32_t* image, int lane, int fixed_words) {
+    const uint32_t before = shared_address(image + lane) - (uint32_t)(kLanes * 4);
+    const uint32_t v0 = load_shared_u32<0>(before);  // shifted out: any readable word will do
+    const uint32_t v1 = load_shared_u32<kLanes * 4>(before);
+    const uint32_t v2 = load_shared_u32<2 * kLanes * 4>(before);
+    lo = funnel_right(v0, v1, 30u);
+    mid = funnel_right(v1, v2, 30u);
+    hi = v2 >> 30;
+    valid = 66;
+    next = before + 3u * kLanes * 4u;
+    last = before + (uint32_t)(fixed_words + 2) * kLanes * 4u;
   }
-  // A well-formed stream never refills past the image's second zero row; a
-  // corrupt one is pulled back here, once per tile (at most 16 refills each).
-  __device__ __forceinline__ void tile_start() {
-    if (next_row > last_row) next_row = last_row;
+  __device__ __forceinline__ uint32_t window() const { return lo; }
+  // `amount`: only its low five bits count.
+  __device__ __forceinline__ void shift_out(uint32_t amount) {
+    lo = funnel_right(lo, mid, amount);
+    mid = funnel_right(mid, hi, amount);
+    hi = funnel_right(hi, 0u, amount);
   }
-  // 32 stream bits starting `extra` bits after the position (shift + extra < 64).
-  __device__ __forceinline__ uint32_t peek(int extra) const {
-    const int s = shift + extra;
-    const bool far = s >= 32;
-    return __funnelshift_r(far ? n1 : cur, far ? n2 : n1, s);  // amount is taken modulo 32
-  }
-  __device__ __forceinline__ uint32_t peek0() const { return __funnelshift_r(cur, n1, shift); }
-  __device__ __forceinline__ void advance(int bits) {  // bits <= 32
-    shift += bits;
-    if (shift >= 32) {
-      shift -= 32;
-      cur = n1;
-      n1 = n2;
-      n2 = *next_row;
-      next_row += kLanes;
+  // When fewer than 64 bits are loaded, insert the lane's next word above them.
+  __device__ __forceinline__ void refill() {
+    if (valid < 64) {
+      const uint32_t word = load_shared_u32<0>(next);
+      next += (uint32_t)(kLanes * 4);
+      mid |= __funnelshift_l(0u, word, (uint32_t)valid);  // word << (valid - 32)
+      hi = __funnelshift_l(word, 0u, (uint32_t)valid);    // the bits of word that did not fit
+      valid += 32;
     }
+  }
+  // Once per half tile: a lane never fetches more than 9 words past this (8 pairs of at most 32
+  // bits), which still lies inside the CTA's shared memory (the image is followed by the head).
+  __device__ __forceinline__ void half_start() { next = min(next, last); }
+  // Consume a full-pair entry (refill separately).
+  __device__ __forceinline__ void take_pair(uint32_t entry) {
+    shift_out(entry);
+    valid = dot_bytes(entry, (int)0xFF000000u, valid);
+  }
+  // Consume `bits` (<= 31) and refill.
+  __device__ __forceinline__ void take(uint32_t bits) {
+    shift_out(bits);
+    valid -= (int)bits;
+    refill();
   }
 };
 
-// Unroll factor of the lane-phase loop (16 pairs per tile).  Measured on B200
-// (64 Mi elements): 16 -> 81.9 us, 8 -> 80.8, 4 -> 80.0, 2 -> 80.9; the fully
-// unrolled loop pays in instruction-cache misses for what it saves in address
-// arithmetic.
-#ifndef LCT_DECODE_UNROLL
-#define LCT_DECODE_UNROLL 4
-#endif
-#define LCT_PRAGMA(x) _Pragma(#x)
-#define LCT_UNROLL(n) LCT_PRAGMA(unroll n)
+using LaneReader = ShiftCursor;
 
-// One symbol from a table entry and the stream bits it was looked up with.
-__device__ __forceinline__ uint32_t symbol_of(uint32_t entry, uint32_t bits, const DecodeShared& sh,
-                                              int rare_length, int* length) {
-  if (entry & kEscape) {
-    *length = rare_length + 8;
-    return sh.index_to_byte[(bits >> rare_length) & 255u];
-  }
-  *length = (int)((entry >> 16) & 15u);
-  return entry & 255u;
+
+// What the lane phase of one thread needs besides its cursor.
+struct LaneTables {
+  uint32_t table;       // shared address of the two-symbol table
+  uint32_t byte_table;  // shared address of index_to_byte[256]
+  uint32_t tile_lane;   // shared address of this lane's slot in row pair 0 of the warp's tile
+};
+
+// Tile layout.  tile[p][x], x = 0..31, holds e(row 2p) | e(row 2p+1) << 8 of the lane
+// x ^ (2p & lane_mask & 6), i.e. of column c = x ^ (2p & lane_mask & 0x18): inside an aligned
+// group of 8 the tile is in column order, while the groups keep the lanes' order.  A lane
+// therefore only applies the two low mask bits (four address values, constant when the loop is
+// unrolled), and the row side, which needs the group bits for its side bytes anyway, reads or
+// writes group j ^ (2p & lane_mask & 0x18) / 8 for its columns 8j..8j+7.
+template <int kLaneMask>
+__device__ __forceinline__ uint32_t tile_slot_xor(int p, int lane_mask) {
+  const int mask = kLaneMask >= 0 ? kLaneMask : lane_mask;
+  return (uint32_t)(((2 * p) & mask & 6) << 1);
 }
 
-// Pair whose table entry is not "two direct symbols": take the first symbol
-// from the entry already in hand, look the second one up on its own.
-// Returns the pair in table-entry form (bytes: first, second, -, bits consumed).
+constexpr unsigned kFullWarp = 0xFFFFFFFFu;
+
+// The rest of a pair whose table entry is not a full pair.  The entry still carries its
+// first symbol and that symbol's length, and take_pair(entry) has already shifted that length
+// out of the cursor (and subtracted the entry's flag byte from the bit counter, which is put
+// right here); `before` is the window the entry was looked up with.  Accounts for the first
+// symbol, looks the second one up on its own and consumes it.
+// Returns (e0 | e1 << 8) << 8, the form a full-pair entry has.
 template <typename Reader>
-__device__ __forceinline__ uint32_t slow_pair(const Reader& r, uint32_t entry, uint32_t bits,
-                                              const DecodeShared& sh, int rare_length) {
-  // Every entry carries the length of its first symbol, escapes included, so the second
-  // lookup does not wait for an escape test; literals are patched in afterwards.
-  const uint32_t l0 = (entry >> 16) & 31u;
-  const uint32_t bits1 = r.peek((int)l0);
-  const uint32_t second = sh.table[table_slot(bits1)];
-  uint32_t e0 = entry & 255u, e1 = second & 255u;
-  if ((entry | second) & kEscape) {
-    if (entry & kEscape) e0 = sh.index_to_byte[(bits >> rare_length) & 255u];
-    if (second & kEscape) e1 = sh.index_to_byte[(bits1 >> rare_length) & 255u];
-  }
-  return e0 | (e1 << 8) | ((l0 + ((second >> 16) & 31u)) << 24);
+__device__ __forceinline__ uint32_t finish_slow_pair(Reader& r, uint32_t entry, uint32_t before,
+                                                     const LaneTables& t, int rare_length) {
+  // All three lookups are issued before any of them is used: the literal of the first symbol,
+  // the entry of the second (the cursor's low word is valid whatever the bit counter says) and
+  // the literal it would have.
+  const uint32_t bits1 = r.window();
+  const uint32_t literal0 = load_shared_u8(t.byte_table + ((before >> (rare_length + 2)) & 255u));
+  const uint32_t second = load_shared_u32(entry_address(bits1, t.table));
+  const uint32_t literal1 = load_shared_u8(t.byte_table + ((bits1 >> (rare_length + 2)) & 255u));
+  r.valid += (int)(entry >> 24) - (int)(entry & 31u);
+  r.refill();
+  const uint32_t e0 = (entry & kEscape) ? literal0 : entry_first_symbol(entry);
+  const uint32_t e1 = (second & kEscape) ? literal1 : entry_first_symbol(second);
+  r.take(entry_first_length(second));
+  return (e0 << 8) | (e1 << 16);
 }
 
-// Lane phase for one tile.  `coded` = number of leading steps of this lane that
-// are in the bit stream (its overflow start or its valid length, whichever is
-// first); steps from `tail_from` on come from the raw tail.
-template <typename Reader>
-__device__ __forceinline__ void decode_tile_rows(Reader& r, const DecodeShared& sh,
-                                                 uint16_t* tile, int lane32, int step0, int coded,
-                                                 int tail_from, const uint8_t* tail_bytes,
-                                                 int rare_length, int lane_mask) {
-  r.tile_start();
-  // Tiles start on multiples of 32 rows, so the low mask bits of pair p are 2p & lane_mask.
-  if (__all_sync(0xFFFFFFFFu, step0 + kTileRows <= coded)) {
-    LCT_UNROLL(LCT_DECODE_UNROLL)
-    for (int p = 0; p < kTilePairs; ++p) {
-      const uint32_t bits = r.peek0();
-      uint32_t entry = sh.table[table_slot(bits)];
-      if ((int32_t)entry < 0) entry = slow_pair(r, entry, bits, sh, rare_length);
-      tile[p * 32 + (lane32 ^ ((2 * p) & lane_mask))] = (uint16_t)entry;
-      r.advance((int)(entry >> 24));
-    }
+constexpr int kHalfPairs = kTilePairs / 2;  // a half tile: 8 row pairs = 16 rows
+
+// Work of the caller that is issued between the pairs of a lane phase (slice<k>() after pair k
+// of a half tile, k = 0..7; rest() for whatever the lane phase did not get to).  The lane
+// phase is one dependent chain per lane (mask -> table load -> shift); independent row-side
+// work placed between its links fills the chain's latency, and spreads the row side's memory
+// traffic over the whole iteration.
+struct NoSlices {
+  template <int k> __device__ __forceinline__ void slice() {}
+  __device__ __forceinline__ void rest() {}
+};
+
+// One fully coded pair of every lane of the warp (kPair: its index in the tile, a compile-time
+// constant so that the tile address is a register plus an immediate).
+template <int kPair, typename Reader, typename Slices>
+__device__ __forceinline__ void decode_pair_uniform(Reader& r, const LaneTables& t,
+                                                    const uint32_t (&slot)[4], int rare_length,
+                                                    Slices& slices) {
+  const uint32_t before = r.window();
+  uint32_t entry = load_shared_u32(entry_address(before, t.table));
+  // Issued behind the lookup and ahead of its first use: this is what runs while the lookup is
+  // in flight (a warp issues in order).
+  slices.template slice<kPair % kHalfPairs>();
+  r.take_pair(entry);
+  if (__any_sync(kFullWarp, (int32_t)entry < 0)) {
+    if ((int32_t)entry < 0) entry = finish_slow_pair(r, entry, before, t, rare_length);
+  }
+  if (kPair & 1) r.refill();  // two full pairs take at most 24 bits: one check serves both
+  store_shared_u16<kPair * 64>(slot[kPair & 3], entry >> 8);
+}
+
+template <int kHalf, int kIndex, typename Reader, typename Slices>
+struct UniformPairs {
+  static __device__ __forceinline__ void run(Reader& r, const LaneTables& t,
+                                             const uint32_t (&slot)[4], int rare_length,
+                                             Slices& slices) {
+    decode_pair_uniform<kHalf * kHalfPairs + kIndex>(r, t, slot, rare_length, slices);
+    UniformPairs<kHalf, kIndex + 1, Reader, Slices>::run(r, t, slot, rare_length, slices);
+  }
+};
+template <int kHalf, typename Reader, typename Slices>
+struct UniformPairs<kHalf, kHalfPairs, Reader, Slices> {
+  static __device__ __forceinline__ void run(Reader&, const LaneTables&, const uint32_t (&)[4], int,
+                                             Slices&) {}
+};
+
+// Lane phase for half a tile: row pairs kHalf * 8 .. + 7 of the tile that starts at row `step0`
+// of the block.  `coded` = number of leading steps of this lane that are in the bit stream (its
+// overflow start or its valid length, whichever is first); steps from `tail_from` on come from
+// the raw tail.  `slices`: see NoSlices; all of its work has been issued on return.
+template <int kLaneMask, int kHalf, typename Reader, typename Slices>
+__device__ __forceinline__ void decode_half_rows(Reader& r, const LaneTables& t, int step0,
+                                                 int coded, int tail_from,
+                                                 const uint8_t* tail_bytes, int rare_length,
+                                                 int lane_mask, Slices& slices) {
+  const int first = step0 + kHalf * (kTileRows / 2);
+  r.half_start();
+  if (__all_sync(kFullWarp, first + kTileRows / 2 <= coded)) {
+    // Every lane of the warp has all 16 rows in its stream: no per-lane conditions except the
+    // rare entry that is not a full pair, found by a warp vote so that the common case is one
+    // uniform branch.  The four tile addresses a lane uses (see tile_slot_xor):
+    const uint32_t slot[4] = {t.tile_lane ^ tile_slot_xor<kLaneMask>(0, lane_mask),
+                              t.tile_lane ^ tile_slot_xor<kLaneMask>(1, lane_mask),
+                              t.tile_lane ^ tile_slot_xor<kLaneMask>(2, lane_mask),
+                              t.tile_lane ^ tile_slot_xor<kLaneMask>(3, lane_mask)};
+    UniformPairs<kHalf, 0, Reader, Slices>::run(r, t, slot, rare_length, slices);
     return;
   }
-  for (int p = 0; p < kTilePairs; ++p) {
+#pragma unroll 1
+  for (int p = kHalf * kHalfPairs; p < (kHalf + 1) * kHalfPairs; ++p) {
     const int step = step0 + 2 * p;
     uint32_t pair = 0;
     if (step + 2 <= coded) {
-      const uint32_t bits = r.peek0();
-      pair = sh.table[table_slot(bits)];
-      if ((int32_t)pair < 0) pair = slow_pair(r, pair, bits, sh, rare_length);
-      r.advance((int)(pair >> 24));
+      const uint32_t before = r.window();
+      pair = load_shared_u32(entry_address(before, t.table));
+      r.take_pair(pair);
+      if ((int32_t)pair < 0) {
+        pair = finish_slow_pair(r, pair, before, t, rare_length);
+      } else {
+        r.refill();
+      }
+      pair >>= 8;
     } else if (step >= tail_from) {
       const uint32_t t0 = tail_bytes[step - tail_from], t1 = tail_bytes[step + 1 - tail_from];
       pair = ((t0 + 127u) & 255u) | (((t1 + 127u) & 255u) << 8);
     } else if (step + 1 == coded) {
-      int l0;
-      const uint32_t bits = r.peek0();
-      pair = symbol_of(sh.table[table_slot(bits)], bits, sh, rare_length, &l0);
-      r.advance(l0);
+      // The lane's last coded step is the first row of this pair.
+      const uint32_t before = r.window();
+      const uint32_t entry = load_shared_u32(entry_address(before, t.table));
+      pair = entry_first_symbol(entry);
+      if (entry & kEscape)
+        pair = load_shared_u8(t.byte_table + ((before >> (rare_length + 2)) & 255u));
+      r.take(entry_first_length(entry));
     }
-    tile[p * 32 + (lane32 ^ ((2 * p) & lane_mask))] = (uint16_t)pair;
+    store_shared_u16_at((t.tile_lane ^ tile_slot_xor<kLaneMask>(p, lane_mask)) + (uint32_t)(p * 64),
+                        pair);
   }
+  slices.rest();
+}
+
+// Lane phase for one whole tile, nothing interleaved.
+template <int kLaneMask, typename Reader>
+__device__ __forceinline__ void decode_tile_rows(Reader& r, const LaneTables& t, int step0,
+                                                 int coded, int tail_from,
+                                                 const uint8_t* tail_bytes, int rare_length,
+                                                 int lane_mask) {
+  NoSlices none;
+  decode_half_rows<kLaneMask, 0>(r, t, step0, coded, tail_from, tail_bytes, rare_length, lane_mask,
+                                 none);
+  decode_half_rows<kLaneMask, 1>(r, t, step0, coded, tail_from, tail_bytes, rare_length, lane_mask,
+                                 none);
 }
 
 struct NoExtraWork {
@@ -206,26 +389,27 @@ struct NoExtraWork {
 // `before_barrier` runs once per thread after this block's loads have been issued and before
 // the closing barrier (work of the caller that the same barrier should publish).
 template <typename Extra = NoExtraWork>
-__device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payload,
-                                              const OperandView& a, const Shape& g, int64_t block,
+__device__ __forceinline__ void prepare_block(const OperandShared& sh, const OperandView& a,
+                                              const Shape& g, int64_t block,
                                               Extra before_barrier = Extra()) {
   const int tid = threadIdx.x;
+  DecodeHead& head = *sh.head;
   // Word w of the block's 256 streams is one contiguous, 1 KB aligned row.
   const uint32_t* rows = a.encoded + block * kLanes;
   for (int i = tid; i < g.fixed_words * (kLanes / 4); i += kThreads) {
     const int w = i >> 6, c = (i & 63) * 4;
-    cp_async_16(&payload[w * kLanes + c], rows + (int64_t)w * g.streams + c);
+    cp_async_16(&sh.image[w * kLanes + c], rows + (int64_t)w * g.streams + c);
   }
-  payload[g.fixed_words * kLanes + tid] = 0u;
-  payload[(g.fixed_words + 1) * kLanes + tid] = 0u;
+  sh.image[g.fixed_words * kLanes + tid] = 0u;
+  sh.image[(g.fixed_words + 1) * kLanes + tid] = 0u;
 
   // The codebook's table for this tensor's center, ready to use (symbols are exponent bytes).
   const int center = *a.center;
   const uint32_t* source = a.pair_table + (size_t)((center + 128) & 255) * kPairEntries;
   for (int i = tid; i < kPairEntries / 4; i += kThreads) cp_async_16(&sh.table[4 * i], source + 4 * i);
-  sh.index_to_byte[tid] = (uint8_t)index_to_exponent_byte((uint32_t)tid, center);
-  sh.overflow_start[tid] = (uint16_t)g.steps;
-  sh.overflow_offset[tid] = 0;
+  head.index_to_byte[tid] = (uint8_t)index_to_exponent_byte((uint32_t)tid, center);
+  head.overflow_start[tid] = (uint16_t)g.steps;
+  head.overflow_offset[tid] = 0;
   __syncthreads();
   if (a.mode != 0) {
     bool usable = true;
@@ -248,10 +432,10 @@ __device__ __forceinline__ void prepare_block(DecodeShared& sh, uint32_t* payloa
         start = a.starts[start_at + tid];
       }
       int unused;
-      const int prefix = block_exclusive_scan(tid < count ? g.steps - start : 0, sh.scan, &unused);
+      const int prefix = block_exclusive_scan(tid < count ? g.steps - start : 0, head.scan, &unused);
       if (tid < count) {
-        sh.overflow_start[lane] = (uint16_t)start;
-        sh.overflow_offset[lane] = byte_base + prefix;
+        head.overflow_start[lane] = (uint16_t)start;
+        head.overflow_offset[lane] = byte_base + prefix;
       }
     }
   }
@@ -265,12 +449,36 @@ __device__ __forceinline__ const uint8_t* tail_origin(const OperandView& a) {
   return a.tail + a.base;
 }
 
+// Per-lane state of a decoding thread, set up after prepare_block.
+struct LaneState {
+  LaneReader reader;
+  LaneTables tables;
+  const uint8_t* tail_bytes;
+  int tail_from;
+  int coded;
+};
+
+__device__ __forceinline__ LaneState open_lane(const OperandShared& sh, const OperandView& a,
+                                               const Shape& g, int valid) {
+  const int tid = threadIdx.x;
+  LaneState s;
+  s.tail_from = sh.head->overflow_start[tid];
+  s.coded = min(valid, s.tail_from);
+  s.tail_bytes = a.mode ? tail_origin(a) + sh.head->overflow_offset[tid] : nullptr;
+  s.reader.open(sh.image, tid, g.fixed_words);
+  s.tables.table = shared_address(sh.table);
+  s.tables.byte_table = shared_address(sh.head->index_to_byte);
+  s.tables.tile_lane = shared_address(&sh.head->tile[tid >> 5][tid & 31]);
+  return s;
+}
+
 // Where one row-phase unit (row pair p of the tile, 8-column subgroup j4 of the
-// warp's 32 columns) lives in the tensor.
+// warp's 32 columns) lives in the tensor and in the tile.
 struct UnitPlace {
   int64_t logical;   // element offset of the top row's first column
   int64_t storage;   // byte offset of the top row's first lane in the side bytes
   uint32_t q;        // pair permutation between lane order and column order
+  int tile_index;    // uint16 index of the unit's 8 tile entries (column order)
 };
 
 __device__ __forceinline__ UnitPlace place_unit(int warp, int p, int j4, int64_t row0, int step0,
@@ -279,28 +487,41 @@ __device__ __forceinline__ UnitPlace place_unit(int warp, int p, int j4, int64_t
   const int64_t tile_row = row0 + step0;
   const int in_tile = (2 * p) & lane_mask;
   const int group = warp ^ ((int)(tile_row & lane_mask) >> 5);
+  const int swapped = (8 * j4) ^ (in_tile & 0x18);
   UnitPlace u;
   u.logical = (tile_row + 2 * p) * kLanes + 32 * group + 8 * j4;
-  u.storage = block_base + (int64_t)(step0 + 2 * p) * kLanes + 32 * warp + ((8 * j4) ^ (in_tile & 0x18));
+  u.storage = block_base + (int64_t)(step0 + 2 * p) * kLanes + 32 * warp + swapped;
   u.q = (uint32_t)(in_tile >> 1) & 3u;
+  u.tile_index = p * 32 + swapped;
   return u;
 }
 
-// Rebuild the 8 BF16 values (4 words, column order) of one row from the unit's
-// tile words and that row's side bytes (lane order).
-__device__ __forceinline__ void join_row(const uint4& tile_words, uint2 side_lane_order, uint32_t q,
-                                         bool second_row, uint32_t out[4]) {
-  const uint32_t pick = second_row ? 0x7531u : 0x6420u;
-  const uint32_t e03 = prmt(tile_words.x, tile_words.y, pick);
-  const uint32_t e47 = prmt(tile_words.z, tile_words.w, pick);
-  const uint32_t s03 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_low(q));
-  const uint32_t s47 = prmt(side_lane_order.x, side_lane_order.y, pair_selector_high(q));
-  const uint32_t l03 = bf16_low_bytes(e03, s03), h03 = bf16_high_bytes(e03, s03);
-  const uint32_t l47 = bf16_low_bytes(e47, s47), h47 = bf16_high_bytes(e47, s47);
-  out[0] = prmt(l03, h03, 0x5140);
-  out[1] = prmt(l03, h03, 0x7362);
-  out[2] = prmt(l47, h47, 0x5140);
-  out[3] = prmt(l47, h47, 0x7362);
+// PRMT selectors that spread the side bytes of lane pair (i ^ q) of an 8-lane group over the
+// two BF16 halves of output word i: bytes [s_a, s_a, s_b, s_b].
+struct SideSelectors {
+  uint32_t word[4];
+};
+__device__ __forceinline__ SideSelectors side_selectors(uint32_t q) {
+  SideSelectors s;
+#pragma unroll
+  for (uint32_t i = 0; i < 4; ++i) s.word[i] = 0x1100u + 2u * (i ^ q) * 0x1111u;
+  return s;
+}
+
+// Rebuild the 8 BF16 values (4 words, column order) of one row from the unit's tile words
+// (column pairs, both rows) and that row's side bytes (lane order).  Per output word:
+// exponents of the row into bits 7..14 of both halves (one shift), side bytes spread by one
+// byte permute, merged by one bit select.
+__device__ __forceinline__ void join_row(const uint4& tile_words, uint2 side_lane_order,
+                                         const SideSelectors& sel, bool second_row,
+                                         uint32_t out[4]) {
+  const uint32_t tw[4] = {tile_words.x, tile_words.y, tile_words.z, tile_words.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t exponents = second_row ? (tw[i] >> 1) : (tw[i] << 7);
+    const uint32_t sides = prmt(side_lane_order.x, side_lane_order.y, sel.word[i]);
+    out[i] = (exponents & 0x7F807F80u) | (sides & 0x807F807Fu);
+  }
 }
 
 struct OpSpec {

@@ -2,18 +2,21 @@
 //
 // One CTA (256 threads) per codec block; between the prologue and the epilogue
 // every warp runs on its own (see common.cuh: a warp's 32 lanes own one
-// 64-byte segment of every row).  Per 32-row tile, per warp:
-//   row phase  - thread = 8 columns of a row pair: 128-bit loads of the BF16
-//                source (requested one tile ahead), four values at a time
-//                split into exponent bytes -> column-ordered shared tile and
-//                side bytes -> lane order, stored 64 bits at a time;
-//   lane phase - thread = lane: reads its exponent pair from the tile, fetches
-//                both (code, length) entries from the shared encode table,
-//                appends them at its absolute bit position and drops finished
-//                32-bit words into a shared image of the block's payload.
+// 64-byte segment of every row).  Per half tile of 16 rows, per warp:
+//   row side  - thread = 8 columns of a row pair: 128-bit loads of the BF16
+//               source (requested one half tile ahead), four values at a time
+//               split into exponent bytes -> the warp's shared tile and side
+//               bytes -> lane order, stored 64 bits at a time;
+//   lane side - thread = lane: two byte loads of its exponent pair from the
+//               tile, both (code, length) rows of the shared encode table,
+//               code appended at the lane's bit position; a finished 32-bit
+//               word goes into a shared image of the block's payload by
+//               predicated instructions (encode_core.cuh).
 // At the end the payload image (zero where nothing was written, so the output
 // is deterministic) is copied out with coalesced 128-bit stores, and the
 // block's overflow summary is reduced.
+#include <type_traits>
+
 #include "batch.cuh"
 #include "common.cuh"
 #include "encode_core.cuh"
@@ -21,10 +24,9 @@
 
 namespace lct {
 
-// Resident CTAs per SM the encoder is compiled for (register cap = 65536 / 256 / this).
-#ifndef LCT_ENCODE_MIN_CTAS
-#define LCT_ENCODE_MIN_CTAS 4
-#endif
+// Resident CTAs per SM the encoder is compiled for (register cap = 65536 / 256 / this; five or
+// six were measured slower, 63.5 and 65.7 us against 61.5 for 64 Mi elements).
+constexpr int kEncodeMinCtas = 4;
 
 struct EncodeShape {
   int64_t size;
@@ -94,6 +96,84 @@ __device__ __forceinline__ UnitSource load_unit(const void* src, int64_t at, int
   return u;
 }
 
+// Row side of one half tile (16 rows) for one thread: 8 columns of one row pair - field split,
+// side bytes to global memory in lane order, exponent bytes into the warp's tile.  Cut into
+// slices (the form a lane phase can issue between its lookups); the last slice requests the
+// source of the half tile after this one.
+template <bool kPrecomputed>
+struct EncodeRowSlices {
+  const void* src;
+  uint8_t* side;
+  uint16_t* tile;
+  int64_t logical_numel, row0, block_base;
+  int halves, warp, lane32, lane_mask;
+  bool vector_ok, full_block;
+  int h = 0;           // the half tile whose source is in `source`
+  UnitSource source;
+  uint32_t l03, h03, l47, h47, bl03, bh03, bl47, bh47;
+  uint32_t e_top03, e_top47, e_bot03, e_bot47;
+
+  __device__ __forceinline__ int pair() const { return kHalfPairs * (h & 1) + (lane32 >> 2); }
+  // Request the source rows of half tile `which` (nothing when it does not exist).
+  __device__ __forceinline__ void request(int which) {
+    h = which;
+    if (which >= halves) return;
+    const int64_t row = row0 + kTileRows * (which >> 1) + 2 * pair();
+    const int64_t logical =
+        row * kLanes + 32 * (warp ^ ((int)(row & lane_mask) >> 5)) + 8 * (lane32 & 3);
+    source = load_unit<kPrecomputed>(src, logical, logical_numel, vector_ok, full_block);
+  }
+  template <int k>
+  __device__ __forceinline__ void slice() {
+    const int p = pair();
+    const int in_tile = (2 * p) & lane_mask;
+    const int swapped = (8 * (lane32 & 3)) ^ (in_tile & 0x18);
+    if (kPrecomputed) {
+      if (k == 0) {
+        e_top03 = source.top.x; e_top47 = source.top.y;
+        e_bot03 = source.bottom.x; e_bot47 = source.bottom.y;
+      }
+    } else {
+      const uint32_t q = (uint32_t)(in_tile >> 1) & 3u;
+      uint8_t* s = side + block_base + (int64_t)(kTileRows * (h >> 1) + 2 * p) * kLanes + 32 * warp + swapped;
+      if (k == 0) {
+        const uint4 t = source.top;
+        l03 = prmt(t.x, t.y, 0x6420); h03 = prmt(t.x, t.y, 0x7531);
+        l47 = prmt(t.z, t.w, 0x6420); h47 = prmt(t.z, t.w, 0x7531);
+      }
+      if (k == 1) {
+        const uint4 b = source.bottom;
+        bl03 = prmt(b.x, b.y, 0x6420); bh03 = prmt(b.x, b.y, 0x7531);
+        bl47 = prmt(b.z, b.w, 0x6420); bh47 = prmt(b.z, b.w, 0x7531);
+      }
+      if (k == 2) {
+        e_top03 = exponent_bytes(l03, h03); e_top47 = exponent_bytes(l47, h47);
+        // Side bytes: column order -> lane order, one 8-byte store per row.
+        const uint32_t s03 = side_bytes(l03, h03), s47 = side_bytes(l47, h47);
+        __stcs(reinterpret_cast<uint2*>(s),
+               make_uint2(prmt(s03, s47, pair_selector_low(q)), prmt(s03, s47, pair_selector_high(q))));
+      }
+      if (k == 3) {
+        e_bot03 = exponent_bytes(bl03, bh03); e_bot47 = exponent_bytes(bl47, bh47);
+        const uint32_t s03 = side_bytes(bl03, bh03), s47 = side_bytes(bl47, bh47);
+        __stcs(reinterpret_cast<uint2*>(s + kLanes),
+               make_uint2(prmt(s03, s47, pair_selector_low(q)), prmt(s03, s47, pair_selector_high(q))));
+      }
+    }
+    if (k == 4) {
+      // tile word for columns (2k, 2k+1): [e_top(2k), e_bot(2k), e_top(2k+1), e_bot(2k+1)];
+      // the unit's group of 8 sits where its lanes are (see tile_slot_xor).
+      *reinterpret_cast<uint4*>(&tile[p * 32 + swapped]) =
+          make_uint4(prmt(e_top03, e_bot03, 0x5140), prmt(e_top03, e_bot03, 0x7362),
+                     prmt(e_top47, e_bot47, 0x5140), prmt(e_top47, e_bot47, 0x7362));
+    }
+    if (k == 5) request(h + 1);
+  }
+  __device__ __forceinline__ void rest() {
+    slice<0>(); slice<1>(); slice<2>(); slice<3>(); slice<4>(); slice<5>();
+  }
+};
+
 // One codec block.  extra_starts and summaries are the tensor's own arrays
 // (summaries holds g.n_blocks entries per row).
 // kLaneMask: the lane mapping as a compile-time constant (254, the default mapping), or -1 to
@@ -120,25 +200,35 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   const int budget_bits = g.fixed_words * 32;
   uint16_t* tile = sh.tile[warp];
-  const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
+  const uint32_t tile_lane = shared_address(&tile[lane32]);
+  const uint32_t table_address = shared_address(sh.table);
   uint32_t* payload_column = payload + tid;
+  const SharedWordSink sink{shared_address(payload_column)};
   uint32_t lo = 0;
   int pos = 0;
   int extra_start = -1;  // first overflowing step, -1 = none
   bool open = true;
 
-  // This thread's two row-phase units: row pair p, 8-column subgroup j4.
-  const int j4 = lane32 & 3;
-  const int unit_p[2] = {lane32 >> 2, (lane32 >> 2) + 8};
-  auto logical_of = [&](int step) {
-    const int64_t row = row0 + step;
-    return row * kLanes + 32 * (warp ^ ((int)(row & g.lane_mask) >> 5)) + 8 * j4;
-  };
-  UnitSource source[2];
-#pragma unroll
-  for (int u = 0; u < 2; ++u)
-    source[u] = load_unit<kPrecomputed>(src, logical_of(2 * unit_p[u]), g.logical_numel,
-                                        src_vector_ok, full_block);
+  // Rows of this block that hold elements.  Half tiles of pure padding (the tail of a ragged or
+  // tiny tensor) carry no bits; their side bytes are cleared in one sweep after the loop.
+  const int rows_used =
+      full_block ? g.steps : (int)((g.logical_numel - block_base + kLanes - 1) / kLanes);
+  const int halves = (rows_used + kTileRows / 2 - 1) / (kTileRows / 2);
+
+  EncodeRowSlices<kPrecomputed> rows;
+  rows.src = src;
+  rows.side = side;
+  rows.tile = tile;
+  rows.logical_numel = g.logical_numel;
+  rows.vector_ok = src_vector_ok;
+  rows.full_block = full_block;
+  rows.halves = halves;
+  rows.warp = warp;
+  rows.lane32 = lane32;
+  rows.row0 = row0;
+  rows.block_base = block_base;
+  rows.lane_mask = g.lane_mask;
+  rows.request(0);
   // Everything above is independent of the tensor's center.  The shifted table may come from
   // a kernel that is still running when this grid was launched with programmatic stream
   // serialisation (lct_compress): wait for it only now, with the first source rows in flight.
@@ -152,66 +242,41 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
   }
   __syncthreads();
 
-  // Rows of this block that hold elements.  Tiles of pure padding (the tail of a ragged or tiny
-  // tensor) carry no bits; their side bytes are cleared in one sweep after the loop.
-  const int rows_used =
-      full_block ? g.steps : (int)((g.logical_numel - block_base + kLanes - 1) / kLanes);
-  for (int step0 = 0; step0 < rows_used; step0 += kTileRows) {
-    // ---- row phase ----
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int p = unit_p[u];
-      const int step = step0 + 2 * p;
-      uint32_t e_top03, e_top47, e_bot03, e_bot47;
-      if (kPrecomputed) {
-        e_top03 = source[u].top.x; e_top47 = source[u].top.y;
-        e_bot03 = source[u].bottom.x; e_bot47 = source[u].bottom.y;
-      } else {
-        const uint4 t = source[u].top, b = source[u].bottom;
-        const uint32_t tl03 = prmt(t.x, t.y, 0x6420), th03 = prmt(t.x, t.y, 0x7531);
-        const uint32_t tl47 = prmt(t.z, t.w, 0x6420), th47 = prmt(t.z, t.w, 0x7531);
-        const uint32_t bl03 = prmt(b.x, b.y, 0x6420), bh03 = prmt(b.x, b.y, 0x7531);
-        const uint32_t bl47 = prmt(b.z, b.w, 0x6420), bh47 = prmt(b.z, b.w, 0x7531);
-        e_top03 = exponent_bytes(tl03, th03); e_top47 = exponent_bytes(tl47, th47);
-        e_bot03 = exponent_bytes(bl03, bh03); e_bot47 = exponent_bytes(bl47, bh47);
-        // Side bytes: column order -> lane order, one 8-byte store per row.
-        // mask bits 1..4 of this row pair are 2p & lane_mask (tiles start on multiples of 32 rows).
-        const int in_tile = (2 * p) & g.lane_mask;
-        const uint32_t q = (uint32_t)(in_tile >> 1) & 3u;
-        uint8_t* s = side + block_base + (int64_t)step * kLanes + 32 * warp + ((8 * j4) ^ (in_tile & 0x18));
-        const uint32_t ts03 = side_bytes(tl03, th03), ts47 = side_bytes(tl47, th47);
-        const uint32_t bs03 = side_bytes(bl03, bh03), bs47 = side_bytes(bl47, bh47);
-        __stcs(reinterpret_cast<uint2*>(s),
-               make_uint2(prmt(ts03, ts47, pair_selector_low(q)), prmt(ts03, ts47, pair_selector_high(q))));
-        __stcs(reinterpret_cast<uint2*>(s + kLanes),
-               make_uint2(prmt(bs03, bs47, pair_selector_low(q)), prmt(bs03, bs47, pair_selector_high(q))));
+  // Half tiles of 16 rows alternate between the two sides: the row side splits half tile h + 1
+  // into the free half of the warp's tile buffer (and ends by requesting the source of half
+  // tile h + 2, which then has a whole lane phase to arrive), the lanes encode half tile h.
+  // Issuing the row side's work between the lanes' lookups instead (one instruction stream)
+  // was measured slower: 66-68 us against 61.5 for 64 Mi elements.
+  rows.rest();   // half tile 0; leaves the source of half tile 1 requested
+  __syncwarp();
+  NoSlices nothing;
+  auto lanes = [&](auto half_tag, int h) {
+    constexpr int kHalf = decltype(half_tag)::value;
+    if (full_block)
+      encode_half_rows<false, kLaneMask, kHalf>(table_address, tile_lane, sink, g.lane_mask,
+                                                kTileRows * (h >> 1), valid, budget_bits, pos, lo,
+                                                extra_start, open, nothing);
+    else
+      encode_half_rows<true, kLaneMask, kHalf>(table_address, tile_lane, sink, g.lane_mask,
+                                               kTileRows * (h >> 1), valid, budget_bits, pos, lo,
+                                               extra_start, open, nothing);
+  };
+  for (int h = 0; h < halves; h += 2) {
+    lanes(std::integral_constant<int, 0>(), h);
+    __syncwarp();
+    if (h + 1 < halves) {
+      rows.rest();
+      __syncwarp();
+      lanes(std::integral_constant<int, 1>(), h + 1);
+      __syncwarp();
+      if (h + 2 < halves) {
+        rows.rest();
+        __syncwarp();
       }
-      // tile word for columns (2k, 2k+1): [e_top(2k), e_bot(2k), e_top(2k+1), e_bot(2k+1)]
-      *reinterpret_cast<uint4*>(&tile[p * 32 + 8 * j4]) =
-          make_uint4(prmt(e_top03, e_bot03, 0x5140), prmt(e_top03, e_bot03, 0x7362),
-                     prmt(e_top47, e_bot47, 0x5140), prmt(e_top47, e_bot47, 0x7362));
     }
-    __syncwarp();
-    // Request the next tile's source now; it arrives while the lanes encode.
-    if (step0 + kTileRows < rows_used) {
-#pragma unroll
-      for (int u = 0; u < 2; ++u)
-        source[u] = load_unit<kPrecomputed>(src, logical_of(step0 + kTileRows + 2 * unit_p[u]),
-                                            g.logical_numel, src_vector_ok, full_block);
-    }
-    // ---- lane phase ----
-    if (open) {
-      if (full_block)
-        open = encode_tile_rows<false>(sh.table, tile_bytes, payload_column, kLanes, lane32, g.lane_mask, step0, valid,
-                                       budget_bits, pos, lo, extra_start);
-      else
-        open = encode_tile_rows<true>(sh.table, tile_bytes, payload_column, kLanes, lane32, g.lane_mask, step0, valid,
-                                      budget_bits, pos, lo, extra_start);
-    }
-    __syncwarp();
   }
   if (!kPrecomputed && !full_block) {
-    const int first_untouched = (rows_used + kTileRows - 1) / kTileRows * kTileRows;
+    const int first_untouched = halves * (kTileRows / 2);
     uint4* rest = reinterpret_cast<uint4*>(side + block_base + (int64_t)first_untouched * kLanes);
     for (int i = tid; i < (g.steps - first_untouched) * (kLanes / 16); i += kThreads)
       __stcs(rest + i, make_uint4(0u, 0u, 0u, 0u));
@@ -245,7 +310,7 @@ __device__ __forceinline__ void encode_block(const void* __restrict__ src, bool 
 }
 
 template <bool kPrecomputed, int kLaneMask>
-__global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kEncodeMinCtas)
 encode_kernel(const void* __restrict__ src, bool src_vector_ok, uint8_t* __restrict__ side,
               uint32_t* __restrict__ encoded, const int32_t* __restrict__ shifted_encode,
               uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries, EncodeShape g) {
@@ -275,7 +340,7 @@ __device__ __forceinline__ int find_encode_job(const Job* jobs, int n_jobs, int6
 }
 
 template <int kLaneMask>
-__global__ void __launch_bounds__(kThreads, LCT_ENCODE_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kEncodeMinCtas)
 encode_batch_kernel(const lct_encode_job* __restrict__ jobs, int n_jobs,
                     const int32_t* __restrict__ shifted_encode, uint8_t* __restrict__ extra_starts,
                     int32_t* __restrict__ summaries, EncodeShape common) {

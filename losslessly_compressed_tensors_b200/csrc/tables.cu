@@ -161,29 +161,28 @@ shift_tables_kernel(const int32_t* __restrict__ base_encode, const int32_t* __re
 // center (CTA c serves center c - 128), symbols stored as raw exponent bytes so
 // a decoder copies the table of its tensor's center and uses it as it is.  The
 // second symbol is present only when both codes are direct and fit in the 12
-// bits together.  The entry for stream window i is stored at table_slot(i).
+// bits together.  The entry for stream window i is stored at table_slot(i) = i.
 __global__ void __launch_bounds__(kTableThreads)
 pair_table_kernel(const int32_t* __restrict__ decode, int rare_length,
                   uint32_t* __restrict__ pair_table) {
   const int center = (int)blockIdx.x - 128;
   uint32_t* table = pair_table + (size_t)blockIdx.x * kPairEntries;
   for (int slot = threadIdx.x; slot < kPairEntries; slot += blockDim.x) {
-    const int i = (int)table_window((uint32_t)slot);
+    const int i = slot;  // table_slot is the identity on 12-bit windows
     const int32_t first = decode[i & kFirstMask];
     uint32_t entry;
     if (first == 0) {
-      entry = kSlow | kEscape | ((uint32_t)(rare_length + 8) << 16);  // prefix + 8-bit literal
+      entry = make_single_entry((uint32_t)(rare_length + 8), 0u, true);  // prefix + 8-bit literal
     } else {
       const uint32_t len0 = (uint32_t)first & 255u;
       const uint32_t byte0 = index_to_exponent_byte(((uint32_t)first >> 8) & 255u, center);
-      entry = byte0 | (len0 << 16);
       const int32_t second = decode[(i >> len0) & kFirstMask];
       const uint32_t len1 = (uint32_t)second & 255u;
       if (second != 0 && len0 + len1 <= (uint32_t)kPairBits) {
         const uint32_t byte1 = index_to_exponent_byte(((uint32_t)second >> 8) & 255u, center);
-        entry |= byte1 << 8 | (len0 + len1) << 24;
+        entry = make_pair_entry(len0, byte0, len1, byte1);
       } else {
-        entry |= kSlow;
+        entry = make_single_entry(len0, byte0, false);
       }
     }
     table[slot] = entry;

@@ -36,15 +36,51 @@ namespace lct {
 // when a stream uses its whole budget; the refill pointer is clamped to that
 // last row on every pair).
 
+// Read position of one sampled lane: a 96-bit register window over its shared column (the
+// word under the position and the two after it) plus the bit offset inside the first word.
+struct BitReader {
+  const uint32_t* next_row;  // column word that enters the window at the next refill
+  const uint32_t* last_row;  // the column's last zero row
+  uint32_t cur, n1, n2;
+  int shift;                 // 0..31 between pairs
+
+  // `column`: fixed_words + 2 rows with stride kLanes, the last two zero.
+  __device__ __forceinline__ void open(const uint32_t* column, int fixed_words) {
+    cur = column[0];
+    n1 = column[kLanes];
+    n2 = column[2 * kLanes];
+    next_row = column + 3 * kLanes;
+    last_row = column + (fixed_words + 1) * kLanes;
+    shift = 0;
+  }
+  __device__ __forceinline__ void tile_start() {
+    if (next_row > last_row) next_row = last_row;
+  }
+  // 32 stream bits starting `extra` bits after the position (shift + extra < 64).
+  __device__ __forceinline__ uint32_t peek(int extra) const {
+    const int s = shift + extra;
+    const bool far = s >= 32;
+    return __funnelshift_r(far ? n1 : cur, far ? n2 : n1, s);  // amount is taken modulo 32
+  }
+  __device__ __forceinline__ uint32_t peek0() const { return __funnelshift_r(cur, n1, shift); }
+  __device__ __forceinline__ void advance(int bits) {  // bits <= 32
+    shift += bits;
+    if (shift >= 32) {
+      shift -= 32;
+      cur = n1;
+      n1 = n2;
+      n2 = *next_row;
+      next_row += kLanes;
+    }
+  }
+};
+
 // One symbol (exponent byte) from an entry and the bits it was looked up with.
 __device__ __forceinline__ uint32_t byte_of(uint32_t entry, uint32_t bits, int rare_length,
                                             int center, int* length) {
-  if (entry & kEscape) {
-    *length = rare_length + 8;
-    return index_to_exponent_byte((bits >> rare_length) & 255u, center);
-  }
-  *length = (int)((entry >> 16) & 15u);
-  return entry & 255u;
+  *length = (int)entry_first_length(entry);
+  if (entry & kEscape) return index_to_exponent_byte((bits >> rare_length) & 255u, center);
+  return entry_first_symbol(entry);
 }
 
 // Raw-tail exponent byte of A at (block, step, lane), or -1 when that step is in the bit stream.
@@ -87,9 +123,9 @@ __device__ __forceinline__ uint32_t walk_to(const uint32_t* __restrict__ table, 
       second = byte_of(__ldg(table + table_slot(bits1)), bits1, g.rare_length, center, &l1);
       consumed = l0 + l1;
     } else {
-      first = entry & 255u;
-      second = (entry >> 8) & 255u;
-      consumed = (int)(entry >> 24);
+      first = entry_first_symbol(entry);
+      second = entry_second_symbol(entry);
+      consumed = (int)(entry & 31u);
     }
     r.advance(consumed);
   }
@@ -209,7 +245,7 @@ __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint3
       make_uint2(prmt(c03, c47, pair_selector_low(q)), prmt(c03, c47, pair_selector_high(q)));
 }
 
-// Shared memory: [input payload image | DecodeShared | encode table].  Finished output
+// Shared memory: [decode table | encode table | the input operand (head | payload image)].  Finished output
 // words go straight to global memory (a warp's lanes write neighbouring words of the same
 // payload rows; L2 merges the sectors), which keeps four CTAs resident per SM.
 // One codec block.  extra_starts and summaries are the tensor's own arrays.
@@ -223,10 +259,8 @@ __device__ __forceinline__ void update_fused_block(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Shape g = g_in;
   if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // compile-time lane mapping, see decode_block
-  const size_t image = (size_t)(g.fixed_words + 2) * kLanes * 4;
-  uint32_t* payload = reinterpret_cast<uint32_t*>(smem_raw);
-  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem_raw + image);
-  uint2* encode_table = reinterpret_cast<uint2*>(smem_raw + image + sizeof(DecodeShared));
+  const OperandShared sh = carve_operand(smem_raw, 0, 1, g.fixed_words, 256 * sizeof(uint2));
+  uint2* encode_table = reinterpret_cast<uint2*>(smem_raw + kTableBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
   const int64_t row0 = block * g.steps;
@@ -236,7 +270,7 @@ __device__ __forceinline__ void update_fused_block(
   // The input operand does not depend on the result's center: its payload is staged and its
   // tables are built before this grid waits for the kernel that writes the shifted encode
   // table (which may still be running when the grid was launched by lct_update).
-  prepare_block(sh, payload, a, g, block, [&] {
+  prepare_block(sh, a, g, block, [&] {
     cudaGridDependencySynchronize();
     const uint32_t packed = (uint32_t)shifted_encode[tid];
     encode_table[tid] = make_uint2(packed & 0xFFFFFu, packed >> 20);
@@ -245,22 +279,21 @@ __device__ __forceinline__ void update_fused_block(
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
-  const int tail_from = sh.overflow_start[tid];
-  const int coded = min(valid, tail_from);
-  const uint8_t* tail_bytes = a.mode ? tail_origin(a) + sh.overflow_offset[tid] : nullptr;
-  BitReader reader;
-  reader.open(payload + tid, g.fixed_words);
-  uint16_t* tile = sh.tile[warp];
+  LaneState lane = open_lane(sh, a, g, valid);
+  uint16_t* tile = sh.head->tile[warp];
   const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(tile);
+  const uint32_t encode_table_address = shared_address(encode_table);
   uint32_t* out_column = encoded_out + block * kLanes + tid;
+  const GlobalWordSink sink{out_column, g.streams};
+  const SideSelectors selectors = side_selectors((uint32_t)(((2 * (lane32 >> 2)) & g.lane_mask) >> 1) & 3u);
   const int budget_bits = g.fixed_words * 32;
   uint32_t lo = 0;
   int pos = 0, extra_start = -1;
   bool open = true;
 
   for (int step0 = 0; step0 < g.steps; step0 += kTileRows) {
-    decode_tile_rows(reader, sh, tile, lane32, step0, coded, tail_from, tail_bytes, g.rare_length,
-                     g.lane_mask);
+    decode_tile_rows<kLaneMask>(lane.reader, lane.tables, step0, lane.coded, lane.tail_from,
+                                lane.tail_bytes, g.rare_length, g.lane_mask);
     __syncwarp();
     // ---- row side: A (op) B, new side bytes out, new exponents back into the tile ----
     // Side bytes of all four rows first (registers allow no more at four CTAs per SM); B's
@@ -278,14 +311,13 @@ __device__ __forceinline__ void update_fused_block(
     }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int p = (lane32 >> 2) + 8 * u, j4 = lane32 & 3;
       const UnitPlace place = place_of[u];
       uint32_t right_in[2][4];
 #pragma unroll
       for (int half = 0; half < 2; ++half)
         load_dense8(other, place.logical + half * kLanes, g.logical_numel, other_vector_ok,
                     right_in[half]);
-      uint4* slot = reinterpret_cast<uint4*>(&tile[p * 32 + 8 * j4]);
+      uint4* slot = reinterpret_cast<uint4*>(&tile[place.tile_index]);
       const uint4 words = *slot;
       uint32_t e_top03, e_top47, e_bot03, e_bot47;
 #pragma unroll
@@ -294,7 +326,7 @@ __device__ __forceinline__ void update_fused_block(
         const int64_t l_at = place.logical + half * kLanes;
         uint32_t left[4], result[4];
         const uint32_t* right = right_in[half];
-        join_row(words, side_in[u][half], place.q, half == 1, left);
+        join_row(words, side_in[u][half], selectors, half == 1, left);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           result[k] = apply_op(left[k], right[k], spec.op, spec.alpha_is_one != 0,
@@ -316,11 +348,13 @@ __device__ __forceinline__ void update_fused_block(
     // ---- lane side: encode the result exponents ----
     if (open) {
       if (full_block)
-        open = encode_tile_rows<false>(encode_table, tile_bytes, out_column, g.streams, lane32, g.lane_mask, step0, valid,
-                                       budget_bits, pos, lo, extra_start);
+        open = encode_tile_rows<false, kLaneMask>(encode_table_address, lane.tables.tile_lane, sink,
+                                                  g.lane_mask, step0, valid, budget_bits, pos, lo,
+                                                  extra_start);
       else
-        open = encode_tile_rows<true>(encode_table, tile_bytes, out_column, g.streams, lane32, g.lane_mask, step0, valid,
-                                      budget_bits, pos, lo, extra_start);
+        open = encode_tile_rows<true, kLaneMask>(encode_table_address, lane.tables.tile_lane, sink,
+                                                 g.lane_mask, step0, valid, budget_bits, pos, lo,
+                                                 extra_start);
     }
     if (!open) {
       // Raw exponents of the overflowed lane, from its overflow step on, for the tail pass.
@@ -330,7 +364,7 @@ __device__ __forceinline__ void update_fused_block(
       for (int p = from; p < kTilePairs; ++p) {
         const int column = lane32 ^ ((2 * p) & g.lane_mask);
         const int64_t logical = (tile_row + 2 * p) * kLanes + 32 * group + column;
-        const uint8_t* e = tile_bytes + 2 * (p * 32 + column);
+        const uint8_t* e = tile_bytes + 2 * (p * 32 + (lane32 ^ ((2 * p) & g.lane_mask & 6)));
         if (logical < g.logical_numel) spill[logical] = e[0];
         if (logical + kLanes < g.logical_numel) spill[logical + kLanes] = e[1];
       }
@@ -351,11 +385,11 @@ __device__ __forceinline__ void update_fused_block(
     bad += __shfl_down_sync(0xFFFFFFFFu, bad, d);
     bytes += __shfl_down_sync(0xFFFFFFFFu, bytes, d);
   }
-  if (lane32 == 0) { sh.scan[warp] = bad; sh.scan[8 + warp] = bytes; }
+  if (lane32 == 0) { sh.head->scan[warp] = bad; sh.head->scan[8 + warp] = bytes; }
   __syncthreads();
   if (tid == 0) {
     int total_bad = 0, total_bytes = 0;
-    for (int w = 0; w < kWarps; ++w) { total_bad += sh.scan[w]; total_bytes += sh.scan[8 + w]; }
+    for (int w = 0; w < kWarps; ++w) { total_bad += sh.head->scan[w]; total_bytes += sh.head->scan[8 + w]; }
     summaries[block] = total_bad;
     summaries[g.n_blocks + block] = total_bytes;
   }

@@ -68,10 +68,25 @@ class Plan:
     offsets: list[list[dict[str, tuple[int, int]]]] = field(default_factory=list)
     arena_offset: list[int] = field(default_factory=list)
     wire_bytes: int = 0
-    # Prepared launches, keyed by the addresses they were prepared for: a training loop that
-    # re-encodes the same parameters into the same wire buffer every step pays the Python cost
-    # of describing 150+ shards once.
+    # Prepared launches, keyed by the addresses AND layouts they were prepared for: a training
+    # loop that re-encodes the same parameters into the same wire buffer every step pays the
+    # Python cost of describing 150+ shards once.  A prepared launch keeps its tensors alive, so
+    # only launches on caller-owned, reusable buffers are kept, and only the most recent few.
     prepared: dict = field(default_factory=dict, repr=False, compare=False)
+    max_prepared: int = 8
+
+    def remember(self, key, value) -> None:
+        """Keep a prepared launch; the oldest entries go once ``max_prepared`` are held."""
+        self.prepared.pop(key, None)
+        self.prepared[key] = value
+        while len(self.prepared) > self.max_prepared:
+            self.prepared.pop(next(iter(self.prepared)))
+
+    def recall(self, key):
+        hit = self.prepared.pop(key, None)
+        if hit is not None:
+            self.prepared[key] = hit     # most recently used last
+        return hit
 
     def shard_blocks(self, shard: Shard) -> int:
         block_symbols = geometry(self.distribution)[0]
@@ -181,6 +196,11 @@ class _Placement:
         return view
 
 
+def _identity(t: torch.Tensor) -> tuple:
+    """What a prepared launch depends on: where a tensor lives and how it is laid out."""
+    return (t.data_ptr(), tuple(t.shape), t.dtype, tuple(t.stride()))
+
+
 def shard_source(tensors: list[torch.Tensor], shard: Shard) -> torch.Tensor:
     """The rows of the weight set that ``shard`` covers (a view when the tensor is contiguous)."""
     tensor = tensors[shard.index]
@@ -224,12 +244,13 @@ def encode_rank(plan: Plan, rank: int, tensors: list[torch.Tensor],
     from .tensor_buffer import TensorBuffer
 
     device = tensors[0].device if tensors else torch.device("cuda")
+    caller_owns_wire = wire is not None
     if wire is None:
         wire = torch.zeros(plan.wire_bytes, dtype=torch.uint8, device=device)
     elif wire.numel() != plan.wire_bytes or wire.dtype != torch.uint8:
         raise ValueError("wire buffer has the wrong size or dtype")
-    key = ("encode", rank, batched, wire.data_ptr(), tuple(t.data_ptr() for t in tensors))
-    hit = plan.prepared.get(key)
+    key = ("encode", rank, batched, wire.data_ptr(), tuple(_identity(t) for t in tensors))
+    hit = plan.recall(key) if caller_owns_wire else None
     if hit is not None and batched:
         batch, compressed, arena, metadata_bytes = hit
         arena._storage[:metadata_bytes].zero_()   # same state as a freshly built arena
@@ -267,10 +288,10 @@ def encode_rank(plan: Plan, rank: int, tensors: list[torch.Tensor],
     batch = dispatch.compress_batch(jobs, encode_table, decode_table, arena,
                                     block_symbols=block_symbols, lanes=lanes, steps=steps,
                                     fixed_words=fixed_words)
-    if all(job["src"].data_ptr() == shard_source(tensors, shard).data_ptr()
-           for job, shard in zip(jobs, plan.shards[rank])):   # no temporary copies involved
-        plan.prepared[key] = (batch, compressed, arena,
-                              TensorBuffer.storage_bytes(0, plan.max_free_regions))
+    if caller_owns_wire and all(job["src"].data_ptr() == shard_source(tensors, shard).data_ptr()
+                                for job, shard in zip(jobs, plan.shards[rank])):   # no temporaries
+        plan.remember(key, (batch, compressed, arena,
+                            TensorBuffer.storage_bytes(0, plan.max_free_regions)))
     return wire, compressed, arena
 
 
@@ -358,11 +379,14 @@ def decode_all(plan: Plan, gathered, shapes: list[tuple[int, ...]], *, batched: 
 
     wires = _wires_of(plan, gathered)
     device = wires[0].device
+    # A prepared launch pins the wire buffers and the outputs it was made for.  Outputs made
+    # here are new on every call, so such a launch could never be reused and is not kept.
+    reusable = outputs is not None
     if outputs is None:
         outputs = [torch.empty(shape, dtype=torch.bfloat16, device=device) for shape in shapes]
     key = ("decode", batched, interleave_from, stage_remote_for,
-           tuple(w.data_ptr() for w in wires), tuple(t.data_ptr() for t in outputs))
-    hit = plan.prepared.get(key)
+           tuple(_identity(w) for w in wires), tuple(_identity(t) for t in outputs))
+    hit = plan.recall(key) if reusable else None
     if hit is not None:
         hit.run()
         return outputs
@@ -392,8 +416,8 @@ def decode_all(plan: Plan, gathered, shapes: list[tuple[int, ...]], *, batched: 
         _, _, rare_length = get_distribution_tables(plan.distribution, device)
         batch = dispatch.decode_batch(jobs, block_symbols=block_symbols, lanes=lanes, steps=steps,
                                       fixed_words=fixed_words, rare_length=rare_length)
-        if direct:
-            plan.prepared[key] = batch
+        if direct and reusable:
+            plan.remember(key, batch)
     return outputs
 
 

@@ -111,7 +111,8 @@ def test_decode_from_per_rank_buffers_matches_the_gathered_path(world, row_shard
                                 stage_remote_for=start % world)
     for want, got in zip(host, staged):
         assert np.array_equal(bits_of(got), bits_of(want))
-    # same launch prepared once per set of buffers, reused on the second call
+    # with caller-owned outputs the launch is prepared once per set of buffers and reused
+    sharded.decode_all(plan, wires, shapes, outputs=restored, interleave_from=start)
     before = len(plan.prepared)
     sharded.decode_all(plan, wires, shapes, outputs=restored, interleave_from=start)
     assert len(plan.prepared) == before
@@ -131,3 +132,28 @@ def test_peer_wire_single_rank_is_a_plain_buffer():
     peer.fence()
     outputs = sharded.decode_all(plan, peer.buffers, [s for _, s in SHAPES], interleave_from=1)
     assert all(torch.equal(a, b) for a, b in zip(outputs, tensors)) and not peer.multicast
+
+
+def test_repeated_default_calls_keep_nothing_alive():
+    """decode_all / all_gather_wire with their defaults make new outputs on every call; a
+    prepared launch would pin them (one dense weight set and one gathered buffer per call)."""
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 1, dist, arena_fraction=0.5)
+    wire, _, _ = sharded.encode_rank(plan, 0, tensors)
+    shapes = [s for _, s in SHAPES]
+    for _ in range(3):
+        sharded.decode_all(plan, sharded.all_gather_wire(wire, plan), shapes)
+    torch.cuda.synchronize()
+    held, entries = torch.cuda.memory_allocated(), len(plan.prepared)
+    for _ in range(20):
+        outputs = sharded.decode_all(plan, sharded.all_gather_wire(wire, plan), shapes)
+        del outputs
+    torch.cuda.synchronize()
+    assert len(plan.prepared) == entries == 0
+    assert torch.cuda.memory_allocated() <= held
+    # caller-owned buffers: at most `max_prepared` launches are ever kept
+    for k in range(plan.max_prepared + 3):
+        outs = [torch.empty(shape, dtype=torch.bfloat16, device="cuda") for shape in shapes]
+        sharded.decode_all(plan, sharded.all_gather_wire(wire, plan), shapes, outputs=outs)
+    assert len(plan.prepared) <= plan.max_prepared
