@@ -5,20 +5,26 @@
 Workload (N = 1): BASELINE configuration 2 - an 8192 x 8192 BF16 weight-like tensor, i.i.d.
 Laplace(0, 0.02) from a fixed seed with 1e-4 of the entries multiplied by 100,
 ``Distribution(LAPLACE, param=0.02)``, CLEAN layout, overflow tails in a shared ``TensorBuffer``.
-One step = one ``compress`` + one ``decompress`` of that tensor.  With N > 1 every rank runs the
-same step on its own tensor (independent tensors partitioned across GPUs: weak scaling, no
+One step = one ``compress`` + one ``decompress`` of such a tensor.  With N > 1 every rank runs
+the same step on its own tensors (independent tensors partitioned across GPUs: weak scaling, no
 data-path collective), and the value is the aggregate over ranks against the slowest rank's time.
 
 Reported value: GB/s of BF16 data through the codec = (2N bytes encoded + 2N bytes decoded) /
 (encode time + decode time), device time from CUDA events with the inputs already in HBM and the
-L2 flushed before each timed phase.  ``e2e`` is the same figure through the public API with host
-buffers: pinned-host -> device copy of the input, compress, decompress, device -> pinned-host copy
-of the decoded tensor, all inside the timed region.
+L2 flushed (512 MiB written) before each timed phase.  Cycling three tensors instead of flushing
+(inputs larger than L2) was measured too: the kernels take the same time and the event spans
+then expose the host's launch latency, so the flush stayed.  ``e2e`` is the same figure
+through the public API with host buffers: pinned-host -> device copy of the input, compress,
+decompress, device -> pinned-host copy of the decoded tensor, all inside the timed region;
+``e2e_copies_only`` is the same loop with the copies alone.
+
+``triton_reference`` (N = 1, when a copy of the reference checkout is present) times the
+reference's own Triton kernels, compiled for this GPU, on the same tensors in a process of its
+own: the bar the kernels here are measured against.
 
 ``--impl reference`` times the CPU implementation of the same path: the C restatement of the
 reference's kernels (the oracle), on all host threads, on the same tensor.  The reference itself
-is a Python/Triton project with no CPU build; its interpreter mode needs the reference checkout,
-which does not exist on the benchmark machine.
+is a Python/Triton project with no CPU build; its interpreter mode needs minutes per step.
 """
 from __future__ import annotations
 
@@ -28,6 +34,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -43,12 +50,58 @@ METRIC = "codec_bf16_gbps_per_gpu"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 L2_FLUSH_BYTES = 512 << 20
+WORKLOAD = ("config2: 8192x8192 BF16 Laplace(0,0.02)+1e-4 outliers x100, LAPLACE/CLEAN, "
+            "shared arena; step = compress + decompress")
+L2_NOTE = f"flushed ({L2_FLUSH_BYTES >> 20} MiB write) before each timed phase"
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
-# summarised in profiles/encode_decode_config2.md.  Reads equal the algorithmic reads; part of the
-# written bytes is still in the 126 MB write-back L2 when the kernel ends, so the sum is below the
-# algorithmic 227.6 MB.
+
+def bench_config(world: int) -> dict:
+    """The ``config`` object of the JSON line, the same for both arms."""
+    return {"workload": WORKLOAD, "l2": L2_NOTE,
+            "parallelism": f"{world} independent tensor(s) per step, one per GPU"}
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of the
+# two kernels on this workload.  Reads equal the algorithmic reads; part of the written bytes is
+# still in the 126 MB write-back L2 when the kernel ends, so the sum is below the algorithmic
+# 227.6 MB.
 NCU_TRAFFIC_BYTES = {"lct_encode": 184_015_360, "lct_decode": 176_469_760}
+
+
+class LaunchTrace:
+    """Counts the library's launches while active and, for the entry points named in ``timed``,
+    brackets each launch with CUDA events on the launching stream (the roofline's durations)."""
+
+    def __init__(self, timed=()):
+        self.timed = set(timed)
+        self.count = 0
+        self.events: dict[str, list] = {name: [] for name in self.timed}
+
+    def __enter__(self):
+        from losslessly_compressed_tensors_b200.kernels import dispatch
+
+        self._dispatch, self._call = dispatch, dispatch._call
+
+        def traced(name, device, *args, launches=1):
+            self.count += launches
+            if name not in self.timed:
+                return self._call(name, device, *args, launches=launches)
+            stream = torch.cuda.current_stream(device)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            self._call(name, device, *args, launches=launches)
+            end.record(stream)
+            self.events[name].append((start, end))
+
+        dispatch._call = traced
+        return self
+
+    def __exit__(self, *exc):
+        self._dispatch._call = self._call
+
+    def milliseconds(self, name: str) -> list[float]:
+        """Durations of the timed launches of ``name`` (call after synchronising)."""
+        return [start.elapsed_time(end) for start, end in self.events[name]]
 
 
 def make_workload(seed: int) -> torch.Tensor:
@@ -180,20 +233,44 @@ def run_reference(args, rank: int):
         return
     bits = make_workload(1).view(torch.int16).numpy().reshape(-1)
     cores = os.cpu_count() or 1
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(args.warmup):
         cpu_leg(bits, cores, 0.0, 1)
     value, steps, used, ms = cpu_leg(bits, cores, 1e9, args.steps)
     sample = f"full workload ({ROWS}x{COLS} BF16), {steps} step(s) of compress+decompress"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "config2: 8192x8192 BF16 Laplace(0,0.02)+1e-4 outliers x100, "
-                               "LAPLACE/CLEAN, shared arena", "where": "host cores"},
+        "config": bench_config(args.gpus), "where": "host cores, one rank",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def triton_reference_leg(timeout_s: int = 420) -> dict:
+    """The reference's own kernels, compiled by Triton for this GPU, timed on configurations 2
+    and 4 in a process of its own (``tests/reference_runner.py``; CUDA events, L2 flushed before
+    every timed call, the reference's single-configuration launch lists)."""
+    import reference_runner
+
+    if not reference_runner.available():
+        return {"unavailable": "no copy of the reference checkout under baseline/_ref"}
+    with tempfile.TemporaryDirectory() as scratch:
+        out = os.path.join(scratch, "reference.json")
+        command = [sys.executable, os.path.join(ROOT, "tests", "reference_runner.py"), "bench",
+                   "--out", out, "--iters", "20"]
+        try:
+            done = subprocess.run(command, capture_output=True, text=True, timeout=timeout_s)
+        except subprocess.TimeoutExpired:
+            return {"unavailable": f"the reference did not finish within {timeout_s} s"}
+        if done.returncode != 0 or not os.path.exists(out):
+            return {"unavailable": "the reference failed: " + done.stderr.strip()[-300:]}
+        with open(out) as handle:
+            result = json.load(handle)
+    result["note"] = ("reference kernels (Triton, compiled without Triton's warp-specialisation "
+                      "pass, which aborts on its decoder for sm_100); L2 flushed before every call")
+    return result
 
 
 def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2, with_peer: bool = False) -> dict:
@@ -219,9 +296,10 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2, with_pee
     plan = sharded.make_plan(shapes, world, dist_cfg, row_shard_elements=4 << 20)
     dense_bytes = 2 * sum(t.numel() for t in tensors)
     wire = torch.zeros(plan.wire_bytes, dtype=torch.uint8, device="cuda")
-    times = {"encode": [], "gather": [], "decode": []}
+    times = {"encode": [], "gather": [], "decode": [], "serial": []}
     gathered = torch.empty(world * plan.wire_bytes, dtype=torch.uint8, device="cuda")
     restored = [torch.empty(s, dtype=torch.bfloat16, device="cuda") for _, s in shapes]
+    # (1) the three phases one after the other: encode, ONE all-gather, decode everything
     for it in range(warmup + steps):
         barrier(world)
         e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -234,23 +312,56 @@ def sharded_leg(rank: int, world: int, steps: int = 5, warmup: int = 2, with_pee
         e[3].record()
         torch.cuda.synchronize()
         if it >= warmup:
-            for key, a, b in (("encode", 0, 1), ("gather", 1, 2), ("decode", 2, 3)):
+            for key, a, b in (("encode", 0, 1), ("gather", 1, 2), ("decode", 2, 3), ("serial", 0, 3)):
                 times[key].append(e[a].elapsed_time(e[b]))
     exact = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors, restored))
     ms = {k: max_over_ranks(statistics.mean(v), world) for k, v in times.items()}
+    # (2) the overlapped step: encode (one CUDA graph), one fence, then source-by-source copies
+    #     out of the peers' memory on a side stream while the main stream decodes what has landed
+    overlapped = {}
+    try:
+        for t in restored:
+            t.zero_()
+        exchange = sharded.WeightSetExchange(plan, rank, tensors, [s for _, s in shapes],
+                                             outputs=restored)
+        spans, encode_spans = [], []
+        for it in range(warmup + 2 * steps):
+            barrier(world)
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            exchange.encode()
+            e[1].record()
+            exchange.exchange_and_decode()
+            e[2].record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                spans.append(e[0].elapsed_time(e[2]))
+                encode_spans.append(e[0].elapsed_time(e[1]))
+        overlapped = {
+            "step_ms": max_over_ranks(statistics.mean(spans), world),
+            "encode_ms": max_over_ranks(statistics.mean(encode_spans), world),
+            "bit_exact": bool(all(torch.equal(a.view(torch.int16), b.view(torch.int16))
+                                  for a, b in zip(tensors, restored))),
+            "multicast_bound": bool(exchange.wires[0].multicast),
+        }
+        del exchange
+    except Exception as error:   # symmetric memory not available on this box / build
+        overlapped = {"unavailable": f"{type(error).__name__}: {error}"[:200]}
     peer = (peer_decode_leg(plan, rank, world, tensors, shapes, steps, warmup)
             if world > 1 and with_peer else None)
+    step_ms = overlapped.get("step_ms", ms["serial"])
     return {
         "workload": "config5: GPT-2-small-shaped weight set, 148 tensors, EMPIRICAL/CLEAN, "
-                    "row-shards <= 4 Mi elements",
+                    "row-shards <= 4 Mi elements; step = encode own shards + exchange + decode all",
         "shards": sum(len(r) for r in plan.shards), "dense_bytes": dense_bytes,
         "wire_bytes_per_rank": plan.wire_bytes, "bit_exact": bool(exact),
         "encode_ms": ms["encode"], "all_gather_ms": ms["gather"], "decode_all_ms": ms["decode"],
+        "serial_step_ms": ms["serial"],
         "encode_gbps_aggregate": dense_bytes / ms["encode"] / 1e6,
         "all_gather_gbps": world * plan.wire_bytes / ms["gather"] / 1e6,
         "decode_gbps_aggregate": world * dense_bytes / ms["decode"] / 1e6,
-        "note": "batched launches prepared once: 4 launches per encode, 1 per decode-all",
-        "peer_decode": peer,
+        "peer_decode": peer, "overlapped": overlapped,
+        "step_ms": step_ms, "step_gbps_aggregate": world * dense_bytes / step_ms / 1e6,
     }
 
 
@@ -445,8 +556,8 @@ def update_leg(steps: int = 10, warmup: int = 3) -> dict:
 
 
 def run_ours(args, rank: int, world: int, local: int):
+    from losslessly_compressed_tensors_b200.codec import encode as encode_module
     from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
-    from losslessly_compressed_tensors_b200.kernels import dispatch
     from losslessly_compressed_tensors_b200.operations import compress, decompress
     from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
 
@@ -465,6 +576,7 @@ def run_ours(args, rank: int, world: int, local: int):
     memory = c.memory_size()
     tails = int(c.fallback_used.item()) + 2 * int(c.fallback_count.item())
     algorithmic = bf16_bytes + c.sign_mantissa.numel() + (c.data.numel() - 4) * 4 + tails
+    oracle_match = full_size_oracle_check(host_x, c, dist_cfg) if rank == 0 else None
     c.free()
     del y
 
@@ -491,7 +603,7 @@ def run_ours(args, rank: int, world: int, local: int):
     barrier(world)
     sampler = ClockSampler(local) if rank == 0 else None
     spans = []
-    with dispatch.LaunchTrace(timed=("lct_decode",)) as trace:
+    with LaunchTrace(timed=("lct_decode",)) as trace:
         wall0 = time.perf_counter()
         for _ in range(args.steps):
             one_step(spans)
@@ -506,10 +618,9 @@ def run_ours(args, rank: int, world: int, local: int):
     kernel_ms = {name: statistics.mean(trace.milliseconds(name)) for name in trace.timed}
     # The encoder kernel on its own: compress() above is one call whose four launches overlap,
     # so the kernel is timed in a pass of its own through the stage-by-stage calls (same kernels).
-    from losslessly_compressed_tensors_b200.codec import encode as encode_module
     encode_module.SINGLE_CALL_PIPELINE = False
     try:
-        with dispatch.LaunchTrace(timed=("lct_encode",)) as encode_trace:
+        with LaunchTrace(timed=("lct_encode",)) as encode_trace:
             for _ in range(max(3, min(args.steps, 20))):
                 flush.zero_()
                 compress(x, dist_cfg, buffer).free()
@@ -517,7 +628,7 @@ def run_ours(args, rank: int, world: int, local: int):
     finally:
         encode_module.SINGLE_CALL_PIPELINE = True
     kernel_ms["lct_encode"] = statistics.mean(encode_trace.milliseconds("lct_encode"))
-    # The same step as one captured CUDA graph (compress + decompress + free, seven launches):
+    # The step as one captured CUDA graph (compress + decompress + free, seven launches):
     # what a caller with fixed shapes pays per step once the host is out of the loop.  Back to
     # back, no L2 flush in between (the 128 MiB input and output are each larger than L2).
     graph_ms = None
@@ -609,15 +720,43 @@ def run_ours(args, rank: int, world: int, local: int):
         assert torch.equal(host_out[k].view(torch.int16), host_x.view(torch.int16))
     verify_buffer(buffer)
     e2e_value = world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9
-    clocks = sampler.finish() if sampler else None   # sampled across both timed regions
+    # The same loop with the copies alone (no codec): what the host link allows.
+    def copy_step(i):
+        k = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[k])
+            dev_in[k].copy_(host_x, non_blocking=True)
+            in_ready[k].record(s_in)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(in_ready[k])
+            host_out[k].copy_(dev_in[k], non_blocking=True)
+            in_free[k].record(s_out)
+            out_done[k].record(s_out)
+
+    for i in range(2):
+        copy_step(i)
+    barrier(world)
+    s, t = event(), event()
+    s.record(main)
+    for i in range(e2e_steps):
+        copy_step(i)
+    main.wait_event(out_done[0])
+    main.wait_event(out_done[1])
+    t.record(main)
+    barrier(world)
+    copy_ms = max_over_ranks(s.elapsed_time(t) / e2e_steps, world)
+    clocks = sampler.finish() if sampler else None   # sampled across the timed regions
 
     del host_out, dev_in, dev_out, x, flush
     legs = set() if args.no_sharded else set(args.legs.split(","))
+    if world > 1:
+        legs.add("peer")      # the peer-memory decode is part of every multi-GPU run
     sharded = sharded_leg(rank, world, with_peer="peer" in legs) if "sharded" in legs else None
     update = update_leg() if (rank == 0 and "update" in legs) else None
     arena = arena_leg() if (rank == 0 and "arena" in legs) else None
     if rank != 0:
         return
+    triton_reference = (triton_reference_leg() if world == 1 and "triton" in legs else None)
     peak, peak_kind = peak_hbm_gbs()
     kernels = {}
     for name, ms in kernel_ms.items():
@@ -635,21 +774,23 @@ def run_ours(args, rank: int, world: int, local: int):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "config2: 8192x8192 BF16 Laplace(0,0.02)+1e-4 outliers x100, "
-                               "LAPLACE/CLEAN, shared arena; step = compress + decompress",
-                   "l2": f"flushed ({L2_FLUSH_BYTES >> 20} MiB write) before each timed phase",
-                   "parallelism": f"{world} independent tensor(s), one per GPU"},
+        "config": bench_config(world),
         "encode_ms": statistics.mean(enc_ms), "decode_ms": statistics.mean(dec_ms),
         "encode_gbps": bf16_bytes / statistics.mean(enc_ms) / 1e6,
         "decode_gbps": bf16_bytes / statistics.mean(dec_ms) / 1e6,
         "compression_ratio": bf16_bytes / memory, "memory_size": memory,
+        "bit_exact_vs_oracle_full_size": oracle_match,
         "wall_ms_per_step": wall / args.steps * 1e3,
         "roofline": roofline, "kernels": kernels,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
-        "gpu_launches": launches, "clocks": clocks, "sharded": sharded, "update": update,
-        "arena": arena, "encode_ms_without_arena": statistics.mean(private_ms),
-        "graph_replay_ms_per_step": graph_ms,
+        "e2e_copies_only": {"value": world * 2 * bf16_bytes / (copy_ms * 1e-3) / 1e9, "unit": UNIT,
+                            "ms_per_step": copy_ms,
+                            "note": "the same pinned H2D + D2H copies per step with no codec "
+                                    "between them: what the host link gives this loop"},
+        "gpu_launches": launches, "clocks": clocks,
+        "encode_ms_without_arena": statistics.mean(private_ms),
+        "graph_replay_ms_per_step": graph_ms, "arena": arena, "update": update,
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)
@@ -658,7 +799,28 @@ def run_ours(args, rank: int, world: int, local: int):
             "value": cpu_value, "unit": UNIT, "cores": used, "kind": "port",
             "sample": f"full workload, {cpu_steps} step(s) of compress+decompress, "
                       f"single-threaded C restatement of the reference kernels"}
+    # Last, so that a reader of the line's tail sees them: the reference's own kernels on this
+    # GPU, and the multi-GPU weight-set step.
+    line["triton_reference"] = triton_reference
+    line["sharded"] = sharded
     print(json.dumps(line))
+
+
+def full_size_oracle_check(host_x: torch.Tensor, c, dist_cfg) -> bool:
+    """Every stored component of the 64 Mi-element result against the CPU restatement."""
+    from helpers import oracle_compress
+    from oracle import lct_oracle as oracle
+
+    oracle.build()
+    oracle.set_threads(0)
+    want = oracle_compress(oracle, host_x.view(torch.int16).numpy().reshape(-1), dist_cfg, None)
+    same = (torch.equal(c.data.cpu(), torch.from_numpy(want["encoded"]))
+            and torch.equal(c.sign_mantissa.cpu(), torch.from_numpy(want["side"]))
+            and torch.equal(c.fallback_blocks.cpu(), torch.from_numpy(want["blocks"]))
+            and int(c.center.item()) == int(want["center"])
+            and int(c.fallback_count.item()) == int(want["count"])
+            and int(c.fallback_used.item()) == int(want["tail_bytes"]))
+    return bool(same)
 
 
 def main():
@@ -670,10 +832,11 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--no-sharded", action="store_true",
                         help="skip the extra legs (configurations 3, 4 and 5)")
-    parser.add_argument("--legs", default="sharded,update,arena",
+    parser.add_argument("--legs", default="sharded,update,arena,triton",
                         help="extra legs to run after configuration 2: sharded (configuration 5), "
-                             "update (configuration 4), arena (configuration 3); add 'peer' to also "
-                             "time the peer-memory decode inside the sharded leg (N > 1)")
+                             "update (configuration 4), arena (configuration 3), triton (the "
+                             "reference's own kernels on this GPU, N = 1); with N > 1 the sharded "
+                             "leg always includes the peer-memory decode")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))

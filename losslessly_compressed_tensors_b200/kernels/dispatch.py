@@ -59,32 +59,6 @@ class _on:
             self.guard.__exit__(*exc)
 
 
-class LaunchTrace:
-    """Counts library launches and, for the entry points named in ``timed``, brackets each
-    launch with CUDA events on the launching stream (used by the benchmark's roofline)."""
-
-    def __init__(self, timed=()):
-        self.timed = set(timed)
-        self.count = 0
-        self.events: dict[str, list] = {name: [] for name in self.timed}
-
-    def __enter__(self):
-        global _trace
-        self._previous, _trace = _trace, self
-        return self
-
-    def __exit__(self, *exc):
-        global _trace
-        _trace = self._previous
-
-    def milliseconds(self, name: str) -> list[float]:
-        """Durations of the timed launches of ``name`` (call after synchronising)."""
-        return [start.elapsed_time(end) for start, end in self.events[name]]
-
-
-_trace: LaunchTrace | None = None
-
-
 try:  # raw handle of the current stream without building a torch.cuda.Stream object
     _raw_stream = torch._C._cuda_getCurrentRawStream
 except AttributeError:  # pragma: no cover - older/newer torch without the private helper
@@ -109,30 +83,18 @@ def _call(name: str, device: torch.device, *args, launches: int = 1) -> None:
     function = _functions.get(name)
     if function is None:
         function = _functions[name] = getattr(_lib.load(), name)
-    if config.lane_mapping is not _applied_lane_mapping:
+    if config.lane_mapping != _applied_lane_mapping:
         _apply_lane_mapping()
     index = device.index
     if index is None:
         index = torch.cuda.current_device()
-    trace = _trace
-    if trace is None and index == torch.cuda.current_device():
+    if index == torch.cuda.current_device():
         code = function(*args, _raw_stream(index))
         if code:
             _lib.check(code, name)
         return
     with _on(device):
-        stream = torch.cuda.current_stream(device)
-        if trace is not None:
-            trace.count += launches
-            if name in trace.timed:
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                start.record(stream)
-                code = function(*args, stream.cuda_stream)
-                end.record(stream)
-                trace.events[name].append((start, end))
-                _lib.check(code, name)
-                return
-        _lib.check(function(*args, stream.cuda_stream), name)
+        _lib.check(function(*args, torch.cuda.current_stream(device).cuda_stream), name)
 
 
 # ---------------------------------------------------------------------------

@@ -476,6 +476,143 @@ class PeerWire:
             dist.all_reduce(self._token, group=self.group)
 
 
+class WeightSetExchange:
+    """One rank's prepared, overlapped step of the weight-set path: encode this rank's shards,
+    move every rank's compressed bytes, decode the whole set.
+
+    ``all_gather_wire`` + ``decode_all`` run the collective strictly before a decode of
+    everything.  Here the two overlap: the wire buffers live in symmetric memory (two of them,
+    used alternately), and after one fence this rank copies the other ranks' buffers into its
+    own memory ONE SOURCE AT A TIME on a side stream (each rank starting at its right neighbour,
+    so that no source serves all readers at once) while the main stream decodes the sources that
+    have already arrived - its own shards first, with no transfer at all.  The step then takes
+    about ``encode + max(transfer, decode)`` instead of their sum, and because the buffers
+    alternate, ONE fence per step is enough: a rank re-uses a buffer two steps later, and it
+    cannot pass the fence in between before every rank has finished reading that buffer.
+
+    The encode side (arena reset + four launches) is captured in a CUDA graph per buffer, so a
+    step costs the host a handful of calls.  Copies are plain device-to-device copies out of the
+    peers' mapped memory and the decoders read local memory only; nothing uses multicast.
+
+    ``tensors``: this rank's view of the dense weight set (every rank holds all of it; it only
+    reads the shards it owns).  ``outputs``: where the decoded set goes (made here if ``None``).
+    """
+
+    def __init__(self, plan: Plan, rank: int, tensors: list[torch.Tensor],
+                 shapes: list[tuple[int, ...]], group=None,
+                 outputs: list[torch.Tensor] | None = None, capture_graphs: bool = True):
+        from .codec.decode import operand_of
+        from .compression.huffman_tables import get_distribution_tables
+        from .kernels import dispatch
+
+        self.plan, self.rank, self.tensors = plan, rank, tensors
+        device = tensors[0].device
+        self.outputs = outputs if outputs is not None else [
+            torch.empty(shape, dtype=torch.bfloat16, device=device) for shape in shapes]
+        self.wires = [PeerWire(plan, rank, group, device) for _ in range(2)]
+        self.world = plan.world
+        # Local copies of the other ranks' buffers (this rank's own shards are decoded in place).
+        self.landing = torch.empty(plan.world * plan.wire_bytes, dtype=torch.uint8, device=device)
+        self.side = torch.cuda.Stream(device=device)
+        self.order = [(rank + k) % plan.world for k in range(1, plan.world)]
+        self.arrived = {source: torch.cuda.Event() for source in self.order}
+        self.fenced = torch.cuda.Event()
+        self.consumed = torch.cuda.Event()
+        self.step_index = 0
+        block_symbols, lanes, steps, fixed_words = geometry(plan.distribution)
+        _, _, rare_length = get_distribution_tables(plan.distribution, device)
+        # One prepared decode launch per (buffer, source rank).
+        self.decoders = []
+        for wire in self.wires:
+            per_source = {}
+            for source in range(plan.world):
+                local = wire.local if source == rank else self.landing[
+                    source * plan.wire_bytes:(source + 1) * plan.wire_bytes]
+                jobs, moves = [], []
+                for shard, compressed in self._views(local, source):
+                    target = self.outputs[shard.index]
+                    rows = target.reshape(()) if target.dim() == 0 else target[shard.row_start:shard.row_stop]
+                    if rows.numel() == 0:
+                        continue
+                    if rows.is_contiguous() and rows.data_ptr() % 16 == 0:
+                        flat = rows.reshape(-1).view(torch.int16)
+                    else:
+                        # The batched decoder stores 16 bytes at a time: rows that do not start
+                        # on such a boundary are decoded next to the set and copied in.
+                        flat = torch.empty(rows.numel(), dtype=torch.int16, device=device)
+                        moves.append((rows, flat.view(torch.bfloat16).view(rows.shape)))
+                    jobs.append((operand_of(compressed), flat, compressed.size, flat.numel()))
+                batch = dispatch.DecodeBatch(
+                    jobs, block_symbols=block_symbols, lanes=lanes, steps=steps,
+                    fixed_words=fixed_words, rare_length=rare_length) if jobs else None
+                per_source[source] = (batch, moves)
+            self.decoders.append(per_source)
+        # Encode launches, prepared (and captured) per buffer.
+        self.encoders = []
+        for wire in self.wires:
+            encode_rank(plan, rank, tensors, wire=wire.local)          # prepares the launch
+            graph = None
+            if capture_graphs:
+                torch.cuda.synchronize(device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    encode_rank(plan, rank, tensors, wire=wire.local)
+            self.encoders.append(graph)
+        torch.cuda.synchronize(device)
+
+    def _views(self, wire: torch.Tensor, source: int):
+        from .tensor_buffer import TensorBuffer
+
+        plan = self.plan
+        start = plan.arena_offset[source] + TensorBuffer.storage_bytes(0, plan.max_free_regions)
+        payload = wire[start:start + plan.arena_capacity]
+        return [(shard, _compressed_view(plan, wire, shard, slots, payload))
+                for shard, slots in zip(plan.shards[source], plan.offsets[source])]
+
+    def encode(self) -> None:
+        """This rank's shards into the buffer of the coming step (current stream)."""
+        which = self.step_index & 1
+        if self.encoders[which] is not None:
+            self.encoders[which].replay()
+        else:
+            encode_rank(self.plan, self.rank, self.tensors, wire=self.wires[which].local)
+
+    def exchange_and_decode(self) -> list[torch.Tensor]:
+        """Fence, then copy and decode source by source (see the class text).  Returns the
+        decoded weight set (``self.outputs``); stream-ordered on the current stream."""
+        which = self.step_index & 1
+        wire, decoders = self.wires[which], self.decoders[which]
+        main = torch.cuda.current_stream()
+        wire.fence()                               # every rank's buffer of this step is complete
+        self.fenced.record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.fenced)
+            self.side.wait_event(self.consumed)    # the previous step's decoders are done with `landing`
+            for source in self.order:
+                at = source * self.plan.wire_bytes
+                self.landing[at:at + self.plan.wire_bytes].copy_(wire.buffers[source], non_blocking=True)
+                self.arrived[source].record(self.side)
+        self._decode(decoders[self.rank])
+        for source in self.order:
+            main.wait_event(self.arrived[source])
+            self._decode(decoders[source])
+        self.consumed.record(main)
+        self.step_index += 1
+        return self.outputs
+
+    @staticmethod
+    def _decode(prepared) -> None:
+        batch, moves = prepared
+        if batch is not None:
+            batch.run()
+        for rows, decoded in moves:
+            rows.copy_(decoded)
+
+    def step(self) -> list[torch.Tensor]:
+        self.encode()
+        return self.exchange_and_decode()
+
+
 def gpt2_small_shapes(layers: int = 12, d_model: int = 768, vocab: int = 50304,
                       context: int = 1024) -> list[tuple[str, tuple[int, ...]]]:
     """The 148 tensors (124 475 904 parameters) of a GPT-2-small-shaped weight set, tied head."""

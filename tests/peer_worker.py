@@ -1,8 +1,8 @@
 """One rank of the multi-GPU test of the peer-memory decode (launched by test_gpu_peer.py with
 RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT set, NCCL backend, one GPU per rank).
 Every rank encodes its shards into its symmetric-memory wire buffer, then decodes the whole
-weight set twice - from the peers' buffers and from an NCCL all-gather - and compares both with
-the original tensors."""
+weight set - from the peers' buffers, from an NCCL all-gather, and through the overlapped
+``WeightSetExchange`` step - and compares every result with the original tensors."""
 import datetime
 import os
 import sys
@@ -50,6 +50,14 @@ def main():
             assert torch.equal(a.view(torch.int16), want.view(torch.int16)), (rank, step)
             assert torch.equal(c.view(torch.int16), want.view(torch.int16)), (rank, step)
             assert torch.equal(b.view(torch.int16), want.view(torch.int16)), (rank, step)
+    # The overlapped step: one fence, source-by-source copies on a side stream, decode as they land.
+    exchange = sharded.WeightSetExchange(plan, rank, tensors, shapes)
+    for step in range(4):                       # both wire buffers are used twice
+        tensors[1].add_(0.25)
+        restored = exchange.step()
+        torch.cuda.synchronize()
+        for want, got in zip(tensors, restored):
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (rank, "exchange", step)
     torch.cuda.synchronize()
     dist.barrier()
     print(f"PEER-OK rank {rank} multicast_bound={peer.multicast}", flush=True)

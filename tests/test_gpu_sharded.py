@@ -157,3 +157,21 @@ def test_repeated_default_calls_keep_nothing_alive():
         outs = [torch.empty(shape, dtype=torch.bfloat16, device="cuda") for shape in shapes]
         sharded.decode_all(plan, sharded.all_gather_wire(wire, plan), shapes, outputs=outs)
     assert len(plan.prepared) <= plan.max_prepared
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graph", "eager"])
+def test_overlapped_exchange_on_one_rank(graphs):
+    """WeightSetExchange with a world of one: no transfer, but the prepared encode (captured in
+    a CUDA graph or not), the alternating wire buffers and the prepared per-source decode."""
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 1, dist, row_shard_elements=30000, arena_fraction=0.5)
+    exchange = sharded.WeightSetExchange(plan, 0, tensors, [s for _, s in SHAPES],
+                                         capture_graphs=graphs)
+    for step in range(4):
+        tensors[0].mul_(1.25)          # new values in the same tensors every step
+        restored = exchange.step()
+        assert all(torch.equal(a, b) for a, b in zip(restored, tensors)), step
+    # the wire bytes equal what the unprepared path writes
+    wire, _, _ = sharded.encode_rank(plan, 0, tensors)
+    assert torch.equal(wire, exchange.wires[(exchange.step_index - 1) & 1].local)
