@@ -467,10 +467,15 @@ class PeerWire:
         self.multicast = bool(getattr(self.handle, "multicast_ptr", 0))
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
 
-    def fence(self) -> None:
+    def fence(self, signal: bool = False) -> None:
         """All ranks' earlier work on their current streams is complete before any rank's later
-        work starts (stream-ordered; the host is not blocked)."""
+        work starts (stream-ordered; the host is not blocked).  ``signal``: use the symmetric
+        memory's own barrier (flags in the peers' signal pads, a few microseconds) instead of a
+        one-element all-reduce."""
         if self.plan.world > 1:
+            if signal:
+                self.handle.barrier(channel=0)
+                return
             import torch.distributed as dist
 
             dist.all_reduce(self._token, group=self.group)
@@ -500,7 +505,8 @@ class WeightSetExchange:
 
     def __init__(self, plan: Plan, rank: int, tensors: list[torch.Tensor],
                  shapes: list[tuple[int, ...]], group=None,
-                 outputs: list[torch.Tensor] | None = None, capture_graphs: bool = True):
+                 outputs: list[torch.Tensor] | None = None, capture_graphs: bool = True,
+                 copy_streams: int = 1, signal_fence: bool = False):
         from .codec.decode import operand_of
         from .compression.huffman_tables import get_distribution_tables
         from .kernels import dispatch
@@ -513,7 +519,12 @@ class WeightSetExchange:
         self.world = plan.world
         # Local copies of the other ranks' buffers (this rank's own shards are decoded in place).
         self.landing = torch.empty(plan.world * plan.wire_bytes, dtype=torch.uint8, device=device)
-        self.side = torch.cuda.Stream(device=device)
+        # One side stream by default: with every rank reading a different source at any time the
+        # sources never serve two readers at once.  Measured on eight B200s, whole step: one
+        # stream 0.39-0.41 ms, two 0.44, three 0.48 (copies that overlap compete at the sources);
+        # the signal-pad fence instead of the one-element all-reduce: 0.54.
+        self.sides = [torch.cuda.Stream(device=device) for _ in range(max(1, copy_streams))]
+        self.signal_fence = signal_fence
         self.order = [(rank + k) % plan.world for k in range(1, plan.world)]
         self.arrived = {source: torch.cuda.Event() for source in self.order}
         self.fenced = torch.cuda.Event()
@@ -583,15 +594,17 @@ class WeightSetExchange:
         which = self.step_index & 1
         wire, decoders = self.wires[which], self.decoders[which]
         main = torch.cuda.current_stream()
-        wire.fence()                               # every rank's buffer of this step is complete
+        wire.fence(self.signal_fence)              # every rank's buffer of this step is complete
         self.fenced.record(main)
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(self.fenced)
-            self.side.wait_event(self.consumed)    # the previous step's decoders are done with `landing`
-            for source in self.order:
+        for side in self.sides:
+            side.wait_event(self.fenced)
+            side.wait_event(self.consumed)         # the previous step's decoders are done with `landing`
+        for k, source in enumerate(self.order):
+            side = self.sides[k % len(self.sides)]
+            with torch.cuda.stream(side):
                 at = source * self.plan.wire_bytes
                 self.landing[at:at + self.plan.wire_bytes].copy_(wire.buffers[source], non_blocking=True)
-                self.arrived[source].record(self.side)
+                self.arrived[source].record(side)
         self._decode(decoders[self.rank])
         for source in self.order:
             main.wait_event(self.arrived[source])
