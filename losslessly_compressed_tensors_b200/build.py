@@ -39,10 +39,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Build the shared library if missing or older than its sources; return its path."""
     if not force and not _stale():
         return LIBRARY
+    # Link into a private name and move it into place: another process (a second rank of the same
+    # job, a test worker) never maps a half-written library, and a failed build leaves the old one.
+    partial = f"{LIBRARY}.{os.getpid()}.partial"
     command = [
         _nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
         "-Xcompiler", "-fPIC", "-shared", "-I", INCLUDE, "-I", CSRC,
-        "-o", LIBRARY, *[os.path.join(CSRC, name) for name in SOURCES],
+        "-o", partial, *[os.path.join(CSRC, name) for name in SOURCES],
     ]
     if verbose:
         command[1:1] = ["-Xptxas", "-v"]
@@ -50,7 +53,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose or result.returncode:
         sys.stderr.write(result.stdout + result.stderr)
     if result.returncode:
+        if os.path.exists(partial):
+            os.remove(partial)
         raise RuntimeError("nvcc failed building liblct_b200.so")
+    os.replace(partial, LIBRARY)
     return LIBRARY
 
 

@@ -56,6 +56,14 @@ class _Handle:
             self._compressed = None
         self._dense = None
 
+    def __del__(self):
+        # A graph dropped without a backward pass (an evaluation forward inside the context, an
+        # exception between forward and backward) must give its arena regions back.
+        try:
+            self.discard()
+        except Exception:       # interpreter shutdown: the CUDA context may be gone already
+            pass
+
 
 class ActivationCache:
     """Stores eligible tensors compressed in ``buffer`` (or in private tensors without one)."""

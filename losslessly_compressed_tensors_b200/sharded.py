@@ -345,6 +345,31 @@ def _views_with_rank(plan: Plan, gathered) -> list[tuple[int, Shard, CompressedT
     return result
 
 
+def check(plan: Plan, gathered) -> None:
+    """Raise if any shard of any rank lost its overflow tails.
+
+    Encoding never synchronises the host, so a rank whose arena was too small (or whose
+    allocator gave up) only records that in the shard's descriptor: status 0 = stored.  A decode
+    of such a shard would silently leave its overflow lanes' tails undecoded.  This reads every
+    descriptor and overflow count of the gathered wire in one device-to-host copy; call it once
+    after the first exchange of a new weight set (or every step, at the price of a
+    synchronisation) and raise ``arena_fraction`` in ``make_plan`` when it fires."""
+    views = _views_with_rank(plan, gathered)
+    if not views:
+        return
+    words = torch.stack([torch.cat((c.fallback_descriptor[:3].to(views[0][2].data.device),
+                                    c.fallback_count.to(views[0][2].data.device)))
+                         for _, _, c in views]).cpu().tolist()
+    lost = [f"rank {rank} {shard.name}[{shard.row_start}:{shard.row_stop}] status {status} "
+            f"({count} overflow streams)"
+            for (rank, shard, _), (_, _, status, count) in zip(views, words)
+            if status != 0 and count > 0]
+    if lost:
+        raise RuntimeError("overflow tails were not stored (arena too small for this weight set: "
+                           "raise arena_fraction): " + "; ".join(lost[:8])
+                           + (f" and {len(lost) - 8} more" if len(lost) > 8 else ""))
+
+
 def _interleaved(plan: Plan, views: list, first_rank: int) -> list:
     """Reorder rank-major (shard, tensor) pairs round-robin over the source ranks, starting at
     ``first_rank``: consecutive CTAs of a decode launch then read from different sources, and

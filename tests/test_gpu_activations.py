@@ -84,3 +84,25 @@ def test_compress_weight_replaces_the_parameter():
     assert torch.equal(dense_weight(layer.weight).view(torch.int16), before.view(torch.int16))
     compress_weight(layer)   # idempotent
     assert dense_weight(before) is before
+
+
+def test_a_forward_without_backward_gives_its_regions_back():
+    """Handles that are dropped unloaded (an evaluation forward inside the context, an exception
+    before backward) release their arena regions when they are collected."""
+    import gc
+    model = _model(2)
+    x = torch.randn(512, 256, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    buffer = TensorBuffer(4 << 20)
+    cache = ActivationCache(buffer, act_relu_dist, min_elements=65536)   # a codebook that overflows
+    with compressed_saved_tensors(cache=cache):
+        loss = model(x).float().square().mean()
+    assert cache.stored >= 3
+    del loss
+    gc.collect()
+    verify_buffer(buffer)
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
+    handle = cache.store(torch.randn(300, 700, device="cuda").to(torch.bfloat16))
+    assert handle.is_compressed
+    del handle
+    gc.collect()
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]

@@ -175,3 +175,20 @@ def test_overlapped_exchange_on_one_rank(graphs):
     # the wire bytes equal what the unprepared path writes
     wire, _, _ = sharded.encode_rank(plan, 0, tensors)
     assert torch.equal(wire, exchange.wires[(exchange.step_index - 1) & 1].local)
+
+
+def test_check_reports_shards_whose_tails_did_not_fit():
+    """An arena too small for a rank's overflow tails is recorded per shard on the device;
+    ``check`` turns that into an exception, and passes a weight set that fitted."""
+    dist = Distribution(DistType.EMPIRICAL)
+    tensors = [w.cuda() for w in _weights()]
+    plan = sharded.make_plan(SHAPES, 2, dist, arena_fraction=0.5)
+    wires = [sharded.encode_rank(plan, rank, tensors)[0] for rank in range(2)]
+    sharded.check(plan, wires)
+    sharded.check(plan, torch.cat(wires))
+    small = sharded.make_plan(SHAPES, 2, dist, arena_fraction=0.5)
+    small.arena_capacity = 256                       # far below the "odd" tensor's tails
+    sharded._lay_out(small)
+    wires = [sharded.encode_rank(small, rank, tensors)[0] for rank in range(2)]
+    with pytest.raises(RuntimeError, match=r"odd\[0:77\] status [1-9]"):
+        sharded.check(small, wires)

@@ -4,8 +4,9 @@ A serving loop that forbids allocation after start-up, a process whose device me
 to another pool, or a plain C host has nowhere to get the two work buffers ``lct_encode`` wants
 (one byte per stream, four ints per block).  ``lct_encode_noalloc`` keeps them in an array inside
 the library instead and hands back only the overflow totals.  This test drives both entry points
-through the C ABI on the same inputs and requires identical bytes, twice in a row, the second
-time on a smaller tensor so that anything left in the built-in array by the first call would show.
+through the C ABI on the same inputs and requires identical bytes - equal to each other and to
+the CPU oracle's - twice in a row, the second time on a smaller tensor so that anything left in
+the built-in array by the first call would show.
 
 Collected last on purpose (file name): a run that stops at the first failure has then already run
 every other test.
@@ -67,7 +68,7 @@ def _encode_both(lib, bits, dist, center):
 
 
 @pytest.mark.gpu
-def test_noalloc_entry_point_matches_regular_encode_twice_in_a_row():
+def test_noalloc_entry_point_matches_regular_encode_twice_in_a_row(oracle):
     lib = _lib.load()
     dist = Distribution(DistType.GAUSSIAN)
     # First call: several blocks, wide data (many overflow streams).  Second call: a smaller,
@@ -79,6 +80,12 @@ def test_noalloc_entry_point_matches_regular_encode_twice_in_a_row():
         for want, got, what in zip(regular, built_in, ("side bytes", "payload", "counts")):
             assert torch.equal(want, got), what          # bit-exact, as everywhere in this suite
         totals.append(built_in[2].tolist())
+        # ... and both equal the CPU restatement of the reference's encoder and summary scan.
+        encode_table, decode_table, rare = tables_of(dist)
+        want = oracle.compress(bits, encode_table, decode_table, rare, geometry(dist), center=center)
+        assert np.array_equal(built_in[0].cpu().numpy(), want["side"])
+        assert np.array_equal(built_in[1].cpu().numpy(), want["encoded"])
+        assert built_in[2].tolist()[:2] == [want["count"], want["tail_bytes"]]
     assert totals[0][0] > 0 and totals[0][1] > 0 and totals[0][2:] == [0, 0]
     assert totals[1][0] < totals[0][0]
 
