@@ -487,17 +487,20 @@ def update_leg(steps: int = 10, warmup: int = 3) -> dict:
     out = {}
     for label, fused in (("fused", True), ("two_stage", False)):
         pointwise_module.FUSED_UPDATE = fused
-        times = []
+        times, walls = [], []
         for it in range(warmup + steps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
             a.record()
             for k, state in enumerate(states):
                 state.mul_add_(alpha, grads[(it + k) % len(grads)])
             b.record()
+            walls.append((time.perf_counter() - t0) / n_tensors)
             torch.cuda.synchronize()
             if it >= warmup:
                 times.append(a.elapsed_time(b) / n_tensors)
         out[label + "_ms_per_tensor_step"] = statistics.mean(times)
+        out[label + "_host_ms_per_tensor_step"] = statistics.mean(walls[warmup:]) * 1e3
         out[label + "_algorithmic_gbps"] = per_tensor / statistics.mean(times) / 1e6
     pointwise_module.FUSED_UPDATE = True
     # The twelve states through the many-tensor call: five launches per group of tensors

@@ -4,7 +4,8 @@ Interface of the reference's ``LCT/LCTensor.py:12-111`` (constructor, ``x``, ``n
 ``dense_nbytes``, ``layout``, ``add_``, ``mul_add_``, ``add_comp_``, ``decompress``,
 ``decompress_free``, ``free``; ``.T``/``permute``/``mm`` decode first).  Every in-place update
 builds the new compressed value with one fused call on the old one, in the old value's codebook
-and arena, and then returns the old value's arena region.
+and arena, and then returns the old value's arena region.  A value that an update replaced must
+not be used again: besides its arena region, its storage is reused by a later update.
 """
 from __future__ import annotations
 
@@ -14,6 +15,7 @@ import torch
 from torch import Tensor
 
 from . import operations as ops
+from .codec import pointwise as _pointwise
 from .comp_format import Distribution
 from .comp_tensor import CompressedTensor
 from .tensor_buffer import TensorBuffer
@@ -77,14 +79,34 @@ class LCTTensor(Tensor):
         self.x = make(old, home)
         old.free()
 
+    def _update(self, update: Tensor, operation, **scalars) -> bool:
+        """The update through recycled result storage (no allocation, two library calls);
+        False when that path does not apply to this value."""
+        old = self.x
+        new = _pointwise.recycled_update(old, update, operation, **scalars)
+        if new is None:
+            return False
+        self.x = new
+        _pointwise.release_recycled(old)
+        return True
+
     def add_(self, update: Tensor):
         """``x <- x + update``."""
-        self._become(lambda old, home: ops.compA_add_B(old, update, **home))
+        if not self._update(update, _pointwise.ADD):
+            self._become(lambda old, home: ops.compA_add_B(old, update, **home))
 
     def mul_add_(self, alpha: Tensor, update: Tensor, beta: Tensor | None = None, *,
                  alpha_is_one: bool = False):
         """``x <- alpha * x + beta * update`` (``beta`` defaults to 1; ``alpha_is_one`` treats
         alpha as 1 without reading it)."""
+        if beta is not None:
+            ops._need_device_scalar(alpha, "alpha", self.x.data.device)
+            ops._need_device_scalar(beta, "beta", self.x.data.device)
+        else:
+            ops._need_tensor(alpha, "alpha")
+        if self._update(update, _pointwise.SCALAR_MUL_ADD, alpha=alpha, beta=beta,
+                        alpha_is_one=alpha_is_one):
+            return
         if beta is None:
             self._become(lambda old, home: ops.a_compA_add_B(
                 old, alpha, update, alpha_is_one=alpha_is_one, **home))

@@ -164,6 +164,163 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
     return result
 
 
+# ---------------------------------------------------------------------------
+# In-place updates with recycled result storage
+# ---------------------------------------------------------------------------
+#
+# ``LCTTensor.mul_add_`` / ``add_`` replace a value by a new one and release the old one at
+# once.  Going through ``_fused_update`` that costs about a dozen small allocations, a dataclass
+# and an operand record per call - more host time than the GPU needs for a 16 Mi-element
+# tensor.  Here the storage of a released value is kept (per stream, arena, codebook and shape)
+# and becomes the next result of the same kind, together with the C arguments that describe
+# it, so a call is two library calls (the five-launch update, the release of the old region)
+# and no allocation.  Twelve momentum tensors of one shape share ONE spare set: memory grows
+# by one compressed tensor per shape, not per tensor.
+
+_RESULT_SET = "_b200_result_set"    # attribute of a CompressedTensor whose storage may be reused
+MAX_SPARE_SETS = 2                  # spare result sets kept per kind
+MAX_KINDS = 32                      # kinds whose work buffers and spare sets are kept
+
+
+def forget_spare_storage() -> None:
+    """Drop every spare result set and work buffer held for ``LCTTensor`` updates."""
+    _kinds.clear()
+
+
+class _ResultSet:
+    """Storage of one fused-update result and the C arguments that point into it."""
+
+    __slots__ = ("value", "middle", "outputs", "tail", "status", "kind")
+
+
+class _Kind:
+    """Everything updates of one (stream, arena, codebook, shape) share: tables, work buffers
+    (reused by every call: calls on one stream run in order, and the first launch of an update
+    is an ordinary launch that waits for all earlier work) and the spare result sets."""
+
+    def __init__(self, data: CompressedTensor, result_distribution, buffer):
+        if buffer.capacity_bytes % 4:
+            raise ValueError("TensorBuffer capacity must be divisible by 4")
+        device = data.data.device
+        self.device, self.buffer, self.distribution = device, buffer, result_distribution
+        self.shape, self.size, self.logical_numel = data.shape, data.size, data.logical_numel
+        self.geometry = block_symbols, lanes, steps, fixed_words = data.codec_geometry
+        self.encode_table, self.decode_table, _ = get_distribution_tables(result_distribution, device)
+        _, _, self.rare_length = get_distribution_tables(data.distribution, device)
+        self.blocks = data.size // block_symbols
+        self.count = min(data.logical_numel, 4096)
+
+        self.samples = self._new(self.count, torch.uint8)
+        self.shifted_encode = self._new(256, torch.int32)
+        self.extra_starts = self._new(self.blocks * lanes, torch.uint8)
+        self.summaries = self._new(4 * self.blocks, torch.int32)
+        self.spill = self._new(data.size, torch.uint8)
+        self.head = (self.encode_table.data_ptr(), self.decode_table.data_ptr(),
+                     self.samples.data_ptr())
+        self.work = (self.extra_starts.data_ptr(), self.summaries.data_ptr(), self.spill.data_ptr())
+        self.rest = (buffer._storage.data_ptr(), buffer.max_free_regions, data.size,
+                     data.logical_numel, block_symbols, steps, fixed_words, self.rare_length)
+        self.spare: list[_ResultSet] = []
+
+    def _new(self, count, dtype):
+        return torch.empty(count, dtype=dtype, device=self.device)
+
+    def take(self) -> _ResultSet:
+        if self.spare:
+            return self.spare.pop()
+        new = self._new
+        _, lanes, _, fixed_words = self.geometry
+        counts, descriptor = new(4, torch.int32), new(4, torch.int32)
+        center, values = new(1, torch.int32), new(self.count, torch.int16)
+        shifted_decode = new(self.decode_table.numel(), torch.int32)
+        encoded = new(self.blocks * lanes * fixed_words + 4, torch.int32)
+        side, blocks_out = new(self.size, torch.uint8), new(3 * self.blocks, torch.int32)
+        value = CompressedTensor(
+            encoded, self.size, side, fallback_starts=None, fallback_lanes=None,
+            fallback_blocks=blocks_out, fallback_buffer=self.buffer.data,
+            fallback_descriptor=descriptor, buffer=self.buffer, fallback_count=counts[:1],
+            fallback_used=counts[1:2], distribution=self.distribution, center=center,
+            decode_table=shifted_decode, shape=self.shape, layout=StorageLayout.COMPRESSED,
+            stream_geometry=geometry(self.distribution),
+        )
+        object.__setattr__(value, _SAMPLE_VALUES, values)
+        result = _ResultSet()
+        result.value, result.kind = value, self
+        result.middle = (values.data_ptr(), center.data_ptr())
+        result.outputs = (shifted_decode.data_ptr(), side.data_ptr(), encoded.data_ptr())
+        result.tail = (counts.data_ptr(), descriptor.data_ptr(), blocks_out.data_ptr())
+        result.status = new(1, torch.int32)
+        object.__setattr__(value, _RESULT_SET, result)
+        return result
+
+
+_kinds: dict = {}
+
+
+def recycled_update(data: CompressedTensor, other: Tensor, operation: PointwiseOp, *,
+                    alpha: Tensor | None = None, beta: Tensor | None = None,
+                    alpha_is_one: bool = False) -> CompressedTensor | None:
+    """``data (op) other`` compressed into ``data``'s codebook and arena, in storage recycled
+    from an earlier result; the caller releases ``data`` with ``release_recycled``.  Returns
+    ``None`` when this path does not apply (no arena, RAW or empty tensor, staged pipeline)."""
+    buffer = data.buffer
+    if (buffer is None or data.layout != StorageLayout.COMPRESSED or not data.logical_numel
+            or not FUSED_UPDATE or not encode_module.SINGLE_CALL_PIPELINE):
+        return None
+    if tuple(other.shape) != data.shape:
+        raise ValueError(f"{operation.name} expects tensors with the same shape")
+    if other.dtype != torch.bfloat16:
+        raise TypeError("the dense operand must be bfloat16")
+    if not other.is_contiguous():
+        other = other.contiguous()
+    device = data.data.device
+    scaled = operation is SCALAR_MUL_ADD
+    if scaled and alpha is None:
+        raise ValueError("scalar_mul_add requires an alpha argument")
+    alpha = _scalar(alpha, device) if scaled and not alpha_is_one else None
+    beta = _scalar(beta, device) if scaled else None
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    d = data.distribution
+    key = (index, dispatch._raw_stream(index), id(buffer), d.family, d.param, d.mean, d.zero_prob,
+           d.noise_level, data.shape, data.logical_numel)
+    kind = _kinds.pop(key, None)
+    if kind is None or kind.buffer is not buffer:
+        kind = _Kind(data, data.distribution, buffer)
+    _kinds[key] = kind                       # most recently used last
+    while len(_kinds) > MAX_KINDS:
+        _kinds.pop(next(iter(_kinds)))
+    target = kind.take()
+    known = data.__dict__.get(_SAMPLE_VALUES)
+    if known is not None and (known.numel() != kind.count or known.device != device):
+        known = None
+    dispatch._call(
+        "lct_update", device,
+        dispatch.ctypes.byref(operand_of(data)), other.data_ptr(),
+        alpha.data_ptr() if alpha is not None else None,
+        beta.data_ptr() if beta is not None else None,
+        operation.code, int(not scaled or alpha_is_one), int(not scaled or beta is None),
+        *kind.head, known.data_ptr() if known is not None else None, *target.middle,
+        kind.shifted_encode.data_ptr(), *target.outputs, *kind.work, *target.tail, *kind.rest,
+        launches=5)
+    return target.value
+
+
+def release_recycled(value: CompressedTensor) -> None:
+    """Release ``value`` (the operand of a finished ``recycled_update``): its arena region goes
+    back to the arena and, when its storage came from this module, the storage becomes a spare
+    result set.  ``value`` must not be used afterwards."""
+    held = value.__dict__.get(_RESULT_SET)
+    if held is None:
+        value.free()
+        return
+    kind = held.kind
+    dispatch._call("lct_buffer_free", kind.device, kind.buffer._storage.data_ptr(),
+                   value.fallback_descriptor.data_ptr(), held.status.data_ptr(),
+                   kind.buffer.max_free_regions)
+    if len(kind.spare) < MAX_SPARE_SETS:
+        kind.spare.append(held)
+
+
 def fused_update_many(datas, others, operation, result_distribution, buffer, *, alpha=None,
                       beta=None, alpha_is_one=False):
     """``_fused_update`` of many compressed tensors in five launches in all: every tensor of

@@ -229,3 +229,53 @@ def test_lcttensor_wrapper_surface():
     with pytest.raises(ValueError):
         A_compB(z, w)
     t.free()
+
+
+def test_in_place_updates_recycle_result_storage(oracle):
+    """``mul_add_`` / ``add_`` of tensors that share an arena, a codebook and a shape write into
+    storage recycled from released values: the number of distinct result storages stays at one
+    more than the number of tensors, and every value equals the oracle's at every step."""
+    from losslessly_compressed_tensors_b200.codec import pointwise
+
+    pointwise.forget_spare_storage()
+    dist = MEDIUM
+    shape, n = (96, 1024), 96 * 1024
+    gen = torch.Generator().manual_seed(21)
+    buffer = TensorBuffer(1 << 20)
+    arena = oracle.new_arena(1 << 20)
+    starts = [(torch.randn(n, generator=gen) * (1e-3 if i else 30.0)).to(torch.bfloat16)
+              for i in range(3)]
+    states = [LCTTensor(m.cuda().reshape(shape), buffer, dist) for m in starts]
+    wants = [oracle_compress(oracle, bits_of(m), dist, arena) for m in starts]
+    alpha, beta = _scalar(0.9), _scalar(-0.5)
+    storages = set()
+    for step in range(6):
+        for i, state in enumerate(states):
+            g = (torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16)
+            if step % 3 == 0:
+                state.mul_add_(alpha, g.cuda().reshape(shape))
+                args = (oracle.OP_SCALED, 0.9), dict(alpha_is_one=False, beta_is_one=True)
+            elif step % 3 == 1:
+                state.mul_add_(alpha, g.cuda().reshape(shape), beta)
+                args = (oracle.OP_SCALED, 0.9, -0.5), dict(alpha_is_one=False, beta_is_one=False)
+            else:
+                state.add_(g.cuda().reshape(shape))
+                args = (oracle.OP_ADD,), {}
+            side, exps = oracle.pointwise(wants[i], bits_of(g), *args[0], dense=False, **args[1])
+            new = _recompress(oracle, dist, wants[i], side, exps, arena)
+            assert oracle.buf_free(arena, wants[i]["descriptor"]) in (0, 4)
+            wants[i] = new
+            assert_same_components(state.x, new, f"step {step} tensor {i}")
+            storages.add(state.x.data.data_ptr())
+    assert len(storages) == len(states) + 1
+    for state, want in zip(states, wants):
+        assert np.array_equal(bits_of(state.decompress_free()), oracle.decompress(want))
+    verify_buffer(buffer)
+    fresh = LCTTensor(starts[1].cuda().reshape(shape), buffer, dist)
+    with pytest.raises(ValueError):
+        fresh.mul_add_(alpha, torch.zeros(3, 3, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(TypeError):
+        fresh.mul_add_(alpha, torch.zeros(shape, dtype=torch.float32, device="cuda"))
+    fresh.free()
+    verify_buffer(buffer)
+    pointwise.forget_spare_storage()
