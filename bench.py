@@ -558,6 +558,71 @@ def update_leg(steps: int = 10, warmup: int = 3) -> dict:
     return out
 
 
+def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
+    """Muon's momentum step (reference: LCT/components/sparse_utils.py:88-90,133-146) on twelve
+    4096 x 4096 BF16 momentum tensors in the optimizer's default codebook and one arena:
+    momentum <- lerp(momentum, grad, 1 - mu), grad <- lerp(grad, momentum, mu).  `fused`: one
+    launch chain on the compressed momentum that also writes the direction over the gradient;
+    `sequence`: the reference's decompress_free / lerp_ / lerp_ / compress.  CUDA events around
+    all twelve, per tensor-step."""
+    from losslessly_compressed_tensors_b200.LCTensor import LCTTensor
+    from losslessly_compressed_tensors_b200.components.dist_configs import momentum_dist
+    from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
+
+    mu, n_tensors, shape = 0.95, 12, (4096, 4096)
+    buffer = TensorBuffer(64 << 20)
+    gen = torch.Generator(device="cuda").manual_seed(20)
+    start = [(torch.randn(shape, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
+             for _ in range(n_tensors)]
+    grads = [(torch.randn(shape, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
+             for _ in range(4)]
+    work = [torch.empty(shape, dtype=torch.bfloat16, device="cuda") for _ in range(n_tensors)]
+    w_m = torch.tensor([1 - mu], dtype=torch.float32, device="cuda")
+    w_d = torch.tensor([mu], dtype=torch.float32, device="cuda")
+    out, final = {}, {}
+    for label in ("fused", "sequence"):
+        states = [LCTTensor(m, buffer, momentum_dist) for m in start]
+        times, walls = [], []
+        for it in range(warmup + steps):
+            for k in range(n_tensors):        # the step's gradients (overwritten by the direction)
+                work[k].copy_(grads[(it + k) % len(grads)])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            a.record()
+            for k, state in enumerate(states):
+                if label == "fused":
+                    assert state.lerp_(work[k], w_m, nesterov_out=work[k], nesterov_weight=w_d)
+                else:
+                    dense = state.decompress_free()
+                    dense.lerp_(work[k], 1 - mu)
+                    work[k].lerp_(dense, mu)
+                    states[k] = LCTTensor(dense, buffer, momentum_dist)
+            b.record()
+            walls.append((time.perf_counter() - t0) / n_tensors)
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(a.elapsed_time(b) / n_tensors)
+        out[label + "_ms_per_tensor_step"] = statistics.mean(times)
+        out[label + "_host_ms_per_tensor_step"] = statistics.mean(walls[warmup:]) * 1e3
+        final[label] = ([s.decompress() for s in states], [w.clone() for w in work])
+        if label == "fused":
+            c = states[0].x
+            out["algorithmic_bytes_per_tensor_step"] = (
+                2 * (c.sign_mantissa.numel() + (c.data.numel() - 4) * 4) + 4 * c.logical_numel)
+        for state in states:
+            state.free()
+    verify_buffer(buffer)
+    out["fused_algorithmic_gbps"] = (out["algorithmic_bytes_per_tensor_step"]
+                                     / out["fused_ms_per_tensor_step"] / 1e6)
+    out["speedup"] = out["sequence_ms_per_tensor_step"] / out["fused_ms_per_tensor_step"]
+    out["bit_exact_vs_torch_lerp"] = all(
+        torch.equal(x.view(torch.int16), y.view(torch.int16))
+        for part in (0, 1) for x, y in zip(final["fused"][part], final["sequence"][part]))
+    out["workload"] = ("12 x 4096x4096 BF16 Muon momentum, EMPIRICAL/CLEAN zero_prob 0.02, mu 0.95, "
+                       f"{warmup + steps} steps; bytes = compressed in + out, gradient in, direction out")
+    return out
+
+
 def run_ours(args, rank: int, world: int, local: int):
     from losslessly_compressed_tensors_b200.codec import encode as encode_module
     from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
@@ -757,6 +822,7 @@ def run_ours(args, rank: int, world: int, local: int):
     sharded = sharded_leg(rank, world, with_peer="peer" in legs) if "sharded" in legs else None
     update = update_leg() if (rank == 0 and "update" in legs) else None
     arena = arena_leg() if (rank == 0 and "arena" in legs) else None
+    momentum = momentum_leg() if (rank == 0 and "momentum" in legs) else None
     if rank != 0:
         return
     triton_reference = (triton_reference_leg() if world == 1 and "triton" in legs else None)
@@ -794,6 +860,7 @@ def run_ours(args, rank: int, world: int, local: int):
         "gpu_launches": launches, "clocks": clocks,
         "encode_ms_without_arena": statistics.mean(private_ms),
         "graph_replay_ms_per_step": graph_ms, "arena": arena, "update": update,
+        "momentum": momentum,
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)
@@ -835,9 +902,9 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--no-sharded", action="store_true",
                         help="skip the extra legs (configurations 3, 4 and 5)")
-    parser.add_argument("--legs", default="sharded,update,arena,triton",
+    parser.add_argument("--legs", default="sharded,update,momentum,arena,triton",
                         help="extra legs to run after configuration 2: sharded (configuration 5), "
-                             "update (configuration 4), arena (configuration 3), triton (the "
+                             "update (configuration 4), momentum (Muon's momentum step), arena (configuration 3), triton (the "
                              "reference's own kernels on this GPU, N = 1); with N > 1 the sharded "
                              "leg always includes the peer-memory decode")
     args = parser.parse_args()

@@ -256,6 +256,17 @@ int lct_decode_batch(const lct_decode_job *jobs /* device */, int n_jobs, int64_
 #define LCT_OP_ADD 0            /* bf16(a + b)            generic/pointwise.py:340-343 */
 #define LCT_OP_MULTIPLY 1       /* bf16(a * b)            generic/pointwise.py:346-349 */
 #define LCT_OP_SCALAR_MUL_ADD 2 /* bf16(fma-ordered alpha*a + beta*b), pointwise.py:352-363 */
+/* Two operations of the reference's optimizers on their BF16 state, with the
+ * float32 arithmetic of the PyTorch CUDA kernels the reference calls there
+ * (LCT/components/sparse_utils.py:88,193 momentum.lerp_(grad, w) and :194
+ * square_avg.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)):
+ *   LERP        w = *alpha; d = b - a;
+ *               |w| < 0.5 ? bf16(fma(w, d, a)) : bf16(fma(-d, 1 - w, b))
+ *   EMA_SQUARE  t = bf16(a * *alpha); bf16(fma(*beta, b * b, t))
+ * alpha (and, for EMA_SQUARE, beta) must not be NULL; the *_is_one flags are
+ * ignored. */
+#define LCT_OP_LERP 3
+#define LCT_OP_EMA_SQUARE 4
 
 /* compA (op) B with B dense BF16 in logical order.  compressed_output == 0:
  * output = BF16[logical_numel].  Otherwise output = side bytes uint8[size]
@@ -335,6 +346,41 @@ int lct_update(const lct_operand *a /* host pointer */, const void *other, const
                int32_t *blocks_out, void *arena_storage, int max_free_regions, int64_t size,
                int64_t logical_numel, int block_symbols, int steps, int fixed_words,
                int rare_length, void *stream);
+
+/* lct_update that also writes a dense BF16 tensor from the values it has in
+ * registers anyway, so that an optimizer never materialises its decoded state:
+ *   emit == LCT_EMIT_RESULT     dense_out = the new value of A (what AdamW's
+ *                               weight update reads, sparse_utils.py:195-198);
+ *   emit == LCT_EMIT_NESTEROV   dense_out = lerp(B, new A, *beta) with the LERP
+ *                               arithmetic above: Muon's update direction
+ *                               grad.lerp_(momentum, mu), sparse_utils.py:89-90.
+ * dense_out is BF16[logical_numel], 16-byte aligned, and may be `other` itself
+ * (every element of B is read by the thread that overwrites it, before it does).
+ * emit == LCT_EMIT_NONE is lct_update.  Replaces the reference's sequence
+ * decompress_free -> lerp_ -> lerp_ -> LCTTensor(...) of SparseMuon.step,
+ * sparse_utils.py:133-146.
+ * release_descriptor (may be NULL): descriptor of a region of the same arena -
+ * the one A's overflow tails live in, for an in-place update - which is
+ * returned to the arena right after the result's region has been reserved, by
+ * the same kernel; release_status (int32[1]) receives what lct_buffer_free
+ * would report.  The arena ends up as after lct_update + lct_buffer_free
+ * (LCTensor.py:74-77: new value first, then old.free()).
+ * When known_values is given, the sample pre-pass and the center are one
+ * kernel and `samples` is not touched. */
+#define LCT_EMIT_NONE 0
+#define LCT_EMIT_RESULT 1
+#define LCT_EMIT_NESTEROV 2
+int lct_update_emit(const lct_operand *a /* host pointer */, const void *other, const float *alpha,
+                    const float *beta, int op, int alpha_is_one, int beta_is_one,
+                    const int32_t *encode_table, const int32_t *decode_table, uint8_t *samples,
+                    const uint16_t *known_values, uint16_t *result_values,
+                    int32_t *center, int32_t *shifted_encode, int32_t *shifted_decode,
+                    uint8_t *side_out, int32_t *encoded_out, uint8_t *extra_starts,
+                    int32_t *summaries, uint8_t *spill, int32_t *counts, int32_t *descriptor,
+                    int32_t *blocks_out, void *arena_storage, int max_free_regions, int64_t size,
+                    int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                    int rare_length, void *dense_out, int emit, int32_t *release_descriptor,
+                    int32_t *release_status, void *stream);
 
 /* Many compressed tensors of ONE geometry updated by one call (an optimizer
  * step over all its parameters): the five kernels of lct_update, each launched

@@ -18,6 +18,7 @@ from . import operations as ops
 from .codec import pointwise as _pointwise
 from .comp_format import Distribution
 from .comp_tensor import CompressedTensor
+from .kernels import dispatch
 from .tensor_buffer import TensorBuffer
 
 _aten = torch.ops.aten
@@ -80,14 +81,13 @@ class LCTTensor(Tensor):
         old.free()
 
     def _update(self, update: Tensor, operation, **scalars) -> bool:
-        """The update through recycled result storage (no allocation, two library calls);
+        """The update through recycled result storage (no allocation, one library call);
         False when that path does not apply to this value."""
         old = self.x
         new = _pointwise.recycled_update(old, update, operation, **scalars)
         if new is None:
             return False
-        self.x = new
-        _pointwise.release_recycled(old)
+        self.x = new        # `old` was released by the same call
         return True
 
     def add_(self, update: Tensor):
@@ -113,6 +113,52 @@ class LCTTensor(Tensor):
         else:
             self._become(lambda old, home: ops.a_compA_add_b_B(
                 old, alpha, update, beta, alpha_is_one=alpha_is_one, **home))
+
+    def lerp_(self, end: Tensor, weight: Tensor, *, distribution: Distribution | None = None,
+              nesterov_out: Tensor | None = None, nesterov_weight: Tensor | None = None,
+              dense_out: Tensor | None = None) -> bool:
+        """``x <- lerp(x, end, weight)`` with the arithmetic of ``torch.Tensor.lerp_`` on BF16
+        CUDA tensors, as one launch chain on the compressed value: the momentum update of the
+        reference's Muon and AdamW (``LCT/components/sparse_utils.py:88,193``) without the
+        dense decoded state in between.  ``weight``: float32 device scalar.
+
+        ``nesterov_out`` (with ``nesterov_weight``) also receives ``lerp(end, x_new,
+        nesterov_weight)``, Muon's update direction (``sparse_utils.py:90``); it may be ``end``
+        itself, which is how the reference computes it (``grad.lerp_``).  ``dense_out`` instead
+        receives the new value densely.  ``distribution`` re-encodes with another codebook of
+        the same geometry.
+
+        Returns False, having done nothing, when the value is not in an arena or the codebooks'
+        geometries differ: the caller then takes the decode / update / compress route."""
+        if nesterov_out is not None and dense_out is not None:
+            raise ValueError("one dense output at most")
+        old = self.x
+        emit = (dispatch.EMIT_NESTEROV if nesterov_out is not None
+                else dispatch.EMIT_RESULT if dense_out is not None else dispatch.EMIT_NONE)
+        new = _pointwise.recycled_update(
+            old, end, _pointwise.LERP, alpha=weight, beta=nesterov_weight,
+            distribution=distribution, emit=emit,
+            dense_out=nesterov_out if nesterov_out is not None else dense_out)
+        if new is None:
+            return False
+        self.x = new
+        return True
+
+    def ema_square_(self, grad: Tensor, decay: Tensor, weight: Tensor, *,
+                    dense_out: Tensor | None = None) -> bool:
+        """``x <- x.mul_(decay).addcmul_(grad, grad, value=weight)`` with PyTorch's BF16 CUDA
+        arithmetic (two roundings), on the compressed value: AdamW's second moment
+        (``sparse_utils.py:194``).  ``dense_out`` also receives the new value densely.  Returns
+        False, having done nothing, when the value is not in an arena."""
+        old = self.x
+        new = _pointwise.recycled_update(
+            old, grad, _pointwise.EMA_SQUARE, alpha=decay, beta=weight,
+            emit=dispatch.EMIT_RESULT if dense_out is not None else dispatch.EMIT_NONE,
+            dense_out=dense_out)
+        if new is None:
+            return False
+        self.x = new
+        return True
 
     @staticmethod
     def mul_add_many_(tensors: "list[LCTTensor]", alpha: Tensor, updates: "list[Tensor]",

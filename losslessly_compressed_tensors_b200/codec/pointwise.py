@@ -39,7 +39,16 @@ SCALAR_MUL_ADD = PointwiseOp(
     "scalar_mul_add", dispatch.OP_SCALAR_MUL_ADD,
     lambda left, right, alpha=1.0: (left.float() * alpha + right.float()).to(torch.bfloat16),
 )
-POINTWISE_OPS = {op.name: op for op in (ADD, MULTIPLY, SCALAR_MUL_ADD)}
+def _torch_ema_square(left, right, alpha, beta):
+    return left.clone().mul_(float(alpha)).addcmul_(right, right, value=float(beta))
+
+
+# The optimizers' state updates (``LCT/components/sparse_utils.py:88,193-194``); ``alpha`` is the
+# lerp weight, resp. ``alpha`` = beta2 and ``beta`` = 1 - beta2 of the second-moment average.
+LERP = PointwiseOp("lerp", dispatch.OP_LERP,
+                   lambda left, right, alpha: torch.lerp(left, right, float(alpha)))
+EMA_SQUARE = PointwiseOp("ema_square", dispatch.OP_EMA_SQUARE, _torch_ema_square)
+POINTWISE_OPS = {op.name: op for op in (ADD, MULTIPLY, SCALAR_MUL_ADD, LERP, EMA_SQUARE)}
 
 
 def _outputs(data: CompressedTensor, dense_output: bool):
@@ -173,8 +182,8 @@ def _fused_update(data, other, operation, result_distribution, buffer, *, alpha,
 # and an operand record per call - more host time than the GPU needs for a 16 Mi-element
 # tensor.  Here the storage of a released value is kept (per stream, arena, codebook and shape)
 # and becomes the next result of the same kind, together with the C arguments that describe
-# it, so a call is two library calls (the five-launch update, the release of the old region)
-# and no allocation.  Twelve momentum tensors of one shape share ONE spare set: memory grows
+# it, so a call is ONE library call of four launches (sample + center, decode -> op -> encode,
+# scan + reservation + release of the old region, tails) and no allocation.  Twelve momentum tensors of one shape share ONE spare set: memory grows
 # by one compressed tensor per shape, not per tensor.
 
 _RESULT_SET = "_b200_result_set"    # attribute of a CompressedTensor whose storage may be reused
@@ -190,7 +199,7 @@ def forget_spare_storage() -> None:
 class _ResultSet:
     """Storage of one fused-update result and the C arguments that point into it."""
 
-    __slots__ = ("value", "middle", "outputs", "tail", "status", "kind")
+    __slots__ = ("value", "middle", "outputs", "tail", "kind")
 
 
 class _Kind:
@@ -215,6 +224,7 @@ class _Kind:
         self.extra_starts = self._new(self.blocks * lanes, torch.uint8)
         self.summaries = self._new(4 * self.blocks, torch.int32)
         self.spill = self._new(data.size, torch.uint8)
+        self.release_status = self._new(1, torch.int32)
         self.head = (self.encode_table.data_ptr(), self.decode_table.data_ptr(),
                      self.samples.data_ptr())
         self.work = (self.extra_starts.data_ptr(), self.summaries.data_ptr(), self.spill.data_ptr())
@@ -249,7 +259,6 @@ class _Kind:
         result.middle = (values.data_ptr(), center.data_ptr())
         result.outputs = (shifted_decode.data_ptr(), side.data_ptr(), encoded.data_ptr())
         result.tail = (counts.data_ptr(), descriptor.data_ptr(), blocks_out.data_ptr())
-        result.status = new(1, torch.int32)
         object.__setattr__(value, _RESULT_SET, result)
         return result
 
@@ -259,13 +268,23 @@ _kinds: dict = {}
 
 def recycled_update(data: CompressedTensor, other: Tensor, operation: PointwiseOp, *,
                     alpha: Tensor | None = None, beta: Tensor | None = None,
-                    alpha_is_one: bool = False) -> CompressedTensor | None:
-    """``data (op) other`` compressed into ``data``'s codebook and arena, in storage recycled
-    from an earlier result; the caller releases ``data`` with ``release_recycled``.  Returns
-    ``None`` when this path does not apply (no arena, RAW or empty tensor, staged pipeline)."""
+                    alpha_is_one: bool = False, distribution: Distribution | None = None,
+                    emit: int = dispatch.EMIT_NONE,
+                    dense_out: Tensor | None = None) -> CompressedTensor | None:
+    """The in-place update ``data <- data (op) other``: returns the new value, compressed into
+    ``data``'s arena with ``distribution``'s codebook (default: ``data``'s own) in storage
+    recycled from an earlier result, and releases ``data`` in the same call - its arena region
+    goes back right after the new one has been reserved, and its storage becomes the spare set
+    of a later update.  ``data`` must not be used afterwards.  ``emit`` / ``dense_out``: also write the dense result
+    (``EMIT_RESULT``) or the Nesterov direction ``lerp(other, result, beta)`` (``EMIT_NESTEROV``,
+    ``LERP`` only) to ``dense_out``, a contiguous BF16 tensor of ``data``'s shape that may be
+    ``other`` itself.  Returns ``None`` when this path does not apply (no arena, RAW or empty
+    tensor, staged pipeline, a result codebook of another geometry)."""
     buffer = data.buffer
+    result_distribution = distribution or data.distribution
     if (buffer is None or data.layout != StorageLayout.COMPRESSED or not data.logical_numel
-            or not FUSED_UPDATE or not encode_module.SINGLE_CALL_PIPELINE):
+            or not FUSED_UPDATE or not encode_module.SINGLE_CALL_PIPELINE
+            or geometry(result_distribution) != data.codec_geometry):
         return None
     if tuple(other.shape) != data.shape:
         raise ValueError(f"{operation.name} expects tensors with the same shape")
@@ -275,17 +294,27 @@ def recycled_update(data: CompressedTensor, other: Tensor, operation: PointwiseO
         other = other.contiguous()
     device = data.data.device
     scaled = operation is SCALAR_MUL_ADD
-    if scaled and alpha is None:
-        raise ValueError("scalar_mul_add requires an alpha argument")
-    alpha = _scalar(alpha, device) if scaled and not alpha_is_one else None
-    beta = _scalar(beta, device) if scaled else None
+    takes_scalars = scaled or operation is LERP or operation is EMA_SQUARE
+    if takes_scalars and alpha is None and not (scaled and alpha_is_one):
+        raise ValueError(f"{operation.name} requires an alpha argument")
+    if operation is EMA_SQUARE and beta is None:
+        raise ValueError("ema_square requires a beta argument")
+    alpha = _scalar(alpha, device) if takes_scalars and not (scaled and alpha_is_one) else None
+    beta = _scalar(beta, device) if takes_scalars else None
+    if emit != dispatch.EMIT_NONE:
+        if (dense_out is None or dense_out.dtype != torch.bfloat16 or dense_out.device != device
+                or tuple(dense_out.shape) != data.shape or not dense_out.is_contiguous()):
+            raise ValueError("dense_out must be a contiguous bfloat16 tensor of the operand's "
+                             "shape on its device")
+        if emit == dispatch.EMIT_NESTEROV and (operation is not LERP or beta is None):
+            raise ValueError("the Nesterov direction needs the lerp operation and its weight (beta)")
     index = device.index if device.index is not None else torch.cuda.current_device()
-    d = data.distribution
+    d, r = data.distribution, result_distribution
     key = (index, dispatch._raw_stream(index), id(buffer), d.family, d.param, d.mean, d.zero_prob,
-           d.noise_level, data.shape, data.logical_numel)
+           r.family, r.param, r.mean, r.zero_prob, r.noise_level, data.shape, data.logical_numel)
     kind = _kinds.pop(key, None)
     if kind is None or kind.buffer is not buffer:
-        kind = _Kind(data, data.distribution, buffer)
+        kind = _Kind(data, result_distribution, buffer)
     _kinds[key] = kind                       # most recently used last
     while len(_kinds) > MAX_KINDS:
         _kinds.pop(next(iter(_kinds)))
@@ -294,31 +323,20 @@ def recycled_update(data: CompressedTensor, other: Tensor, operation: PointwiseO
     if known is not None and (known.numel() != kind.count or known.device != device):
         known = None
     dispatch._call(
-        "lct_update", device,
+        "lct_update_emit", device,
         dispatch.ctypes.byref(operand_of(data)), other.data_ptr(),
         alpha.data_ptr() if alpha is not None else None,
         beta.data_ptr() if beta is not None else None,
         operation.code, int(not scaled or alpha_is_one), int(not scaled or beta is None),
         *kind.head, known.data_ptr() if known is not None else None, *target.middle,
         kind.shifted_encode.data_ptr(), *target.outputs, *kind.work, *target.tail, *kind.rest,
-        launches=5)
+        dense_out.data_ptr() if emit != dispatch.EMIT_NONE else None, emit,
+        data.fallback_descriptor.data_ptr(), kind.release_status.data_ptr(),
+        launches=4 if known is not None else 5)
+    held = data.__dict__.get(_RESULT_SET)
+    if held is not None and len(held.kind.spare) < MAX_SPARE_SETS:
+        held.kind.spare.append(held)
     return target.value
-
-
-def release_recycled(value: CompressedTensor) -> None:
-    """Release ``value`` (the operand of a finished ``recycled_update``): its arena region goes
-    back to the arena and, when its storage came from this module, the storage becomes a spare
-    result set.  ``value`` must not be used afterwards."""
-    held = value.__dict__.get(_RESULT_SET)
-    if held is None:
-        value.free()
-        return
-    kind = held.kind
-    dispatch._call("lct_buffer_free", kind.device, kind.buffer._storage.data_ptr(),
-                   value.fallback_descriptor.data_ptr(), held.status.data_ptr(),
-                   kind.buffer.max_free_regions)
-    if len(kind.spare) < MAX_SPARE_SETS:
-        kind.spare.append(held)
 
 
 def fused_update_many(datas, others, operation, result_distribution, buffer, *, alpha=None,

@@ -4,8 +4,10 @@ Drop-in for the three optimizers of the reference (``LCT/components/sparse_utils
 ``SparseSGDM`` :13-66, ``SparseMuon`` :98-160, ``SparseAdamW`` :163-214): same constructor
 arguments, same update arithmetic in the same order, so a training script switches by
 changing the import.  What differs is underneath: every update of compressed state runs
-through this library's launch chains (``LCTTensor.mul_add_``: sample, center, decode -> fma
--> re-encode, scan, tails behind ONE library call; ``add_comp_``: both operands compressed).
+through this library's launch chains (``LCTTensor.mul_add_`` / ``lerp_`` / ``ema_square_``:
+sample, center, decode -> arithmetic -> re-encode, scan, tails behind ONE library call;
+``add_comp_``: both operands compressed), so the momentum of Muon and the moments of AdamW are
+never decoded into a dense tensor of their own.
 
 The codec is lossless, so wherever the compressed and the dense variant of an optimizer run
 the same arithmetic on the dense values (Muon, AdamW) their trajectories are bit-identical;
@@ -142,18 +144,33 @@ def zeropower_via_newtonschulz5(G: Tensor, ns_iters: int) -> Tensor:
     return X.mT if tall else X
 
 
+def _orthogonalised(direction: Tensor, ns_iters: int) -> Tensor:
+    update = zeropower_via_newtonschulz5(direction, ns_iters)
+    update *= max(1, direction.size(-2) / direction.size(-1)) ** 0.5
+    return update
+
+
 def muon_update(grad: Tensor, momentum: Tensor, mu=0.95, nesterov=True, ns_iters=5) -> Tensor:
     """In-place momentum step and the orthogonalised update (``sparse_utils.py:87-95``)."""
     momentum.lerp_(grad.to(momentum.dtype), 1 - mu)
     direction = grad.lerp_(momentum.to(grad.dtype), mu) if nesterov else momentum
-    update = zeropower_via_newtonschulz5(direction, ns_iters)
-    update *= max(1, grad.size(-2) / grad.size(-1)) ** 0.5
-    return update
+    return _orthogonalised(direction, ns_iters)
+
+
+def _fusable(state, grad: Tensor) -> bool:
+    """Compressed state that the fused launch chains can update against ``grad`` directly."""
+    return (isinstance(state, LCTTensor) and grad.dtype == torch.bfloat16
+            and grad.is_contiguous() and state.x.buffer is not None)
 
 
 class SparseMuon(_Base):
-    """Muon with BF16 momentum that is decoded, updated densely and re-compressed every step
-    (the first step with the many-zeros codebook when ``zero_first_step``)."""
+    """Muon with BF16 momentum kept compressed (the first step with the many-zeros codebook
+    when ``zero_first_step``).  Momentum that lives in an arena is advanced by ONE launch chain
+    on its compressed form - decode, ``lerp`` with the gradient, re-encode - which also writes
+    the Nesterov direction over the gradient, so the dense momentum never exists; the values
+    are those of the reference's decode / ``lerp_`` / ``lerp_`` / compress sequence
+    (``sparse_utils.py:133-146``), which remains the route for everything else (first step,
+    no arena, FP32 gradients)."""
 
     def __init__(self, params: Iterable[LCTTensor | Tensor], lr=0.02, weight_decay=0, mu=0.95,
                  buffer: TensorBuffer | None = None, compressed=True, distribution=None,
@@ -166,6 +183,8 @@ class SparseMuon(_Base):
         anchor = self.params[0] if self.params else torch.empty(0, device="cuda")
         self.decay = _scalar(1 - lr * weight_decay, anchor)
         self.neg_lr = _scalar(-lr, anchor)
+        self._momentum_weight = _scalar(1 - mu, anchor)     # lerp weights as float32, which is
+        self._direction_weight = _scalar(mu, anchor)        # what torch's kernel makes of them
         self._slots = [_Slot() for _ in self.params]
 
     @property
@@ -178,11 +197,18 @@ class SparseMuon(_Base):
             grad = p.grad
             if grad is None:
                 continue
-            momentum = slot.take_dense(grad, torch.bfloat16)
-            update = muon_update(grad, momentum, mu=self.mu, ns_iters=self.ns_iters)
-            slot.put(momentum, compress=self.compressed, buffer=self.buffer,
-                     dist=momentum_first_dist if self.first_step else self.distribution)
-            del momentum
+            dist = momentum_first_dist if self.first_step else self.distribution
+            if (self.compressed and _fusable(slot.value, grad)
+                    and slot.value.x.buffer is self.buffer
+                    and slot.value.lerp_(grad, self._momentum_weight, distribution=dist,
+                                         nesterov_out=grad,
+                                         nesterov_weight=self._direction_weight)):
+                update = _orthogonalised(grad, self.ns_iters)
+            else:
+                momentum = slot.take_dense(grad, torch.bfloat16)
+                update = muon_update(grad, momentum, mu=self.mu, ns_iters=self.ns_iters)
+                slot.put(momentum, compress=self.compressed, buffer=self.buffer, dist=dist)
+                del momentum
             if isinstance(p, LCTTensor):   # decay and update in one fused pass over the weights
                 p.mul_add_(self.decay, update, beta=self.neg_lr, alpha_is_one=self.weight_decay == 0)
             else:
@@ -202,6 +228,7 @@ class SparseAdamW(_Base):
         self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
         self.compressed, self.buffer = compressed, buffer
         self.state: dict = {}
+        self._device_scalars: dict = {}
 
     def _all_params(self):
         return [p for group in self.param_groups for p in group["params"]]
@@ -211,10 +238,23 @@ class SparseAdamW(_Base):
         state = self.state.setdefault(p, {"step": 0, "exp_avg": _Slot(), "exp_avg_sq": _Slot()})
         state["step"] += 1
         t = state["step"]
-        avg = state["exp_avg"].take_dense(grad)
-        square_avg = state["exp_avg_sq"].take_dense(grad)
-        avg.lerp_(grad, 1 - beta1)
-        square_avg.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
+        first, second = state["exp_avg"], state["exp_avg_sq"]
+        fused = (self.compressed and _fusable(first.value, grad) and _fusable(second.value, grad)
+                 and first.value.x.buffer is self.buffer and second.value.x.buffer is self.buffer
+                 and first.value.x.distribution == momentum_dist
+                 and second.value.x.distribution == momentum_dist)
+        if fused:
+            # Both moments advance on their compressed forms; the dense new values that the
+            # weight update reads are written by the same launches.
+            scalars = self._scalars(grad)
+            avg, square_avg = torch.empty_like(grad), torch.empty_like(grad)
+            first.value.lerp_(grad, scalars[0], dense_out=avg)
+            second.value.ema_square_(grad, scalars[1], scalars[2], dense_out=square_avg)
+        else:
+            avg = first.take_dense(grad)
+            square_avg = second.take_dense(grad)
+            avg.lerp_(grad, 1 - beta1)
+            square_avg.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
         denom = square_avg.sqrt().div_(math.sqrt(1 - beta2 ** t)).add_(self.eps)
         weight = p.decompress() if isinstance(p, LCTTensor) else p
         weight.mul_(1 - lr * self.weight_decay)
@@ -223,8 +263,21 @@ class SparseAdamW(_Base):
             previous = p.x
             p.x = LCTTensor(weight, buffer=previous.buffer, dist=previous.distribution).x
             previous.free()
-        for key, dense in (("exp_avg", avg), ("exp_avg_sq", square_avg)):
-            state[key].put(dense, compress=self.compressed, buffer=self.buffer, dist=momentum_dist)
+        if not fused:
+            for key, dense in (("exp_avg", avg), ("exp_avg_sq", square_avg)):
+                state[key].put(dense, compress=self.compressed, buffer=self.buffer,
+                               dist=momentum_dist)
+
+    def _scalars(self, like: Tensor):
+        """(1 - beta1, beta2, 1 - beta2) as float32 device scalars: the values PyTorch's kernels
+        make of the Python numbers the reference passes."""
+        key = like.device
+        cached = self._device_scalars.get(key)
+        if cached is None:
+            beta1, beta2 = self.betas
+            cached = self._device_scalars[key] = tuple(
+                _scalar(v, like) for v in (1 - beta1, beta2, 1 - beta2))
+        return cached
 
     @torch.no_grad()
     def step(self):

@@ -139,7 +139,8 @@ arena_free_many_kernel(void* storage, int32_t* const* descriptors, int n, int32_
 // (for a shared arena) the reservation of this tensor's overflow region.
 __global__ void __launch_bounds__(kScanThreads)
 scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, void* arena_storage,
-                     int64_t blocks, int regions) {
+                     int64_t blocks, int regions, int32_t* release_descriptor,
+                     int32_t* release_status) {
   __shared__ int scratch[33];
   __shared__ int alloc_scratch[2];
   // The summaries come from the encoder in front of this kernel; the tail compaction behind
@@ -169,8 +170,19 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
   }
   if (arena_storage != nullptr) {
     // Two metadata bytes per overflowing stream (lane, start) ahead of the tails.
-    arena_allocate(arena_of(arena_storage, regions), regions, running_bytes + 2 * running_count,
-                   descriptor, alloc_scratch);
+    const Arena arena = arena_of(arena_storage, regions);
+    arena_allocate(arena, regions, running_bytes + 2 * running_count, descriptor, alloc_scratch);
+    if (release_descriptor != nullptr) {
+      // An in-place update: the region of the value that was just replaced goes back, after
+      // the new one has been reserved (the order of a separate allocate and free).
+      __syncthreads();
+      if (!arena_lock(arena, alloc_scratch)) {
+        if (threadIdx.x == 0) *release_status = kStatusLockTimeout;
+        return;
+      }
+      arena_free_locked(arena, regions, release_descriptor, release_status, alloc_scratch);
+      arena_unlock(arena);
+    }
   }
 }
 
@@ -310,12 +322,17 @@ scan_batch_kernel(const Job* __restrict__ jobs, int n_jobs, int32_t* summaries,
 
 int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
                          void* arena_storage, int64_t blocks, int max_free_regions,
-                         bool overlapped, cudaStream_t stream) {
+                         bool overlapped, cudaStream_t stream, int32_t* release_descriptor,
+                         int32_t* release_status) {
+  if (release_descriptor != nullptr && (arena_storage == nullptr || release_status == nullptr))
+    return LCT_E_NULL_POINTER;
   if (overlapped)
     return launch_overlapped(scan_allocate_kernel, 1, kScanThreads, 0, stream, summaries, counts,
-                             descriptor, arena_storage, blocks, max_free_regions);
+                             descriptor, arena_storage, blocks, max_free_regions,
+                             release_descriptor, release_status);
   scan_allocate_kernel<<<1, kScanThreads, 0, stream>>>(summaries, counts, descriptor, arena_storage,
-                                                       blocks, max_free_regions);
+                                                       blocks, max_free_regions,
+                                                       release_descriptor, release_status);
   return (int)cudaGetLastError();
 }
 

@@ -45,10 +45,12 @@ int launch_compact(const void* src, uint8_t* lanes, uint8_t* starts, uint8_t* ta
                    int64_t logical_numel, int block_symbols, int steps, int precomputed,
                    bool overlapped, cudaStream_t stream);
 
-// arena.cu: summary scan (+ arena reservation).  `overlapped`: see launch_overlapped.
+// arena.cu: summary scan (+ arena reservation, + release of another region of the same arena
+// right after it).  `overlapped`: see launch_overlapped.
 int launch_scan_allocate(int32_t* summaries, int32_t* counts, int32_t* descriptor,
                          void* arena_storage, int64_t blocks, int max_free_regions,
-                         bool overlapped, cudaStream_t stream);
+                         bool overlapped, cudaStream_t stream,
+                         int32_t* release_descriptor = nullptr, int32_t* release_status = nullptr);
 
 // Launch with programmatic stream serialisation: the grid may be scheduled as soon as every
 // CTA of the previous kernel in the stream has exited or called

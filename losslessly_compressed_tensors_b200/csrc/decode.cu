@@ -372,13 +372,7 @@ int lct_pointwise(const lct_operand* a, const void* other, void* output, uint8_t
   if ((rc = lct::view_of(a, &va)) != 0) return rc;
   if (other == nullptr || output == nullptr) return LCT_E_NULL_POINTER;
   if (compressed_output && auxiliary == nullptr) return LCT_E_NULL_POINTER;
-  if (op < LCT_OP_ADD || op > LCT_OP_SCALAR_MUL_ADD) return LCT_E_BAD_ARGUMENT;
-  if (op == LCT_OP_SCALAR_MUL_ADD) {
-    if (!alpha_is_one && alpha == nullptr) return LCT_E_NULL_POINTER;
-    if (!beta_is_one && beta == nullptr) return LCT_E_NULL_POINTER;
-  } else {
-    alpha_is_one = beta_is_one = 1;
-  }
+  if ((rc = lct::check_op(op, alpha, beta, &alpha_is_one, &beta_is_one)) != 0) return rc;
   if (!lct::aligned16(output) || (compressed_output && !lct::aligned16(auxiliary)))
     return LCT_E_ALIGNMENT;
   if ((reinterpret_cast<uintptr_t>(other) & 1u) != 0) return LCT_E_ALIGNMENT;

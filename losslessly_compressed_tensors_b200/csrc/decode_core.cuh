@@ -540,6 +540,18 @@ __device__ __forceinline__ uint32_t pack_rn(float low, float high) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// torch.lerp(start, end, weight) in float32, as PyTorch's CUDA kernel evaluates it.
+__device__ __forceinline__ float lerp_f32(float start, float end, float weight) {
+  const float d = __fsub_rn(end, start);
+  return fabsf(weight) < 0.5f ? __fmaf_rn(weight, d, start)
+                              : __fmaf_rn(-d, __fsub_rn(1.0f, weight), end);
+}
+// Two lanes of lerp(start, end, weight), rounded to BF16.
+__device__ __forceinline__ uint32_t lerp_pair(uint32_t start, uint32_t end, float weight) {
+  return pack_rn(lerp_f32(bf16_low(start), bf16_low(end), weight),
+                 lerp_f32(bf16_high(start), bf16_high(end), weight));
+}
+
 // Two lanes of `left (op) right`, rounded once to BF16.
 __device__ __forceinline__ uint32_t apply_op(uint32_t left, uint32_t right, int op, bool alpha_one,
                                              bool beta_one, float alpha, float beta) {
@@ -553,8 +565,14 @@ __device__ __forceinline__ uint32_t apply_op(uint32_t left, uint32_t right, int 
                                      *reinterpret_cast<const __nv_bfloat162*>(&right));
     return *reinterpret_cast<const uint32_t*>(&r);
   }
+  if (op == LCT_OP_LERP) return lerp_pair(left, right, alpha);
   const float l0 = bf16_low(left), l1 = bf16_high(left);
   const float r0 = bf16_low(right), r1 = bf16_high(right);
+  if (op == LCT_OP_EMA_SQUARE) {
+    const uint32_t scaled = pack_rn(__fmul_rn(l0, alpha), __fmul_rn(l1, alpha));
+    return pack_rn(__fmaf_rn(beta, __fmul_rn(r0, r0), bf16_low(scaled)),
+                   __fmaf_rn(beta, __fmul_rn(r1, r1), bf16_high(scaled)));
+  }
   if (alpha_one) {
     if (beta_one) return pack_rn(__fadd_rn(l0, r0), __fadd_rn(l1, r1));
     return pack_rn(__fmaf_rn(r0, beta, l0), __fmaf_rn(r1, beta, l1));
@@ -668,6 +686,26 @@ static inline int view_of(const lct_operand* in, OperandView* v) {
   v->blocks = o.blocks;
   v->base = o.base;
   v->mode = o.mode;
+  return 0;
+}
+
+// Operation code and its scalars: which of alpha / beta the kernels will read.
+static inline int check_op(int op, const float* alpha, const float* beta, int* alpha_is_one,
+                           int* beta_is_one) {
+  if (op < LCT_OP_ADD || op > LCT_OP_EMA_SQUARE) return LCT_E_BAD_ARGUMENT;
+  if (op == LCT_OP_SCALAR_MUL_ADD) {
+    if (!*alpha_is_one && alpha == nullptr) return LCT_E_NULL_POINTER;
+    if (!*beta_is_one && beta == nullptr) return LCT_E_NULL_POINTER;
+  } else if (op == LCT_OP_LERP) {
+    if (alpha == nullptr) return LCT_E_NULL_POINTER;
+    *alpha_is_one = 0;
+    *beta_is_one = beta == nullptr;  // beta: weight of the Nesterov direction, when one is emitted
+  } else if (op == LCT_OP_EMA_SQUARE) {
+    if (alpha == nullptr || beta == nullptr) return LCT_E_NULL_POINTER;
+    *alpha_is_one = *beta_is_one = 0;
+  } else {
+    *alpha_is_one = *beta_is_one = 1;
+  }
   return 0;
 }
 

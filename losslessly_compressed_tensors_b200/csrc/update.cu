@@ -24,6 +24,7 @@
 // exponents from the overflow step on into `spill` (logical order), which is
 // what the tail compaction reads afterwards; nothing else touches `spill`.
 #include "batch.cuh"
+#include "center.cuh"
 #include "decode_core.cuh"
 #include "encode_core.cuh"
 
@@ -192,6 +193,37 @@ update_sample_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other,
   update_sample_chunk(a, g, other, spec, known, samples, values, (int)blockIdx.x);
 }
 
+// The sample pre-pass and the center kernel in one, for an operand that carries the BF16
+// values at its sample positions (every result of a fused update does): one CTA, four samples
+// per thread computed from `known` and B, the results kept for the next update, then the
+// center and the shifted tables.  Launched as an ordinary kernel, so everything queued before
+// the update is complete when it starts.
+__global__ void __launch_bounds__(kTableThreads)
+update_center_known_kernel(const uint16_t* __restrict__ other, int64_t n, OpSpec spec,
+                           const uint16_t* __restrict__ known, uint16_t* __restrict__ values,
+                           const int32_t* __restrict__ base_encode,
+                           const int32_t* __restrict__ base_decode, int32_t* center_out,
+                           int32_t* shifted_encode, int32_t* shifted_decode) {
+  cudaTriggerProgrammaticLaunchCompletion();  // the fused kernel may start its prologue
+  const int64_t count = n < kSampleCount ? n : kSampleCount;
+  const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
+  const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
+  int raw[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t idx = threadIdx.x + k * kTableThreads;
+    raw[k] = -1;
+    if (idx < count) {
+      const uint32_t right = other[sample_position(idx, n)];
+      const uint32_t result = apply_op(known[idx], right, spec.op, spec.alpha_is_one != 0,
+                                       spec.beta_is_one != 0, alpha, beta) & 0xFFFFu;
+      raw[k] = (int)((result >> 7) & 0xFFu);
+      if (values != nullptr) values[idx] = (uint16_t)result;
+    }
+  }
+  center_from_samples(raw, base_encode, base_decode, center_out, shifted_encode, shifted_decode);
+}
+
 // Geometry of one job of a batched update (all jobs share `common`).
 __device__ __forceinline__ Shape shape_of_update(const lct_update_job& job, const Shape& common) {
   Shape g = common;
@@ -249,13 +281,16 @@ __device__ __forceinline__ void split_row(const uint32_t r[4], uint32_t q, uint3
 // words go straight to global memory (a warp's lanes write neighbouring words of the same
 // payload rows; L2 merges the sectors), which keeps four CTAs resident per SM.
 // One codec block.  extra_starts and summaries are the tensor's own arrays.
-template <int kLaneMask>
+// kEmit (LCT_EMIT_*): also write a dense BF16 tensor - the result itself or the Nesterov
+// direction lerp(B, result, beta) - to dense_out, which may alias `other` (hence neither is
+// `__restrict__` here: a thread reads its eight values of B before it overwrites them).
+template <int kLaneMask, int kEmit>
 __device__ __forceinline__ void update_fused_block(
-    const OperandView& a, const Shape& g_in, const uint16_t* __restrict__ other,
+    const OperandView& a, const Shape& g_in, const uint16_t* other,
     bool other_vector_ok, const OpSpec& spec, const int32_t* __restrict__ shifted_encode,
     uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
     uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
-    uint8_t* __restrict__ spill, int64_t block) {
+    uint8_t* __restrict__ spill, uint16_t* dense_out, int64_t block) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Shape g = g_in;
   if (kLaneMask >= 0) g.lane_mask = kLaneMask;  // compile-time lane mapping, see decode_block
@@ -336,6 +371,21 @@ __device__ __forceinline__ void update_fused_block(
           for (int i = 0; i < 8; ++i)
             if (l_at + i >= g.logical_numel) result[i >> 1] &= (i & 1) ? 0x0000FFFFu : 0xFFFF0000u;
         }
+        if (kEmit != LCT_EMIT_NONE) {
+          uint32_t dense[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            dense[k] = kEmit == LCT_EMIT_NESTEROV ? lerp_pair(right[k], result[k], beta) : result[k];
+          if (l_at + 8 <= g.logical_numel) {
+            __stcs(reinterpret_cast<uint4*>(dense_out + l_at),
+                   make_uint4(dense[0], dense[1], dense[2], dense[3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (l_at + i < g.logical_numel)
+                dense_out[l_at + i] = (uint16_t)(dense[i >> 1] >> (16 * (i & 1)));
+          }
+        }
         uint2 side_lane_order;
         split_row(result, place.q, half ? &e_bot03 : &e_top03, half ? &e_bot47 : &e_top47,
                   &side_lane_order);
@@ -395,15 +445,16 @@ __device__ __forceinline__ void update_fused_block(
   }
 }
 
-template <int kLaneMask>
+template <int kLaneMask, int kEmit>
 __global__ void __launch_bounds__(kThreads, 4)
-update_fused_kernel(OperandView a, Shape g, const uint16_t* __restrict__ other, bool other_vector_ok,
+update_fused_kernel(OperandView a, Shape g, const uint16_t* other, bool other_vector_ok,
                     OpSpec spec, const int32_t* __restrict__ shifted_encode,
                     uint8_t* __restrict__ side_out, uint32_t* __restrict__ encoded_out,
                     uint8_t* __restrict__ extra_starts, int32_t* __restrict__ summaries,
-                    uint8_t* __restrict__ spill) {
-  update_fused_block<kLaneMask>(a, g, other, other_vector_ok, spec, shifted_encode, side_out,
-                                encoded_out, extra_starts, summaries, spill, blockIdx.x);
+                    uint8_t* __restrict__ spill, uint16_t* dense_out) {
+  update_fused_block<kLaneMask, kEmit>(a, g, other, other_vector_ok, spec, shifted_encode,
+                                       side_out, encoded_out, extra_starts, summaries, spill,
+                                       dense_out, blockIdx.x);
 }
 
 // Every block of every job of a batch: CTA b serves the job whose block range contains b.
@@ -420,13 +471,11 @@ update_fused_batch_kernel(const lct_update_job* __restrict__ jobs, int n_jobs, S
   }
   const lct_update_job& job = jobs[lo];
   const bool vector_ok = (reinterpret_cast<uintptr_t>(job.other) & 15u) == 0;
-  update_fused_block<kLaneMask>(view_of_update(job.a), shape_of_update(job, common),
-                                static_cast<const uint16_t*>(job.other), vector_ok, spec,
-                                shifted_encode + 256 * (int64_t)lo, job.side_out,
-                                reinterpret_cast<uint32_t*>(job.encoded_out),
-                                extra_starts + job.first_block * kLanes,
-                                summaries + 4 * job.first_block, job.spill,
-                                block - job.first_block);
+  update_fused_block<kLaneMask, LCT_EMIT_NONE>(
+      view_of_update(job.a), shape_of_update(job, common), static_cast<const uint16_t*>(job.other),
+      vector_ok, spec, shifted_encode + 256 * (int64_t)lo, job.side_out,
+      reinterpret_cast<uint32_t*>(job.encoded_out), extra_starts + job.first_block * kLanes,
+      summaries + 4 * job.first_block, job.spill, nullptr, block - job.first_block);
 }
 
 }  // namespace lct
@@ -440,14 +489,7 @@ static int check_update_args(const lct_operand* a, const void* other, const floa
   if (rc) return rc;
   if (other == nullptr) return LCT_E_NULL_POINTER;
   if ((reinterpret_cast<uintptr_t>(other) & 1u) != 0) return LCT_E_ALIGNMENT;
-  if (op < LCT_OP_ADD || op > LCT_OP_SCALAR_MUL_ADD) return LCT_E_BAD_ARGUMENT;
-  if (op == LCT_OP_SCALAR_MUL_ADD) {
-    if (!*alpha_is_one && alpha == nullptr) return LCT_E_NULL_POINTER;
-    if (!*beta_is_one && beta == nullptr) return LCT_E_NULL_POINTER;
-  } else {
-    *alpha_is_one = *beta_is_one = 1;
-  }
-  return 0;
+  return lct::check_op(op, alpha, beta, alpha_is_one, beta_is_one);
 }
 
 static int launch_sample(const lct_operand* a, const void* other, const float* alpha,
@@ -478,7 +520,8 @@ static int launch_fused(const lct_operand* a, const void* other, const float* al
                         const int32_t* shifted_encode, uint8_t* side_out, int32_t* encoded_out,
                         uint8_t* extra_starts, int32_t* summaries, uint8_t* spill, int64_t size,
                         int64_t logical_numel, int block_symbols, int steps, int fixed_words,
-                        int rare_length, bool overlapped, cudaStream_t stream) {
+                        int rare_length, bool overlapped, void* dense_out, int emit,
+                        cudaStream_t stream) {
   lct::Shape g;
   lct::OperandView va;
   int rc = lct::check_shape(size, logical_numel, block_symbols, steps, fixed_words, rare_length, &g);
@@ -488,19 +531,34 @@ static int launch_fused(const lct_operand* a, const void* other, const float* al
       extra_starts == nullptr || summaries == nullptr || spill == nullptr)
     return LCT_E_NULL_POINTER;
   if (!lct::aligned16(side_out) || !lct::aligned16(encoded_out)) return LCT_E_ALIGNMENT;
+  if (emit < LCT_EMIT_NONE || emit > LCT_EMIT_NESTEROV) return LCT_E_BAD_ARGUMENT;
+  if (emit != LCT_EMIT_NONE) {
+    if (dense_out == nullptr) return LCT_E_NULL_POINTER;
+    if (!lct::aligned16(dense_out)) return LCT_E_ALIGNMENT;
+    if (emit == LCT_EMIT_NESTEROV && (op != LCT_OP_LERP || beta == nullptr)) return LCT_E_BAD_ARGUMENT;
+  }
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
   const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
-  auto kernel = g.lane_mask == 254 ? lct::update_fused_kernel<254> : lct::update_fused_kernel<-1>;
+  const bool swizzled = g.lane_mask == 254;
+  auto kernel = emit == LCT_EMIT_NESTEROV
+                    ? (swizzled ? lct::update_fused_kernel<254, LCT_EMIT_NESTEROV>
+                                : lct::update_fused_kernel<-1, LCT_EMIT_NESTEROV>)
+                : emit == LCT_EMIT_RESULT
+                    ? (swizzled ? lct::update_fused_kernel<254, LCT_EMIT_RESULT>
+                                : lct::update_fused_kernel<-1, LCT_EMIT_RESULT>)
+                    : (swizzled ? lct::update_fused_kernel<254, LCT_EMIT_NONE>
+                                : lct::update_fused_kernel<-1, LCT_EMIT_NONE>);
   if ((rc = lct::opt_in_shared(kernel, shared)) != 0) return rc;
   const uint16_t* dense = static_cast<const uint16_t*>(other);
   uint32_t* words = reinterpret_cast<uint32_t*>(encoded_out);
+  uint16_t* emitted = static_cast<uint16_t*>(dense_out);
   if (overlapped)
-    return lct::launch_overlapped(kernel, (unsigned)g.n_blocks, lct::kThreads,
-                                  shared, stream, va, g, dense, lct::aligned16(other), spec,
-                                  shifted_encode, side_out, words, extra_starts, summaries, spill);
+    return lct::launch_overlapped(kernel, (unsigned)g.n_blocks, lct::kThreads, shared, stream, va,
+                                  g, dense, lct::aligned16(other), spec, shifted_encode, side_out,
+                                  words, extra_starts, summaries, spill, emitted);
   kernel<<<(unsigned)g.n_blocks, lct::kThreads, shared, stream>>>(
       va, g, dense, lct::aligned16(other), spec, shifted_encode, side_out, words, extra_starts,
-      summaries, spill);
+      summaries, spill, emitted);
   return (int)cudaGetLastError();
 }
 
@@ -522,8 +580,68 @@ int lct_update_fused(const lct_operand* a, const void* other, const float* alpha
                      int rare_length, void* stream) {
   return launch_fused(a, other, alpha, beta, op, alpha_is_one, beta_is_one, shifted_encode,
                       side_out, encoded_out, extra_starts, summaries, spill, size, logical_numel,
-                      block_symbols, steps, fixed_words, rare_length, false,
+                      block_symbols, steps, fixed_words, rare_length, false, nullptr, LCT_EMIT_NONE,
                       static_cast<cudaStream_t>(stream));
+}
+
+int lct_update_emit(const lct_operand* a, const void* other, const float* alpha,
+                    const float* beta, int op, int alpha_is_one, int beta_is_one,
+                    const int32_t* encode_table, const int32_t* decode_table, uint8_t* samples,
+                    const uint16_t* known_values, uint16_t* result_values, int32_t* center,
+                    int32_t* shifted_encode, int32_t* shifted_decode, uint8_t* side_out,
+                    int32_t* encoded_out, uint8_t* extra_starts, int32_t* summaries,
+                    uint8_t* spill, int32_t* counts, int32_t* descriptor, int32_t* blocks_out,
+                    void* arena_storage, int max_free_regions, int64_t size,
+                    int64_t logical_numel, int block_symbols, int steps, int fixed_words,
+                    int rare_length, void* dense_out, int emit, int32_t* release_descriptor,
+                    int32_t* release_status, void* stream) {
+  if (encode_table == nullptr || decode_table == nullptr || center == nullptr ||
+      counts == nullptr || descriptor == nullptr || arena_storage == nullptr)
+    return LCT_E_NULL_POINTER;
+  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (known_values != nullptr) {
+    // 1+2. sample pre-pass and center in one ordinary launch (so everything queued before this
+    //      call is complete and visible before any kernel of the update starts).
+    lct::Shape g;
+    lct::OperandView va;
+    rc = lct::check_shape(size, logical_numel, block_symbols, steps, fixed_words, rare_length, &g);
+    if (rc) return rc;
+    if ((rc = check_update_args(a, other, alpha, beta, op, &alpha_is_one, &beta_is_one, &va))) return rc;
+    if ((reinterpret_cast<uintptr_t>(known_values) | reinterpret_cast<uintptr_t>(result_values)) & 1u)
+      return LCT_E_ALIGNMENT;
+    if (shifted_encode == nullptr || shifted_decode == nullptr) return LCT_E_NULL_POINTER;
+    const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};
+    lct::update_center_known_kernel<<<1, lct::kTableThreads, 0, st>>>(
+        static_cast<const uint16_t*>(other), logical_numel, spec, known_values, result_values,
+        encode_table, decode_table, center, shifted_encode, shifted_decode);
+    if ((rc = (int)cudaGetLastError()) != 0) return rc;
+  } else {
+    // 1. the sample pre-pass: an ordinary launch, as above.
+    rc = launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples,
+                       known_values, result_values, size, logical_numel, block_symbols, steps,
+                       fixed_words, rare_length, st);
+    if (rc) return rc;
+    // 2. the center from the samples.
+    const int64_t count = logical_numel < lct::kSampleCount ? logical_numel : lct::kSampleCount;
+    rc = lct::launch_center(samples, count, true, encode_table, decode_table, center,
+                            shifted_encode, shifted_decode, true, st);
+    if (rc) return rc;
+  }
+  // 3-5. each may be scheduled while its predecessor runs and waits for it on the device.
+  rc = launch_fused(a, other, alpha, beta, op, alpha_is_one, beta_is_one, shifted_encode, side_out,
+                    encoded_out, extra_starts, summaries, spill, size, logical_numel, block_symbols,
+                    steps, fixed_words, rare_length, true, dense_out, emit, st);
+  if (rc) return rc;
+  rc = lct::launch_scan_allocate(summaries, counts, descriptor, arena_storage, size / block_symbols,
+                                 max_free_regions, true, st, release_descriptor, release_status);
+  if (rc) return rc;
+  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
+  uint8_t* payload = static_cast<uint8_t*>(arena_storage) + metadata;
+  return lct::launch_compact(spill, payload, payload, payload, descriptor, counts, blocks_out,
+                             extra_starts, summaries, size, logical_numel, block_symbols, steps, 1,
+                             true, st);
 }
 
 int lct_update(const lct_operand* a, const void* other, const float* alpha, const float* beta,
@@ -535,34 +653,12 @@ int lct_update(const lct_operand* a, const void* other, const float* alpha, cons
                int32_t* counts, int32_t* descriptor, int32_t* blocks_out, void* arena_storage,
                int max_free_regions, int64_t size, int64_t logical_numel, int block_symbols,
                int steps, int fixed_words, int rare_length, void* stream) {
-  if (encode_table == nullptr || decode_table == nullptr || center == nullptr ||
-      counts == nullptr || descriptor == nullptr || arena_storage == nullptr)
-    return LCT_E_NULL_POINTER;
-  if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // 1. the sample pre-pass: an ordinary launch, so everything queued before this call is
-  //    complete and visible before any of the five kernels starts.
-  int rc = launch_sample(a, other, alpha, beta, op, alpha_is_one, beta_is_one, samples,
-                         known_values, result_values, size, logical_numel, block_symbols, steps,
-                         fixed_words, rare_length, st);
-  if (rc) return rc;
-  // 2-5. each may be scheduled while its predecessor runs and waits for it on the device.
-  const int64_t count = logical_numel < lct::kSampleCount ? logical_numel : lct::kSampleCount;
-  rc = lct::launch_center(samples, count, true, encode_table, decode_table, center, shifted_encode,
-                          shifted_decode, true, st);
-  if (rc) return rc;
-  rc = launch_fused(a, other, alpha, beta, op, alpha_is_one, beta_is_one, shifted_encode, side_out,
-                    encoded_out, extra_starts, summaries, spill, size, logical_numel, block_symbols,
-                    steps, fixed_words, rare_length, true, st);
-  if (rc) return rc;
-  rc = lct::launch_scan_allocate(summaries, counts, descriptor, arena_storage, size / block_symbols,
-                                 max_free_regions, true, st);
-  if (rc) return rc;
-  const size_t metadata = ((size_t)8 * max_free_regions + 12 + 15) / 16 * 16;
-  uint8_t* payload = static_cast<uint8_t*>(arena_storage) + metadata;
-  return lct::launch_compact(spill, payload, payload, payload, descriptor, counts, blocks_out,
-                             extra_starts, summaries, size, logical_numel, block_symbols, steps, 1,
-                             true, st);
+  return lct_update_emit(a, other, alpha, beta, op, alpha_is_one, beta_is_one, encode_table,
+                         decode_table, samples, known_values, result_values, center,
+                         shifted_encode, shifted_decode, side_out, encoded_out, extra_starts,
+                         summaries, spill, counts, descriptor, blocks_out, arena_storage,
+                         max_free_regions, size, logical_numel, block_symbols, steps, fixed_words,
+                         rare_length, nullptr, LCT_EMIT_NONE, nullptr, nullptr, stream);
 }
 
 int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
@@ -579,16 +675,11 @@ int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_block
   if (n_jobs <= 0 || n_jobs > 65535 || total_blocks <= 0 || total_blocks > 0x7FFFFFFFLL)
     return LCT_E_BAD_ARGUMENT;
   if (max_free_regions <= 0 || (max_free_regions & (max_free_regions - 1))) return LCT_E_BAD_ARGUMENT;
-  if (op < LCT_OP_ADD || op > LCT_OP_SCALAR_MUL_ADD) return LCT_E_BAD_ARGUMENT;
-  if (op == LCT_OP_SCALAR_MUL_ADD) {
-    if (!alpha_is_one && alpha == nullptr) return LCT_E_NULL_POINTER;
-    if (!beta_is_one && beta == nullptr) return LCT_E_NULL_POINTER;
-  } else {
-    alpha_is_one = beta_is_one = 1;
-  }
   lct::Shape g;
-  int rc = lct::check_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words,
-                            rare_length, &g);
+  int rc = lct::check_op(op, alpha, beta, &alpha_is_one, &beta_is_one);
+  if (rc) return rc;
+  rc = lct::check_shape(block_symbols, block_symbols, block_symbols, steps, fixed_words,
+                        rare_length, &g);
   if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const lct::OpSpec spec{alpha, beta, op, alpha_is_one, beta_is_one};

@@ -84,6 +84,9 @@ _SIGNATURES = {
                          _i64, _i64, _i, _i, _i, _i, _p],
     "lct_update": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p,
                    _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _p],
+    "lct_update_emit": [ctypes.POINTER(Operand), _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p,
+                        _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _p,
+                        _i, _p, _p, _p],
     "lct_update_batch": [_p, _i, _i64, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i,
                          _i, _i, _p],
     "lct_dual_scale_add": [ctypes.POINTER(Operand), ctypes.POINTER(Operand), _p, _p, _p, _i,

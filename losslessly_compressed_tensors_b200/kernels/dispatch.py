@@ -26,7 +26,8 @@ from . import _lib
 from ._lib import DecodeJob, EncodeJob, Operand, Overflow, UpdateJob
 from .backends import FallbackStorage
 
-OP_ADD, OP_MULTIPLY, OP_SCALAR_MUL_ADD = 0, 1, 2
+OP_ADD, OP_MULTIPLY, OP_SCALAR_MUL_ADD, OP_LERP, OP_EMA_SQUARE = 0, 1, 2, 3, 4
+EMIT_NONE, EMIT_RESULT, EMIT_NESTEROV = 0, 1, 2
 
 
 def _ptr(tensor: torch.Tensor | None) -> int | None:

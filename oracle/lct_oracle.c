@@ -405,7 +405,15 @@ static uint16_t double_to_bf16(double d) {
   return sign | (uint16_t)bits;
 }
 
-enum { OP_ADD = 0, OP_MULTIPLY = 1, OP_SCALED = 2 };
+enum { OP_ADD = 0, OP_MULTIPLY = 1, OP_SCALED = 2, OP_LERP = 3, OP_EMA_SQUARE = 4 };
+
+/* torch.lerp(start, end, weight) on float32 as PyTorch's CUDA kernel evaluates it (the formula
+ * of ATen/native/Lerp.h with the multiply-adds contracted; pinned against torch on a GPU by
+ * tests/test_gpu_momentum.py): what LCT/components/sparse_utils.py:88-90,193 computes. */
+static float lerp_f32(float start, float end, float weight) {
+  float d = end - start;
+  return fabsf(weight) < 0.5f ? fmaf(weight, d, start) : fmaf(-d, 1.0f - weight, end);
+}
 
 /* pointwise.py:340-363 followed by the BF16 rounding of :50. */
 static uint16_t apply_op(int op, uint16_t left, uint16_t right, float alpha, float beta,
@@ -415,6 +423,11 @@ static uint16_t apply_op(int op, uint16_t left, uint16_t right, float alpha, flo
    * (products) or to far more than twice the target precision (sums). */
   if (op == OP_ADD) return double_to_bf16((double)a + (double)b);
   if (op == OP_MULTIPLY) return double_to_bf16((double)a * (double)b);
+  if (op == OP_LERP) return float_to_bf16(lerp_f32(a, b, alpha));
+  if (op == OP_EMA_SQUARE) { /* sparse_utils.py:194: mul_(beta2) rounds, then addcmul_ */
+    float scaled = bf16_to_float(float_to_bf16(a * alpha));
+    return float_to_bf16(fmaf(beta, b * b, scaled));
+  }
   float r;
   if (alpha_is_one) r = beta_is_one ? a + b : fmaf(b, beta, a);
   else r = fmaf(a, alpha, beta_is_one ? b : b * beta);
@@ -468,6 +481,15 @@ void orc_pointwise(const int32_t *encoded, const uint8_t *side, const int32_t *s
       }
     }
   }
+}
+
+/* out = bf16(lerp(start, end, weight)) elementwise on BF16 bit patterns: the Nesterov direction
+ * grad.lerp_(momentum, mu) of sparse_utils.py:90. */
+void orc_lerp_dense(const uint16_t *start, const uint16_t *end, float weight, int64_t n,
+                    uint16_t *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i)
+    out[i] = float_to_bf16(lerp_f32(bf16_to_float(start[i]), bf16_to_float(end[i]), weight));
 }
 
 /* alpha * compA + compB: pointwise_scalar_dual.py:118-346. */

@@ -20,7 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "liblct_oracle.so")
 
 LANES = 256
-OP_ADD, OP_MULTIPLY, OP_SCALED = 0, 1, 2
+OP_ADD, OP_MULTIPLY, OP_SCALED, OP_LERP, OP_EMA_SQUARE = 0, 1, 2, 3, 4
 
 
 def build(force: bool = False) -> str:
@@ -183,6 +183,16 @@ def pointwise(c: dict, other: np.ndarray, op: int, alpha: float = 1.0, beta: flo
                         ctypes.c_float(beta), _i32(int(alpha_is_one)), _i32(int(beta_is_one)),
                         _p(dense_out), _p(side_out), _p(exp_out))
     return dense_out if dense else (side_out, exp_out)
+
+
+def lerp_dense(start: np.ndarray, end: np.ndarray, weight: float) -> np.ndarray:
+    """``bf16(torch.lerp(start, end, weight))`` on BF16 bit patterns, float32 arithmetic of
+    PyTorch's CUDA kernel (``sparse_utils.py:90``: the Nesterov direction)."""
+    start = np.ascontiguousarray(start).reshape(-1).view(np.uint16)
+    end = np.ascontiguousarray(end).reshape(-1).view(np.uint16)
+    out = np.zeros(start.size, np.uint16)
+    lib().orc_lerp_dense(_p(start), _p(end), ctypes.c_float(weight), _i64(start.size), _p(out))
+    return out
 
 
 def dual(a: dict, b: dict, alpha: float, *, dense: bool = True):
