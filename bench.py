@@ -623,6 +623,67 @@ def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
     return out
 
 
+def activations_leg(steps: int = 10, warmup: int = 3) -> dict:
+    """The activations one GPT-2-small block saves for backward (8 x 1024 tokens, d_model 768:
+    block input, two layer-norm outputs, QKV, attention output, MLP pre-activation and GELU
+    output; seeded N(0, 1) values through the real nonlinearities), kept compressed between
+    forward and backward in one arena (reference pattern: LCT/components/layers.py:57,116,166,
+    211,237 - compress at save, decompress + free in backward).  A step = store all, load all.
+    `per_tensor`: one compress / decompress / free per tensor; `batched`: the group calls of
+    ActivationCache(batch=0).  CUDA events around the step; launches counted on the host."""
+    from losslessly_compressed_tensors_b200.components.activations import ActivationCache
+    from losslessly_compressed_tensors_b200.components.dist_configs import act_dist
+    from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer, verify_buffer
+
+    tokens, d = 8 * 1024, 768
+    gen = torch.Generator(device="cuda").manual_seed(30)
+
+    def normal(cols):
+        return torch.randn(tokens, cols, device="cuda", generator=gen)
+
+    x = normal(d)
+    ln1 = torch.nn.functional.layer_norm(x, (d,))
+    qkv = normal(3 * d)
+    attn = normal(d) * 0.5
+    x2 = x + attn
+    ln2 = torch.nn.functional.layer_norm(x2, (d,))
+    fc = normal(4 * d)
+    act = torch.nn.functional.gelu(fc)
+    saved = [t.to(torch.bfloat16) for t in (x, ln1, qkv, attn, ln2, fc, act)]
+    dense_bytes = sum(t.numel() * 2 for t in saved)
+    buffer = TensorBuffer(64 << 20)
+    out = {"tensors": len(saved), "dense_bytes_per_step": dense_bytes}
+    for label, batch in (("per_tensor", None), ("batched", 0)):
+        cache = ActivationCache(buffer, act_dist, min_elements=65536, batch=batch)
+        times, exact = [], True
+        for it in range(warmup + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with LaunchTrace() as trace:
+                a.record()
+                handles = [cache.store(t) for t in saved]
+                cache.flush()
+                loaded = [h.load() for h in reversed(handles)]
+                b.record()
+            launches = trace.count
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(a.elapsed_time(b))
+            if it == warmup:
+                exact = all(torch.equal(got.view(torch.int16), want.view(torch.int16))
+                            for got, want in zip(loaded, reversed(saved)))
+            del handles, loaded
+        out[label + "_ms_per_step"] = statistics.mean(times)
+        out[label + "_launches_per_step"] = launches
+        out[label + "_gbps"] = 2 * dense_bytes / statistics.mean(times) / 1e6
+        out[label + "_bit_exact"] = exact
+    verify_buffer(buffer)
+    out["speedup"] = out["per_tensor_ms_per_step"] / out["batched_ms_per_step"]
+    out["workload"] = ("saved activations of one GPT-2-small block, 8192 tokens, LAPLACE/CLEAN, one "
+                       "64 MiB arena; step = compress all + decompress all + free all; "
+                       "gbps = BF16 bytes in + out per step")
+    return out
+
+
 def run_ours(args, rank: int, world: int, local: int):
     from losslessly_compressed_tensors_b200.codec import encode as encode_module
     from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType
@@ -823,6 +884,7 @@ def run_ours(args, rank: int, world: int, local: int):
     update = update_leg() if (rank == 0 and "update" in legs) else None
     arena = arena_leg() if (rank == 0 and "arena" in legs) else None
     momentum = momentum_leg() if (rank == 0 and "momentum" in legs) else None
+    activations = activations_leg() if (rank == 0 and "activations" in legs) else None
     if rank != 0:
         return
     triton_reference = (triton_reference_leg() if world == 1 and "triton" in legs else None)
@@ -860,7 +922,7 @@ def run_ours(args, rank: int, world: int, local: int):
         "gpu_launches": launches, "clocks": clocks,
         "encode_ms_without_arena": statistics.mean(private_ms),
         "graph_replay_ms_per_step": graph_ms, "arena": arena, "update": update,
-        "momentum": momentum,
+        "momentum": momentum, "activations": activations,
     }
     if world == 1 and not args.no_cpu:
         bits = host_x.view(torch.int16).numpy().reshape(-1)
@@ -902,9 +964,10 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--no-sharded", action="store_true",
                         help="skip the extra legs (configurations 3, 4 and 5)")
-    parser.add_argument("--legs", default="sharded,update,momentum,arena,triton",
+    parser.add_argument("--legs", default="sharded,update,momentum,activations,arena,triton",
                         help="extra legs to run after configuration 2: sharded (configuration 5), "
-                             "update (configuration 4), momentum (Muon's momentum step), arena (configuration 3), triton (the "
+                             "update (configuration 4), momentum (Muon's momentum step), activations (a block's saved activations), "
+                             "arena (configuration 3), triton (the "
                              "reference's own kernels on this GPU, N = 1); with N > 1 the sharded "
                              "leg always includes the peer-memory decode")
     args = parser.parse_args()

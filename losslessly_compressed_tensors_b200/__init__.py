@@ -8,5 +8,5 @@ loaded on first use by ``kernels.dispatch``.
 
 __all__ = [
     "comp_format", "comp_tensor", "tensor_buffer", "operations", "LCTensor",
-    "codec", "compression", "kernels", "config", "sharded",
+    "codec", "compression", "kernels", "config", "sharded", "serialization",
 ]

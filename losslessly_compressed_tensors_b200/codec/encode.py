@@ -205,3 +205,59 @@ def encode(data: torch.Tensor, distribution: Distribution, buffer: TensorBuffer 
         source.view(torch.int16), sign_mantissa, storage_numel, distribution, buffer, shape,
         precomputed=False, logical_numel=logical_numel, out=out,
     )
+
+
+def encode_many(tensors: list[torch.Tensor], distribution: Distribution,
+                buffer: TensorBuffer) -> list[CompressedTensor]:
+    """Compress many BF16 tensors of any shapes with ONE codebook into ``buffer``'s arena by four
+    launches in all (centers, encode, scans + reservations in list order, tails) instead of four
+    per tensor.  Every result holds the tensors and the bytes ``encode`` gives it, and the arena
+    ends up as after one ``encode`` per tensor in list order.  Nothing synchronises the host.
+    No counterpart in the reference, which compresses one tensor per call
+    (``LCT/codec/encode.py:189-218``); its layers do so for every activation they save."""
+    if buffer is None:
+        raise ValueError("encode_many needs a TensorBuffer")
+    if buffer.capacity_bytes % 4:
+        raise ValueError("TensorBuffer capacity must be divisible by 4")
+    if not tensors:
+        return []
+    device = tensors[0].device
+    stream_geometry = geometry(distribution)
+    block_symbols, lanes, steps, fixed_words = stream_geometry
+    encode_table, decode_table, _ = get_distribution_tables(distribution, device)
+
+    def new(n, dtype):
+        return torch.empty(n, dtype=dtype, device=device)
+
+    results: list[CompressedTensor | None] = []
+    jobs = []
+    for data in tensors:
+        if data.dtype != torch.bfloat16:
+            raise TypeError(f"the codec compresses bfloat16 tensors, got {data.dtype}")
+        if data.device != device:
+            raise ValueError("encode_many needs all tensors on one device")
+        if not data.numel():                 # nothing to launch: the one-tensor path's metadata
+            results.append(encode(data, distribution, buffer))
+            continue
+        source = data.detach().contiguous().view(-1).view(torch.int16)
+        blocks = -(-source.numel() // block_symbols)
+        size = blocks * block_symbols
+        counts = new(4, torch.int32)
+        c = CompressedTensor(
+            new(blocks * lanes * fixed_words + 4, torch.int32), size, new(size, torch.uint8),
+            fallback_starts=None, fallback_lanes=None, fallback_blocks=new(3 * blocks, torch.int32),
+            fallback_buffer=buffer.data, fallback_descriptor=new(4, torch.int32), buffer=buffer,
+            fallback_count=counts[:1], fallback_used=counts[1:2], distribution=distribution,
+            center=new(1, torch.int32), decode_table=new(decode_table.numel(), torch.int32),
+            shape=tuple(data.shape), layout=StorageLayout.COMPRESSED,
+            stream_geometry=stream_geometry)
+        jobs.append(dict(src=source, side=c.sign_mantissa, encoded=c.data, center=c.center,
+                         decode_table=c.decode_table, counts=counts,
+                         descriptor=c.fallback_descriptor, blocks=c.fallback_blocks, size=size,
+                         logical_numel=source.numel()))
+        results.append(c)
+    if jobs:
+        dispatch.compress_batch(jobs, encode_table, decode_table, buffer,
+                                block_symbols=block_symbols, lanes=lanes, steps=steps,
+                                fixed_words=fixed_words)
+    return results

@@ -102,6 +102,22 @@ class CompressedTensor:
         return (_owned_bytes(t for t in owned if isinstance(t, torch.Tensor))
                 + self.memory_buffer_size())
 
+    # -- leaving the process -------------------------------------------------------------------------
+
+    def to_bytes(self) -> bytes:
+        """Self-describing byte form (header with geometry, codebook, shape and component
+        offsets, then the codec bytes); see ``serialization.py``.  One host synchronisation."""
+        from .serialization import to_bytes
+
+        return to_bytes(self)
+
+    @classmethod
+    def from_bytes(cls, blob, device="cuda") -> "CompressedTensor":
+        """The tensor ``to_bytes`` wrote, on ``device``, owning all its memory."""
+        from .serialization import from_bytes
+
+        return from_bytes(blob, device)
+
     def free(self) -> None:
         """Return this tensor's arena region, if it has one.  Reading it afterwards is undefined."""
         if self.buffer is None or self.fallback_descriptor is None:

@@ -11,6 +11,9 @@ the arena region.  Here the same ownership pattern is offered for ANY module, in
 * ``compressed_saved_tensors(...)`` - a context manager over autograd's saved-tensor hooks that
   applies the cache to every eligible tensor the wrapped forward saves.
 
+A cache built with ``batch=...`` compresses the tensors of a layer together (four launches
+per group instead of four per tensor) and decodes them together (one launch).
+
 Eligible: CUDA, bfloat16, at least ``min_elements`` elements, not a parameter (leaf that
 requires grad).  Everything else is kept as it is.  The codec is lossless, so gradients are
 bit-identical with and without the cache.
@@ -18,35 +21,78 @@ bit-identical with and without the cache.
 from __future__ import annotations
 
 import contextlib
+import weakref
 
 import torch
 from torch import Tensor
 
 from ..LCTensor import LCTTensor
 from ..comp_format import Distribution
-from ..operations import compress, decompress
+from ..operations import compress, compress_many, decompress, decompress_many, free_many
 from ..tensor_buffer import TensorBuffer
 from .dist_configs import act_dist, weight_dist
+
+
+class _Group:
+    """Tensors stored between two ``flush`` calls of a batching cache: compressed together by
+    four launches, decoded together by one when the first of them is loaded, released together
+    by one."""
+
+    __slots__ = ("cache", "members")
+
+    def __init__(self, cache: "ActivationCache"):
+        self.cache, self.members = cache, []      # weak: a dropped graph must free its handles
+
+    def add(self, handle: "_Handle") -> None:
+        self.members.append(weakref.ref(handle))
+
+    @property
+    def handles(self) -> list:
+        return [h for h in (ref() for ref in self.members) if h is not None]
+
+    def compress(self) -> None:
+        waiting = [h for h in self.handles if h._pending is not None]
+        if not waiting:
+            return
+        results = compress_many([h._pending for h in waiting], self.cache.distribution,
+                                self.cache.buffer)
+        for handle, compressed in zip(waiting, results):
+            handle._compressed, handle._pending = compressed, None
+
+    def decode(self) -> None:
+        held = [h for h in self.handles if h._compressed is not None]
+        if not held:
+            return
+        for handle, dense in zip(held, decompress_many([h._compressed for h in held])):
+            handle._dense = dense
+        free_many([h._compressed for h in held])
+        for handle in held:
+            handle._compressed = None
 
 
 class _Handle:
     """One cached activation.  ``load`` may be called more than once (retained graphs); the
     compressed form is released at the first call and the dense tensor is kept from then on."""
 
-    __slots__ = ("_compressed", "_dense")
+    __slots__ = ("_compressed", "_dense", "_pending", "_group", "__weakref__")
 
-    def __init__(self, compressed=None, dense=None):
-        self._compressed, self._dense = compressed, dense
+    def __init__(self, compressed=None, dense=None, pending=None, group=None):
+        self._compressed, self._dense, self._pending, self._group = compressed, dense, pending, group
 
     @property
     def is_compressed(self) -> bool:
         return self._compressed is not None
 
     def load(self) -> Tensor:
-        if self._compressed is not None:
-            self._dense = decompress(self._compressed)
-            self._compressed.free()
-            self._compressed = None
+        if self._pending is not None:         # loaded before its group was compressed
+            self._dense, self._pending = self._pending, None
+        elif self._compressed is not None:
+            if self._group is not None:
+                self._group.decode()          # the whole group with one launch
+            else:
+                self._dense = decompress(self._compressed)
+                self._compressed.free()
+                self._compressed = None
         return self._dense
 
     def discard(self) -> None:
@@ -54,7 +100,7 @@ class _Handle:
         if self._compressed is not None:
             self._compressed.free()
             self._compressed = None
-        self._dense = None
+        self._dense = self._pending = None
 
     def __del__(self):
         # A graph dropped without a backward pass (an evaluation forward inside the context, an
@@ -66,14 +112,26 @@ class _Handle:
 
 
 class ActivationCache:
-    """Stores eligible tensors compressed in ``buffer`` (or in private tensors without one)."""
+    """Stores eligible tensors compressed in ``buffer`` (or in private tensors without one).
+
+    ``batch``: collect that many eligible tensors (or all until ``flush()``, with ``batch=0``)
+    and compress them together - four launches per group instead of four per tensor; the first
+    ``load`` of a group member decodes the whole group with one launch and releases its regions
+    with one more.  A layer's activations are saved together and needed together, so a group
+    per layer (``flush()`` at each layer's end, or ``batch`` = tensors saved per layer) costs
+    no extra peak memory.  Until a group is compressed its tensors are kept dense.  Needs a
+    ``buffer``.  ``batch=None`` (default): every tensor is compressed on its own at once."""
 
     def __init__(self, buffer: TensorBuffer | None = None, distribution: Distribution | None = None,
-                 min_elements: int = 65536):
+                 min_elements: int = 65536, batch: int | None = None):
+        if batch is not None and buffer is None:
+            raise ValueError("a batching ActivationCache needs a TensorBuffer")
         self.buffer = buffer
         self.distribution = distribution or act_dist
         self.min_elements = int(min_elements)
-        self.stored = 0           # tensors compressed so far
+        self.batch = batch
+        self._group = _Group(self) if batch is not None else None
+        self.stored = 0           # tensors compressed (or queued for it) so far
         self.dense_bytes = 0      # their BF16 bytes
         self.compressed_bytes = 0
 
@@ -86,12 +144,24 @@ class ActivationCache:
     def store(self, tensor: Tensor, *, track_sizes: bool = False) -> _Handle:
         if not self.eligible(tensor):
             return _Handle(dense=tensor)
-        compressed = compress(tensor.detach(), distribution=self.distribution, buffer=self.buffer)
         self.stored += 1
+        if self._group is not None:
+            handle = _Handle(pending=tensor.detach(), group=self._group)
+            self._group.add(handle)
+            if self.batch and len(self._group.members) >= self.batch:
+                self.flush()
+            return handle
+        compressed = compress(tensor.detach(), distribution=self.distribution, buffer=self.buffer)
         if track_sizes:   # memory_size() reads device counters: a host synchronisation
             self.dense_bytes += tensor.numel() * 2
             self.compressed_bytes += compressed.memory_size()
         return _Handle(compressed=compressed)
+
+    def flush(self) -> None:
+        """Compress the tensors stored since the last flush as one group and start a new one."""
+        if self._group is not None and self._group.members:
+            self._group.compress()
+            self._group = _Group(self)
 
 
 @contextlib.contextmanager
@@ -101,8 +171,11 @@ def compressed_saved_tensors(buffer: TensorBuffer | None = None,
     """Within the block, tensors that autograd saves for backward go through an
     ``ActivationCache`` (yielded, for its counters)."""
     cache = cache or ActivationCache(buffer, distribution, min_elements)
-    with torch.autograd.graph.saved_tensors_hooks(cache.store, _Handle.load):
-        yield cache
+    try:
+        with torch.autograd.graph.saved_tensors_hooks(cache.store, _Handle.load):
+            yield cache
+    finally:
+        cache.flush()      # a batching cache: what the forward stored last
 
 
 def dense_weight(weight: Tensor) -> Tensor:

@@ -357,9 +357,13 @@ def dual_scale_add(a: Operand, b: Operand, output, auxiliary, alpha, n_elements,
 # ---------------------------------------------------------------------------
 
 def _to_device(records, device: torch.device) -> torch.Tensor:
-    """A ctypes array of job records as a device byte tensor."""
-    raw = torch.frombuffer(bytearray(bytes(records)), dtype=torch.uint8)
-    return raw.to(device, non_blocking=True)
+    """A ctypes array of job records as a device byte tensor.  Staged through pinned memory so
+    that the copy is asynchronous: from pageable memory the host would wait for everything
+    queued on the stream before it could go on preparing the next call."""
+    nbytes = ctypes.sizeof(records)
+    staged = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    ctypes.memmove(staged.data_ptr(), ctypes.addressof(records), nbytes)
+    return staged.to(device, non_blocking=True)
 
 
 class CompressBatch:
@@ -397,7 +401,7 @@ class CompressBatch:
             self.shifted_encode.data_ptr(), block_symbols, steps, fixed_words)
 
     def run(self) -> None:
-        _call("lct_compress_batch", self.device, *self.args)
+        _call("lct_compress_batch", self.device, *self.args, launches=4)
 
 
 def compress_batch(jobs: list[dict], encode_table, decode_table, buffer, **geometry_kw):

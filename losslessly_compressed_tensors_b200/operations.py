@@ -62,6 +62,34 @@ def decompress(data: CompressedTensor) -> Tensor:
     return _decode.decode(data)
 
 
+@torch.compiler.disable
+def compress_many(tensors: list[Tensor], distribution: Distribution | None = None,
+                  buffer: TensorBuffer | None = None) -> list[CompressedTensor]:
+    """``compress`` of every tensor of a list with one codebook: four launches in all when a
+    ``buffer`` is given (one call per tensor without one).  Same results, same arena."""
+    distribution = distribution if distribution is not None else Distribution()
+    if buffer is None:
+        return [compress(t, distribution, None) for t in tensors]
+    return _encode.encode_many(list(tensors), distribution, buffer)
+
+
+@torch.compiler.disable
+def decompress_many(items: list[CompressedTensor]) -> list[Tensor]:
+    """``decompress`` of every item with one launch per codebook geometry."""
+    return _decode.decode_many(list(items))
+
+
+def free_many(items: list[CompressedTensor]) -> None:
+    """``free()`` of every item: one launch per arena instead of one per tensor, the regions
+    returned in list order."""
+    arenas: dict = {}
+    for item in items:
+        if item.buffer is not None and item.fallback_descriptor is not None:
+            arenas.setdefault(id(item.buffer), (item.buffer, []))[1].append(item.fallback_descriptor)
+    for buffer, descriptors in arenas.values():
+        buffer.free_many(descriptors)
+
+
 # ---- matrix products through a decoded weight ----------------------------------------------
 
 def A_compB(A: Tensor, B_comp: CompressedTensor) -> Tensor:

@@ -146,6 +146,20 @@ class TensorBuffer:
         dispatch.buffer_free(self._storage, allocation.descriptor, status, self.max_free_regions)
         return status
 
+    def free_many(self, descriptors: list[torch.Tensor]) -> torch.Tensor:
+        """Return many regions with one launch, in list order (the free list ends up as after
+        one ``free`` each); the result holds one status word per descriptor."""
+        status = torch.empty(max(1, len(descriptors)), dtype=torch.int32, device=self.device)
+        if descriptors:
+            pointers = torch.empty(len(descriptors), dtype=torch.int64, pin_memory=True)
+            pointers.copy_(torch.tensor([d.data_ptr() for d in descriptors], dtype=torch.int64))
+            table = pointers.to(self.device, non_blocking=True)     # asynchronous: pinned source
+            dispatch._call("lct_buffer_free_many", self.device, self._storage.data_ptr(),
+                           table.data_ptr(), len(descriptors), status.data_ptr(),
+                           self.max_free_regions)
+            self._keep = (table, descriptors)      # until the next call: the launch reads them
+        return status
+
     def reset(self) -> None:
         """Forget every allocation; outstanding descriptors become stale (generation bump)."""
         dispatch.buffer_reset(self._storage, self.max_free_regions, self.capacity_bytes)

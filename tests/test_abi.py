@@ -85,3 +85,42 @@ def test_lane_mapping_switch_is_host_state_only():
     assert lib.lct_set_lane_mapping(1) == 0 and lib.lct_get_lane_mapping() == 1
     assert lib.lct_set_lane_mapping(2) != 0 and lib.lct_get_lane_mapping() == 1   # rejected, unchanged
     assert lib.lct_set_lane_mapping(0) == 0 and lib.lct_get_lane_mapping() == 0
+
+
+def test_byte_form_framing_on_the_host():
+    """to_bytes / from_bytes without a GPU: every field and component of a (fabricated) compressed
+    tensor survives the round trip, arena-held overflow lists become private ones."""
+    import numpy as np
+    import torch
+
+    from losslessly_compressed_tensors_b200.comp_format import Distribution, DistType, StorageLayout
+    from losslessly_compressed_tensors_b200.comp_tensor import CompressedTensor
+    from losslessly_compressed_tensors_b200.serialization import from_bytes, to_bytes
+
+    rng = np.random.default_rng(0)
+    dist = Distribution(DistType.LAPLACE, param=0.02)
+    blocks, count, tail = 2, 3, 40
+    arena = torch.from_numpy(rng.integers(0, 255, 4096, dtype=np.uint8))
+    c = CompressedTensor(
+        torch.from_numpy(rng.integers(-2**31, 2**31 - 1, blocks * 256 * 25 + 4, dtype=np.int32)),
+        blocks * 65536, torch.from_numpy(rng.integers(0, 255, blocks * 65536, dtype=np.uint8)),
+        shape=(2, 60000), layout=StorageLayout.COMPRESSED, distribution=dist,
+        stream_geometry=(65536, 256, 256, 25), center=torch.tensor([-7], dtype=torch.int32),
+        decode_table=torch.arange(1024, dtype=torch.int32),
+        fallback_count=torch.tensor([count], dtype=torch.int32),
+        fallback_used=torch.tensor([tail], dtype=torch.int32),
+        fallback_blocks=torch.arange(3 * blocks, dtype=torch.int32),
+        fallback_descriptor=torch.tensor([1024, 48, 0, 1], dtype=torch.int32),
+        fallback_buffer=arena)
+    blob = to_bytes(c)
+    back = from_bytes(blob, "cpu")
+    assert back.shape == c.shape and back.size == c.size and back.distribution == dist
+    assert back.stream_geometry == c.stream_geometry and int(back.center.item()) == -7
+    for name in ("data", "sign_mantissa", "decode_table", "fallback_blocks", "fallback_count",
+                 "fallback_used"):
+        assert torch.equal(getattr(back, name), getattr(c, name)), name
+    assert back.fallback_descriptor is None and back.buffer is None
+    assert torch.equal(back.fallback_lanes, arena[1024:1027])
+    assert torch.equal(back.fallback_starts, arena[1027:1030])
+    assert torch.equal(back.fallback_buffer, arena[1030:1070])
+    assert to_bytes(back) == blob

@@ -106,3 +106,69 @@ def test_a_forward_without_backward_gives_its_regions_back():
     del handle
     gc.collect()
     assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
+
+
+def test_many_tensor_calls_match_the_one_tensor_calls(oracle=None):
+    """compress_many / decompress_many / free_many: the results and the arena of one call per
+    tensor in list order, for mixed shapes (ragged, one-dimensional, empty)."""
+    from losslessly_compressed_tensors_b200.operations import (
+        compress, compress_many, decompress, decompress_many, free_many)
+
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    shapes = [(300, 700), (65536,), (0, 8), (17, 3, 1001), (1,)]
+    tensors = [(torch.randn(s, device="cuda", generator=gen) *
+                torch.exp(torch.randn(s, device="cuda", generator=gen) * 3)).relu().to(torch.bfloat16)
+               for s in shapes]
+    one, many = TensorBuffer(1 << 20), TensorBuffer(1 << 20)
+    singles = [compress(t, act_relu_dist, one) for t in tensors]
+    batch = compress_many(tensors, act_relu_dist, many)
+    assert _free_regions_snapshot(one) == _free_regions_snapshot(many)
+    for a, b, t in zip(singles, batch, tensors):
+        assert b.shape == tuple(t.shape) and a.memory_size() == b.memory_size()
+        for name in ("data", "sign_mantissa", "center", "decode_table", "fallback_blocks",
+                     "fallback_count", "fallback_used", "fallback_descriptor"):
+            assert torch.equal(getattr(a, name), getattr(b, name)), name
+    assert torch.equal(one.data, many.data)
+    for t, d in zip(tensors, decompress_many(batch)):
+        assert d.shape == t.shape and torch.equal(d.view(torch.int16), t.view(torch.int16))
+    free_many(batch)
+    for c in singles:
+        c.free()
+    assert _free_regions_snapshot(one) == _free_regions_snapshot(many) == [(0, 1 << 20)]
+    private = compress_many(tensors[:2], act_relu_dist, None)       # no arena: one call each
+    assert all(torch.equal(decompress(c), t) for c, t in zip(private, tensors))
+
+
+@pytest.mark.parametrize("batch", [0, 2], ids=["flush-at-exit", "groups-of-two"])
+def test_batching_cache_keeps_gradients_bit_identical(batch):
+    import contextlib
+    import gc
+    model = _model(4)
+    x = torch.randn(512, 256, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)
+                    ).to(torch.bfloat16)
+    want, want_loss = _run(model, x, contextlib.nullcontext())
+    buffer = TensorBuffer(4 << 20)
+    cache = ActivationCache(buffer, min_elements=65536, batch=batch)
+    got, got_loss = _run(model, x, compressed_saved_tensors(cache=cache))
+    assert cache.stored >= 3 and torch.equal(got_loss, want_loss)
+    for g, w in zip(got, want):
+        assert torch.equal(g.view(torch.int16), w.view(torch.int16))
+    verify_buffer(buffer)
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
+    # explicit use: stored tensors stay dense until the flush, and a load before it is free
+    a = torch.randn(300, 700, device="cuda").relu().to(torch.bfloat16)
+    cache = ActivationCache(buffer, act_relu_dist, min_elements=1, batch=0)
+    first, second, third = cache.store(a), cache.store(a * 2), cache.store(a * 3)
+    assert not first.is_compressed and first.load() is not None
+    cache.flush()
+    assert second.is_compressed and third.is_compressed and not first.is_compressed
+    assert torch.equal(second.load(), a * 2)            # decodes the whole group ...
+    assert not third.is_compressed and torch.equal(third.load(), a * 3)
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]     # ... and releases it
+    fourth = cache.store(a)
+    cache.flush()
+    del fourth
+    gc.collect()
+    assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]
+    with pytest.raises(ValueError):
+        ActivationCache(None, batch=4)
