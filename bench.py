@@ -65,7 +65,7 @@ def bench_config(world: int) -> dict:
 # two kernels on this workload.  Reads equal the algorithmic reads; part of the written bytes is
 # still in the 126 MB write-back L2 when the kernel ends, so the sum is below the algorithmic
 # 227.6 MB.
-NCU_TRAFFIC_BYTES = {"lct_encode": 184_015_360, "lct_decode": 176_469_760}
+NCU_TRAFFIC_BYTES = {"lct_encode": 184_886_016, "lct_decode": 170_119_680}
 
 
 class LaunchTrace:
@@ -874,6 +874,24 @@ def run_ours(args, rank: int, world: int, local: int):
     t.record(main)
     barrier(world)
     copy_ms = max_over_ranks(s.elapsed_time(t) / e2e_steps, world)
+    # Each direction alone: with both directions perfectly overlapped a step cannot take less
+    # than the slower of the two.
+    one_way_ms = []
+    for direction in ("h2d", "d2h"):
+        stream = s_in if direction == "h2d" else s_out
+        s, t = event(), event()
+        with torch.cuda.stream(stream):
+            stream.wait_stream(main)
+            s.record(stream)
+            for i in range(e2e_steps):
+                if direction == "h2d":
+                    dev_in[i & 1].copy_(host_x, non_blocking=True)
+                else:
+                    host_out[i & 1].copy_(dev_in[i & 1], non_blocking=True)
+            t.record(stream)
+        main.wait_stream(stream)
+        barrier(world)
+        one_way_ms.append(max_over_ranks(s.elapsed_time(t) / e2e_steps, world))
     clocks = sampler.finish() if sampler else None   # sampled across the timed regions
 
     del host_out, dev_in, dev_out, x, flush
@@ -917,8 +935,14 @@ def run_ours(args, rank: int, world: int, local: int):
                 "h2d_bytes_per_step": bf16_bytes, "d2h_bytes_per_step": bf16_bytes},
         "e2e_copies_only": {"value": world * 2 * bf16_bytes / (copy_ms * 1e-3) / 1e9, "unit": UNIT,
                             "ms_per_step": copy_ms,
-                            "note": "the same pinned H2D + D2H copies per step with no codec "
-                                    "between them: what the host link gives this loop"},
+                            "h2d_alone_gbps": world * bf16_bytes / (one_way_ms[0] * 1e-3) / 1e9,
+                            "d2h_alone_gbps": world * bf16_bytes / (one_way_ms[1] * 1e-3) / 1e9,
+                            "duplex_ceiling": world * 2 * bf16_bytes / (max(one_way_ms) * 1e-3) / 1e9,
+                            "note": "value: the same pinned H2D + D2H copies per step with no "
+                                    "codec between them (both directions started together, which "
+                                    "on some hosts is slower than the staggered copies of the real "
+                                    "loop); *_alone: each direction by itself; duplex_ceiling: "
+                                    "2 x bytes / the slower direction, which no e2e step can beat"},
         "gpu_launches": launches, "clocks": clocks,
         "encode_ms_without_arena": statistics.mean(private_ms),
         "graph_replay_ms_per_step": graph_ms, "arena": arena, "update": update,

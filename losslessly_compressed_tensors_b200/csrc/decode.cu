@@ -147,19 +147,17 @@ __device__ __forceinline__ void decode_block(const OperandView& a, const Shape& 
                                  lane.tail_bytes, g.rare_length, g.lane_mask, nothing);
   hand_over();
   group_barrier();
-  for (int h = 1; h < halves; h += 2) {
+  // One copy of the code serves both halves of the tile buffer (the second half's rows are
+  // 512 bytes further on): the loop stays within the instruction cache.
+  LaneTables tables = lane.tables;
+#pragma unroll 1
+  for (int h = 1; h < halves; ++h) {
     request(h);
-    decode_half_rows<kLaneMask, 1>(lane.reader, lane.tables, kTileRows * (h >> 1), lane.coded,
+    tables.tile_lane = lane.tables.tile_lane + (uint32_t)((h & 1) * kHalfPairs * 64);
+    decode_half_rows<kLaneMask, 0>(lane.reader, tables, (kTileRows / 2) * h, lane.coded,
                                    lane.tail_from, lane.tail_bytes, g.rare_length, g.lane_mask, rows);
     hand_over();
     group_barrier();
-    if (h + 1 < halves) {
-      request(h + 1);
-      decode_half_rows<kLaneMask, 0>(lane.reader, lane.tables, kTileRows * ((h + 1) >> 1), lane.coded,
-                                     lane.tail_from, lane.tail_bytes, g.rare_length, g.lane_mask, rows);
-      hand_over();
-      group_barrier();
-    }
   }
   rows.rest();  // the last half tile
 }

@@ -298,33 +298,35 @@ __device__ __forceinline__ void decode_pair_uniform(Reader& r, const LaneTables&
   store_shared_u16<kPair * 64>(slot[kPair & 3], entry >> 8);
 }
 
-template <int kHalf, int kIndex, typename Reader, typename Slices>
+// Pairs kPair .. kEnd - 1 of a tile, unrolled.
+template <int kPair, int kEnd, typename Reader, typename Slices>
 struct UniformPairs {
   static __device__ __forceinline__ void run(Reader& r, const LaneTables& t,
                                              const uint32_t (&slot)[4], int rare_length,
                                              Slices& slices) {
-    decode_pair_uniform<kHalf * kHalfPairs + kIndex>(r, t, slot, rare_length, slices);
-    UniformPairs<kHalf, kIndex + 1, Reader, Slices>::run(r, t, slot, rare_length, slices);
+    decode_pair_uniform<kPair>(r, t, slot, rare_length, slices);
+    UniformPairs<kPair + 1, kEnd, Reader, Slices>::run(r, t, slot, rare_length, slices);
   }
 };
-template <int kHalf, typename Reader, typename Slices>
-struct UniformPairs<kHalf, kHalfPairs, Reader, Slices> {
+template <int kEnd, typename Reader, typename Slices>
+struct UniformPairs<kEnd, kEnd, Reader, Slices> {
   static __device__ __forceinline__ void run(Reader&, const LaneTables&, const uint32_t (&)[4], int,
                                              Slices&) {}
 };
 
-// Lane phase for half a tile: row pairs kHalf * 8 .. + 7 of the tile that starts at row `step0`
-// of the block.  `coded` = number of leading steps of this lane that are in the bit stream (its
+// Lane phase for part of a tile: row pairs kHalf * kPairs .. + kPairs - 1 (half a tile by
+// default) of the tile that starts at row `step0` of the block.  `coded` = number of leading steps of this lane that are in the bit stream (its
 // overflow start or its valid length, whichever is first); steps from `tail_from` on come from
 // the raw tail.  `slices`: see NoSlices; all of its work has been issued on return.
-template <int kLaneMask, int kHalf, typename Reader, typename Slices>
+template <int kLaneMask, int kHalf, typename Reader, typename Slices, int kPairs = kHalfPairs>
 __device__ __forceinline__ void decode_half_rows(Reader& r, const LaneTables& t, int step0,
                                                  int coded, int tail_from,
                                                  const uint8_t* tail_bytes, int rare_length,
                                                  int lane_mask, Slices& slices) {
-  const int first = step0 + kHalf * (kTileRows / 2);
+  static_assert(kPairs % 2 == 0 && kPairs <= kHalfPairs, "whole refill periods, at most half a tile");
+  const int first = step0 + kHalf * 2 * kPairs;
   r.half_start();
-  if (__all_sync(kFullWarp, first + kTileRows / 2 <= coded)) {
+  if (__all_sync(kFullWarp, first + 2 * kPairs <= coded)) {
     // Every lane of the warp has all 16 rows in its stream: no per-lane conditions except the
     // rare entry that is not a full pair, found by a warp vote so that the common case is one
     // uniform branch.  The four tile addresses a lane uses (see tile_slot_xor):
@@ -332,11 +334,12 @@ __device__ __forceinline__ void decode_half_rows(Reader& r, const LaneTables& t,
                               t.tile_lane ^ tile_slot_xor<kLaneMask>(1, lane_mask),
                               t.tile_lane ^ tile_slot_xor<kLaneMask>(2, lane_mask),
                               t.tile_lane ^ tile_slot_xor<kLaneMask>(3, lane_mask)};
-    UniformPairs<kHalf, 0, Reader, Slices>::run(r, t, slot, rare_length, slices);
+    UniformPairs<kHalf * kPairs, (kHalf + 1) * kPairs, Reader, Slices>::run(r, t, slot, rare_length,
+                                                                            slices);
     return;
   }
 #pragma unroll 1
-  for (int p = kHalf * kHalfPairs; p < (kHalf + 1) * kHalfPairs; ++p) {
+  for (int p = kHalf * kPairs; p < (kHalf + 1) * kPairs; ++p) {
     const int step = step0 + 2 * p;
     uint32_t pair = 0;
     if (step + 2 <= coded) {
@@ -367,17 +370,27 @@ __device__ __forceinline__ void decode_half_rows(Reader& r, const LaneTables& t,
   slices.rest();
 }
 
-// Lane phase for one whole tile, nothing interleaved.
+// Lane phase for one whole tile, nothing interleaved.  The tile's row pairs run through ONE copy
+// of the code for kLoopPairs pairs (each part's tile rows are kLoopPairs * 64 bytes further on),
+// which keeps kernels that also hold an encoder within the instruction cache.
+#ifndef LCT_LOOP_PAIRS
+#define LCT_LOOP_PAIRS 8
+#endif
+constexpr int kLoopPairs = LCT_LOOP_PAIRS;
 template <int kLaneMask, typename Reader>
 __device__ __forceinline__ void decode_tile_rows(Reader& r, const LaneTables& t, int step0,
                                                  int coded, int tail_from,
                                                  const uint8_t* tail_bytes, int rare_length,
                                                  int lane_mask) {
   NoSlices none;
-  decode_half_rows<kLaneMask, 0>(r, t, step0, coded, tail_from, tail_bytes, rare_length, lane_mask,
-                                 none);
-  decode_half_rows<kLaneMask, 1>(r, t, step0, coded, tail_from, tail_bytes, rare_length, lane_mask,
-                                 none);
+  LaneTables part_tables = t;
+#pragma unroll 1
+  for (int part = 0; part < kTilePairs / kLoopPairs; ++part) {
+    decode_half_rows<kLaneMask, 0, Reader, NoSlices, kLoopPairs>(
+        r, part_tables, step0 + part * 2 * kLoopPairs, coded, tail_from, tail_bytes, rare_length,
+        lane_mask, none);
+    part_tables.tile_lane += (uint32_t)(kLoopPairs * 64);
+  }
 }
 
 struct NoExtraWork {

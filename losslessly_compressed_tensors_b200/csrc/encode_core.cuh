@@ -112,35 +112,37 @@ __device__ __forceinline__ bool encode_pair(uint32_t table, const uint32_t (&slo
   return true;
 }
 
-// Pairs kIndex .. 7 of half tile kHalf of one lane; after each pair one slice of the caller's
-// row-side work is issued (see NoSlices in decode_core.cuh).  A lane that has overflowed
-// (`open` false) only runs the slices.
-template <bool kCheckValid, int kHalf, int kIndex, typename WordSink, typename Slices>
+// Pairs kPair .. kEnd - 1 of a tile of one lane, unrolled; after each pair one slice of the
+// caller's row-side work is issued (see NoSlices in decode_core.cuh).  A lane that has
+// overflowed (`open` false) only runs the slices.
+template <bool kCheckValid, int kPair, int kEnd, typename WordSink, typename Slices>
 struct EncodePairs {
   static __device__ __forceinline__ void run(uint32_t table, const uint32_t (&slot)[4],
                                              const WordSink& sink, int step0, int valid,
                                              int budget_bits, int& pos, uint32_t& lo,
                                              int& extra_start, bool& open, Slices& slices) {
     if (open)
-      open = encode_pair<kCheckValid, kHalf * kHalfPairs + kIndex>(
-          table, slot, sink, step0, valid, budget_bits, pos, lo, extra_start, slices);
+      open = encode_pair<kCheckValid, kPair>(table, slot, sink, step0, valid, budget_bits, pos, lo,
+                                             extra_start, slices);
     else
-      slices.template slice<kIndex>();
-    EncodePairs<kCheckValid, kHalf, kIndex + 1, WordSink, Slices>::run(
+      slices.template slice<kPair % kHalfPairs>();
+    EncodePairs<kCheckValid, kPair + 1, kEnd, WordSink, Slices>::run(
         table, slot, sink, step0, valid, budget_bits, pos, lo, extra_start, open, slices);
   }
 };
-template <bool kCheckValid, int kHalf, typename WordSink, typename Slices>
-struct EncodePairs<kCheckValid, kHalf, kHalfPairs, WordSink, Slices> {
+template <bool kCheckValid, int kEnd, typename WordSink, typename Slices>
+struct EncodePairs<kCheckValid, kEnd, kEnd, WordSink, Slices> {
   static __device__ __forceinline__ void run(uint32_t, const uint32_t (&)[4], const WordSink&, int,
                                              int, int, int&, uint32_t&, int&, bool&, Slices&) {}
 };
 
-// Lane phase of half a tile (row pairs kHalf * 8 .. + 7 of the tile that starts at row `step0`;
+// Lane phase of part of a tile (row pairs kHalf * kPairs .. + kPairs - 1, half a tile by default,
+// of the tile that starts at row `step0`;
 // tile layout: see tile_slot_xor).  `open` turns false once the lane has overflowed.  `table`:
 // shared address of the encode table; `tile_lane`: shared address of this lane's slot in row
 // pair 0 of the warp's tile.
-template <bool kCheckValid, int kLaneMask, int kHalf, typename WordSink, typename Slices>
+template <bool kCheckValid, int kLaneMask, int kHalf, typename WordSink, typename Slices,
+          int kPairs = kHalfPairs>
 __device__ __forceinline__ void encode_half_rows(uint32_t table, uint32_t tile_lane,
                                                  const WordSink& sink, int lane_mask, int step0,
                                                  int valid, int budget_bits, int& pos,
@@ -150,9 +152,8 @@ __device__ __forceinline__ void encode_half_rows(uint32_t table, uint32_t tile_l
                             tile_lane ^ tile_slot_xor<kLaneMask>(1, lane_mask),
                             tile_lane ^ tile_slot_xor<kLaneMask>(2, lane_mask),
                             tile_lane ^ tile_slot_xor<kLaneMask>(3, lane_mask)};
-  EncodePairs<kCheckValid, kHalf, 0, WordSink, Slices>::run(table, slot, sink, step0, valid,
-                                                            budget_bits, pos, lo, extra_start, open,
-                                                            slices);
+  EncodePairs<kCheckValid, kHalf * kPairs, (kHalf + 1) * kPairs, WordSink, Slices>::run(
+      table, slot, sink, step0, valid, budget_bits, pos, lo, extra_start, open, slices);
 }
 
 // Lane phase of one whole tile, nothing interleaved.  Returns false once the lane has overflowed.
@@ -163,10 +164,11 @@ __device__ __forceinline__ bool encode_tile_rows(uint32_t table, uint32_t tile_l
                                                  uint32_t& lo, int& extra_start) {
   NoSlices none;
   bool open = true;
-  encode_half_rows<kCheckValid, kLaneMask, 0>(table, tile_lane, sink, lane_mask, step0, valid,
-                                              budget_bits, pos, lo, extra_start, open, none);
-  encode_half_rows<kCheckValid, kLaneMask, 1>(table, tile_lane, sink, lane_mask, step0, valid,
-                                              budget_bits, pos, lo, extra_start, open, none);
+#pragma unroll 1
+  for (int part = 0; part < kTilePairs / kLoopPairs; ++part)  // one copy of the code: see decode_tile_rows
+    encode_half_rows<kCheckValid, kLaneMask, 0, WordSink, NoSlices, kLoopPairs>(
+        table, tile_lane + (uint32_t)(part * kLoopPairs * 64), sink, lane_mask,
+        step0 + part * 2 * kLoopPairs, valid, budget_bits, pos, lo, extra_start, open, none);
   return open;
 }
 
