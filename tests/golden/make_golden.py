@@ -3,7 +3,7 @@
     python tests/golden/make_golden.py            # writes tables.npz, codec.json
     LCT_GOLDEN_LANE_MAPPING=linear python tests/golden/make_golden.py linear   # adds the linear-mapping cases
 
-Needs the reference checkout (``LCT_REFERENCE_ROOT``, default ``/root/reference``)
+Needs the reference checkout (its location: ``LCT_REFERENCE_ROOT``, see ``reference_shim``)
 and runs its Triton kernels under ``TRITON_INTERPRET=1`` through
 ``reference_shim``; that takes a few minutes.  The test-suite only reads the
 files written here and never imports the reference.
