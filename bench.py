@@ -562,8 +562,9 @@ def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
     """Muon's momentum step (reference: LCT/components/sparse_utils.py:88-90,133-146) on twelve
     4096 x 4096 BF16 momentum tensors in the optimizer's default codebook and one arena:
     momentum <- lerp(momentum, grad, 1 - mu), grad <- lerp(grad, momentum, mu).  `fused`: one
-    launch chain on the compressed momentum that also writes the direction over the gradient;
-    `sequence`: the reference's decompress_free / lerp_ / lerp_ / compress.  CUDA events around
+    launch chain per tensor on the compressed momentum that also writes the direction over the
+    gradient; `plan`: the same for all twelve tensors as one prepared call (what SparseMuon.step
+    does); `sequence`: the reference's decompress_free / lerp_ / lerp_ / compress.  CUDA events around
     all twelve, per tensor-step."""
     from losslessly_compressed_tensors_b200.LCTensor import LCTTensor
     from losslessly_compressed_tensors_b200.components.dist_configs import momentum_dist
@@ -580,8 +581,14 @@ def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
     w_m = torch.tensor([1 - mu], dtype=torch.float32, device="cuda")
     w_d = torch.tensor([mu], dtype=torch.float32, device="cuda")
     out, final = {}, {}
-    for label in ("fused", "sequence"):
+    from losslessly_compressed_tensors_b200.codec import pointwise
+    from losslessly_compressed_tensors_b200.kernels import dispatch
+    from losslessly_compressed_tensors_b200.update_plan import UpdatePlan
+
+    for label in ("fused", "plan", "sequence"):
         states = [LCTTensor(m, buffer, momentum_dist) for m in start]
+        plan = (UpdatePlan(states, w_m, w_d, operation=pointwise.LERP, emit=dispatch.EMIT_NESTEROV)
+                if label == "plan" else None)
         times, walls = [], []
         for it in range(warmup + steps):
             for k in range(n_tensors):        # the step's gradients (overwritten by the direction)
@@ -589,7 +596,11 @@ def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0 = time.perf_counter()
             a.record()
+            if plan is not None:
+                plan.step(work, dense_outs=work)
             for k, state in enumerate(states):
+                if plan is not None:
+                    break
                 if label == "fused":
                     assert state.lerp_(work[k], w_m, nesterov_out=work[k], nesterov_weight=w_d)
                 else:
@@ -614,10 +625,14 @@ def momentum_leg(steps: int = 10, warmup: int = 3) -> dict:
     verify_buffer(buffer)
     out["fused_algorithmic_gbps"] = (out["algorithmic_bytes_per_tensor_step"]
                                      / out["fused_ms_per_tensor_step"] / 1e6)
+    out["plan_algorithmic_gbps"] = (out["algorithmic_bytes_per_tensor_step"]
+                                    / out["plan_ms_per_tensor_step"] / 1e6)
     out["speedup"] = out["sequence_ms_per_tensor_step"] / out["fused_ms_per_tensor_step"]
+    out["plan_speedup"] = out["sequence_ms_per_tensor_step"] / out["plan_ms_per_tensor_step"]
     out["bit_exact_vs_torch_lerp"] = all(
         torch.equal(x.view(torch.int16), y.view(torch.int16))
-        for part in (0, 1) for x, y in zip(final["fused"][part], final["sequence"][part]))
+        for label in ("fused", "plan")
+        for part in (0, 1) for x, y in zip(final[label][part], final["sequence"][part]))
     out["workload"] = ("12 x 4096x4096 BF16 Muon momentum, EMPIRICAL/CLEAN zero_prob 0.02, mu 0.95, "
                        f"{warmup + steps} steps; bytes = compressed in + out, gradient in, direction out")
     return out

@@ -411,6 +411,8 @@ typedef struct lct_update_job {
   int64_t size;
   int64_t logical_numel;
   int64_t first_block;
+  void *dense_out;               /* lct_update_batch_emit only: BF16[logical_numel], 16-byte aligned,
+                                    may be `other`; ignored (may be NULL) otherwise */
 } lct_update_job;
 
 int lct_update_batch(const lct_update_job *jobs /* device */, int n_jobs, int64_t total_blocks,
@@ -420,6 +422,21 @@ int lct_update_batch(const lct_update_job *jobs /* device */, int n_jobs, int64_
                      int32_t *shifted_encode, uint8_t *extra_starts, int32_t *summaries,
                      int block_symbols, int steps, int fixed_words, int rare_length,
                      void *stream);
+
+/* lct_update_batch with the dense by-product of lct_update_emit for every job
+ * (emit = LCT_EMIT_RESULT or LCT_EMIT_NESTEROV, written to jobs[j].dense_out):
+ * the momentum step of all of Muon's parameters as one call, the Nesterov
+ * directions overwriting the gradients (LCT/components/sparse_utils.py:88-90
+ * for every parameter of :124-146 at once; the updates of different
+ * parameters are independent, so doing them before the per-parameter
+ * Newton-Schulz iterations changes no value). */
+int lct_update_batch_emit(const lct_update_job *jobs /* device */, int n_jobs,
+                          int64_t total_blocks, const float *alpha, const float *beta, int op,
+                          int alpha_is_one, int beta_is_one, const int32_t *encode_table,
+                          const int32_t *decode_table, void *arena_storage, int max_free_regions,
+                          uint8_t *samples, int32_t *shifted_encode, uint8_t *extra_starts,
+                          int32_t *summaries, int block_symbols, int steps, int fixed_words,
+                          int rare_length, int emit, void *stream);
 
 /* ---- shared overflow arena (TensorBuffer) ---------------------------------- */
 /* storage layout: int32 free_starts[R] | free_sizes[R] | free_count | lock |

@@ -186,19 +186,51 @@ class SparseMuon(_Base):
         self._momentum_weight = _scalar(1 - mu, anchor)     # lerp weights as float32, which is
         self._direction_weight = _scalar(mu, anchor)        # what torch's kernel makes of them
         self._slots = [_Slot() for _ in self.params]
+        self._plan: UpdatePlan | None = None
 
     @property
     def momentums(self):
         return [slot.value for slot in self._slots]
 
+    def _advance_all(self) -> bool:
+        """Every momentum advanced by ONE prepared call for the whole parameter list (the
+        momentum steps of different parameters are independent, so taking them out of the
+        per-parameter loop changes no value): full waves of the fused kernel instead of one
+        partial wave per tensor, six launches per step.  Needs every parameter to have a
+        contiguous BF16 gradient and a momentum in this optimizer's arena, all of one shape
+        class (one codebook, one geometry)."""
+        states = [slot.value for slot in self._slots]
+        grads = [p.grad for p in self.params]
+        if not (self.compressed and not self.first_step and len(states) > 1
+                and all(g is not None and _fusable(s, g) and s.x.buffer is self.buffer
+                        and s.x.distribution == states[0].x.distribution
+                        and s.x.codec_geometry == states[0].x.codec_geometry
+                        and s.x.logical_numel for s, g in zip(states, grads))):
+            return False
+        if (self._plan is None or len(self._plan.tensors) != len(states)
+                or any(a is not b for a, b in zip(self._plan.tensors, states))):
+            from ..codec import pointwise
+            from ..codec.geometry import geometry
+            from ..kernels import dispatch
+            if geometry(self.distribution) != states[0].x.codec_geometry:
+                return False
+            self._plan = UpdatePlan(states, self._momentum_weight, self._direction_weight,
+                                    operation=pointwise.LERP, emit=dispatch.EMIT_NESTEROV,
+                                    distribution=self.distribution)
+        self._plan.step(grads, dense_outs=grads)
+        return True
+
     @torch.no_grad()
     def step(self):
+        advanced = self._advance_all()
         for slot, p in zip(self._slots, self.params):
             grad = p.grad
             if grad is None:
                 continue
             dist = momentum_first_dist if self.first_step else self.distribution
-            if (self.compressed and _fusable(slot.value, grad)
+            if advanced:
+                update = _orthogonalised(grad, self.ns_iters)     # grad holds the direction now
+            elif (self.compressed and _fusable(slot.value, grad)
                     and slot.value.x.buffer is self.buffer
                     and slot.value.lerp_(grad, self._momentum_weight, distribution=dist,
                                          nesterov_out=grad,

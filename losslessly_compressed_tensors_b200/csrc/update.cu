@@ -313,6 +313,9 @@ __device__ __forceinline__ void update_fused_block(
 
   const float alpha = spec.alpha_is_one ? 1.0f : *spec.alpha;
   const float beta = spec.beta_is_one ? 1.0f : *spec.beta;
+  // A job table comes from the caller's device memory: an unaligned by-product pointer takes
+  // the scalar stores, a missing one is skipped.
+  const bool dense_vector_ok = (reinterpret_cast<uintptr_t>(dense_out) & 15u) == 0;
   const int valid = valid_steps_of(block, tid, g.steps, g.block_symbols, g.logical_numel, g.lane_mask);
   LaneState lane = open_lane(sh, a, g, valid);
   uint16_t* tile = sh.head->tile[warp];
@@ -371,12 +374,12 @@ __device__ __forceinline__ void update_fused_block(
           for (int i = 0; i < 8; ++i)
             if (l_at + i >= g.logical_numel) result[i >> 1] &= (i & 1) ? 0x0000FFFFu : 0xFFFF0000u;
         }
-        if (kEmit != LCT_EMIT_NONE) {
+        if (kEmit != LCT_EMIT_NONE && dense_out != nullptr) {
           uint32_t dense[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             dense[k] = kEmit == LCT_EMIT_NESTEROV ? lerp_pair(right[k], result[k], beta) : result[k];
-          if (l_at + 8 <= g.logical_numel) {
+          if (dense_vector_ok && l_at + 8 <= g.logical_numel) {
             __stcs(reinterpret_cast<uint4*>(dense_out + l_at),
                    make_uint4(dense[0], dense[1], dense[2], dense[3]));
           } else {
@@ -458,7 +461,7 @@ update_fused_kernel(OperandView a, Shape g, const uint16_t* other, bool other_ve
 }
 
 // Every block of every job of a batch: CTA b serves the job whose block range contains b.
-template <int kLaneMask>
+template <int kLaneMask, int kEmit>
 __global__ void __launch_bounds__(kThreads, 4)
 update_fused_batch_kernel(const lct_update_job* __restrict__ jobs, int n_jobs, Shape common,
                           OpSpec spec, const int32_t* __restrict__ shifted_encode,
@@ -471,11 +474,12 @@ update_fused_batch_kernel(const lct_update_job* __restrict__ jobs, int n_jobs, S
   }
   const lct_update_job& job = jobs[lo];
   const bool vector_ok = (reinterpret_cast<uintptr_t>(job.other) & 15u) == 0;
-  update_fused_block<kLaneMask, LCT_EMIT_NONE>(
+  update_fused_block<kLaneMask, kEmit>(
       view_of_update(job.a), shape_of_update(job, common), static_cast<const uint16_t*>(job.other),
       vector_ok, spec, shifted_encode + 256 * (int64_t)lo, job.side_out,
       reinterpret_cast<uint32_t*>(job.encoded_out), extra_starts + job.first_block * kLanes,
-      summaries + 4 * job.first_block, job.spill, nullptr, block - job.first_block);
+      summaries + 4 * job.first_block, job.spill, static_cast<uint16_t*>(job.dense_out),
+      block - job.first_block);
 }
 
 }  // namespace lct
@@ -661,13 +665,13 @@ int lct_update(const lct_operand* a, const void* other, const float* alpha, cons
                          rare_length, nullptr, LCT_EMIT_NONE, nullptr, nullptr, stream);
 }
 
-int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
-                     const float* alpha, const float* beta, int op, int alpha_is_one,
-                     int beta_is_one, const int32_t* encode_table, const int32_t* decode_table,
-                     void* arena_storage, int max_free_regions, uint8_t* samples,
-                     int32_t* shifted_encode, uint8_t* extra_starts, int32_t* summaries,
-                     int block_symbols, int steps, int fixed_words, int rare_length,
-                     void* stream) {
+int lct_update_batch_emit(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
+                          const float* alpha, const float* beta, int op, int alpha_is_one,
+                          int beta_is_one, const int32_t* encode_table,
+                          const int32_t* decode_table, void* arena_storage, int max_free_regions,
+                          uint8_t* samples, int32_t* shifted_encode, uint8_t* extra_starts,
+                          int32_t* summaries, int block_symbols, int steps, int fixed_words,
+                          int rare_length, int emit, void* stream) {
   if (jobs == nullptr || encode_table == nullptr || decode_table == nullptr ||
       arena_storage == nullptr || samples == nullptr || shifted_encode == nullptr ||
       extra_starts == nullptr || summaries == nullptr)
@@ -695,8 +699,17 @@ int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_block
                                      shifted_encode, st)))
     return rc;
   const size_t shared = lct::operand_shared_bytes(fixed_words) + 256 * sizeof(uint2);
-  auto kernel = g.lane_mask == 254 ? lct::update_fused_batch_kernel<254>
-                                   : lct::update_fused_batch_kernel<-1>;
+  if (emit < LCT_EMIT_NONE || emit > LCT_EMIT_NESTEROV) return LCT_E_BAD_ARGUMENT;
+  if (emit == LCT_EMIT_NESTEROV && (op != LCT_OP_LERP || beta == nullptr)) return LCT_E_BAD_ARGUMENT;
+  const bool swizzled = g.lane_mask == 254;
+  auto kernel = emit == LCT_EMIT_NESTEROV
+                    ? (swizzled ? lct::update_fused_batch_kernel<254, LCT_EMIT_NESTEROV>
+                                : lct::update_fused_batch_kernel<-1, LCT_EMIT_NESTEROV>)
+                : emit == LCT_EMIT_RESULT
+                    ? (swizzled ? lct::update_fused_batch_kernel<254, LCT_EMIT_RESULT>
+                                : lct::update_fused_batch_kernel<-1, LCT_EMIT_RESULT>)
+                    : (swizzled ? lct::update_fused_batch_kernel<254, LCT_EMIT_NONE>
+                                : lct::update_fused_batch_kernel<-1, LCT_EMIT_NONE>);
   if ((rc = lct::opt_in_shared(kernel, shared)) != 0) return rc;
   if ((rc = lct::launch_overlapped(kernel, (unsigned)total_blocks, lct::kThreads, shared, st, jobs,
                                    n_jobs, g, spec, shifted_encode, extra_starts, summaries)))
@@ -710,5 +723,17 @@ int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_block
                                    summaries, block_symbols, steps, fixed_words, st);
 }
 
+int lct_update_batch(const lct_update_job* jobs, int n_jobs, int64_t total_blocks,
+                     const float* alpha, const float* beta, int op, int alpha_is_one,
+                     int beta_is_one, const int32_t* encode_table, const int32_t* decode_table,
+                     void* arena_storage, int max_free_regions, uint8_t* samples,
+                     int32_t* shifted_encode, uint8_t* extra_starts, int32_t* summaries,
+                     int block_symbols, int steps, int fixed_words, int rare_length,
+                     void* stream) {
+  return lct_update_batch_emit(jobs, n_jobs, total_blocks, alpha, beta, op, alpha_is_one,
+                               beta_is_one, encode_table, decode_table, arena_storage,
+                               max_free_regions, samples, shifted_encode, extra_starts, summaries,
+                               block_symbols, steps, fixed_words, rare_length, LCT_EMIT_NONE, stream);
+}
 
 }  // extern "C"

@@ -50,7 +50,7 @@ class UpdateJob(ctypes.Structure):
     _fields_ = [("a", Operand), ("other", _p), ("known_values", _p), ("result_values", _p),
                 ("side_out", _p), ("encoded_out", _p), ("spill", _p), ("center", _p),
                 ("shifted_decode", _p), ("counts", _p), ("descriptor", _p), ("blocks_out", _p),
-                ("size", _i64), ("logical_numel", _i64), ("first_block", _i64)]
+                ("size", _i64), ("logical_numel", _i64), ("first_block", _i64), ("dense_out", _p)]
 
 
 class EncodeJob(ctypes.Structure):
@@ -89,6 +89,8 @@ _SIGNATURES = {
                         _i, _p, _p, _p],
     "lct_update_batch": [_p, _i, _i64, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i,
                          _i, _i, _p],
+    "lct_update_batch_emit": [_p, _i, _i64, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i,
+                              _i, _i, _i, _i, _p],
     "lct_dual_scale_add": [ctypes.POINTER(Operand), ctypes.POINTER(Operand), _p, _p, _p, _i,
                            _i64, _i64, _i, _i, _i, _i, _p],
     "lct_buffer_reset": [_p, _i, _i32, _p],

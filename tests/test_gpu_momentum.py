@@ -143,3 +143,53 @@ def test_codebook_change_and_the_cases_left_to_the_caller():
         state.lerp_(g.cuda()[:, :512], weight)
     state.free()
     verify_buffer(buffer)
+
+
+def test_prepared_plan_does_the_momentum_step_of_every_parameter_at_once(oracle):
+    """UpdatePlan with the lerp operation and the Nesterov by-product: same compressed values,
+    same directions and the same arena as one ``lerp_`` per tensor, over several steps (the
+    plan's two value sets alternate), starting from momentums in the many-zeros codebook."""
+    from losslessly_compressed_tensors_b200.codec import pointwise
+    from losslessly_compressed_tensors_b200.kernels import dispatch
+    from losslessly_compressed_tensors_b200.tensor_buffer import _free_regions_snapshot
+    from losslessly_compressed_tensors_b200.update_plan import UpdatePlan
+
+    mu = 0.95
+    shapes = [(96, 1024), (37, 1001), (300, 257)]
+    one, many = TensorBuffer(2 << 20), TensorBuffer(2 << 20)
+    start = [_values(s, 40 + i, i == 1) for i, s in enumerate(shapes)]
+    single = [LCTTensor(m.cuda(), one, momentum_first_dist) for m in start]
+    batched = [LCTTensor(m.cuda(), many, momentum_first_dist) for m in start]
+    plan = UpdatePlan(batched, _scalar(1 - mu), _scalar(mu), operation=pointwise.LERP,
+                      emit=dispatch.EMIT_NESTEROV, distribution=momentum_dist)
+    for step in range(4):
+        grads = [_values(s, 50 + 10 * step + i, step == 2) for i, s in enumerate(shapes)]
+        a, b = [g.cuda() for g in grads], [g.cuda() for g in grads]
+        for state, g in zip(single, a):
+            assert state.lerp_(g, _scalar(1 - mu), distribution=momentum_dist, nesterov_out=g,
+                               nesterov_weight=_scalar(mu))
+        plan.step(b, dense_outs=b)
+        # (the plan reserves all new regions before it releases the old ones, so the regions
+        # sit elsewhere in the arena than after one update per tensor: sizes, not offsets, agree)
+        assert (sum(size for _, size in _free_regions_snapshot(one))
+                == sum(size for _, size in _free_regions_snapshot(many))), step
+        for s1, s2, g1, g2 in zip(single, batched, a, b):
+            assert s2.x.distribution == momentum_dist
+            for name in ("data", "sign_mantissa", "center", "decode_table", "fallback_blocks",
+                         "fallback_count", "fallback_used"):
+                assert torch.equal(getattr(s1.x, name), getattr(s2.x, name)), (step, name)
+            assert torch.equal(s1.x.fallback_descriptor[1:3], s2.x.fallback_descriptor[1:3])
+            assert np.array_equal(bits_of(s1.decompress()), bits_of(s2.decompress())), step
+            assert np.array_equal(bits_of(g1), bits_of(g2)), step
+    expect = start[0].cuda()
+    for step in range(4):
+        expect.lerp_(_values(shapes[0], 50 + 10 * step, step == 2).cuda(), 1 - mu)
+    assert np.array_equal(bits_of(batched[0].decompress()), bits_of(expect))
+    with pytest.raises(ValueError):
+        plan.step([g.cuda() for g in grads])                        # by-products missing
+    with pytest.raises(ValueError):
+        UpdatePlan(batched, _scalar(0.1), operation=pointwise.LERP, emit=dispatch.EMIT_NESTEROV)
+    for state in single + batched:
+        state.free()
+    verify_buffer(one)
+    verify_buffer(many)
