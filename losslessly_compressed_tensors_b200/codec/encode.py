@@ -207,14 +207,54 @@ def encode(data: torch.Tensor, distribution: Distribution, buffer: TensorBuffer 
     )
 
 
+# Result objects of ``encode_many(..., recycle=True)`` that were given back by
+# ``operations.free_many(..., recycle=True)``, per (device, stream, arena, codebook, shape): the next
+# compression of a tensor of that kind writes into the same storage, and the operand record
+# cached with the object stays valid, so a layer that saves the same activations every step
+# pays no allocation from its second step on.
+_POOL_KEY = "_b200_pool_key"
+_pool: dict = {}
+MAX_POOLED = 4          # spare result objects kept per kind
+MAX_POOL_KINDS = 64
+
+
+def _pool_key(device, buffer, distribution, shape):
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return (index, dispatch._raw_stream(index), id(buffer), distribution.family, distribution.param,
+            distribution.mean, distribution.zero_prob, distribution.noise_level, tuple(shape))
+
+
+def give_back(items) -> None:
+    """Make the storage of released results of ``encode_many(..., recycle=True)`` available to
+    later calls.  The items must not be used afterwards."""
+    for item in items:
+        key = item.__dict__.get(_POOL_KEY)
+        if key is None:
+            continue
+        spare = _pool.pop(key, [])
+        if len(spare) < MAX_POOLED:
+            spare.append(item)
+        _pool[key] = spare                       # most recently used kind last
+    while len(_pool) > MAX_POOL_KINDS:
+        _pool.pop(next(iter(_pool)))
+
+
+def forget_pooled_storage() -> None:
+    _pool.clear()
+
+
 def encode_many(tensors: list[torch.Tensor], distribution: Distribution,
-                buffer: TensorBuffer) -> list[CompressedTensor]:
+                buffer: TensorBuffer, *, recycle: bool = False) -> list[CompressedTensor]:
     """Compress many BF16 tensors of any shapes with ONE codebook into ``buffer``'s arena by four
     launches in all (centers, encode, scans + reservations in list order, tails) instead of four
     per tensor.  Every result holds the tensors and the bytes ``encode`` gives it, and the arena
     ends up as after one ``encode`` per tensor in list order.  Nothing synchronises the host.
     No counterpart in the reference, which compresses one tensor per call
-    (``LCT/codec/encode.py:189-218``); its layers do so for every activation they save."""
+    (``LCT/codec/encode.py:189-218``); its layers do so for every activation they save.
+
+    ``recycle``: take the results' storage from objects that ``free_many(..., recycle=True)``
+    gave back (same arena, codebook and shape) instead of allocating it; for callers that own
+    their compressed tensors exclusively and release them through that call."""
     if buffer is None:
         raise ValueError("encode_many needs a TensorBuffer")
     if buffer.capacity_bytes % 4:
@@ -242,6 +282,16 @@ def encode_many(tensors: list[torch.Tensor], distribution: Distribution,
         source = data.detach().contiguous().view(-1).view(torch.int16)
         blocks = -(-source.numel() // block_symbols)
         size = blocks * block_symbols
+        key = _pool_key(device, buffer, distribution, data.shape) if recycle else None
+        spare = _pool.get(key) if recycle else None
+        if spare and spare[-1].buffer is buffer:
+            c = spare.pop()
+            jobs.append(dict(src=source, side=c.sign_mantissa, encoded=c.data, center=c.center,
+                             decode_table=c.decode_table, counts=c.__dict__["_b200_counts"],
+                             descriptor=c.fallback_descriptor, blocks=c.fallback_blocks,
+                             size=size, logical_numel=source.numel()))
+            results.append(c)
+            continue
         counts = new(4, torch.int32)
         c = CompressedTensor(
             new(blocks * lanes * fixed_words + 4, torch.int32), size, new(size, torch.uint8),
@@ -251,6 +301,9 @@ def encode_many(tensors: list[torch.Tensor], distribution: Distribution,
             center=new(1, torch.int32), decode_table=new(decode_table.numel(), torch.int32),
             shape=tuple(data.shape), layout=StorageLayout.COMPRESSED,
             stream_geometry=stream_geometry)
+        object.__setattr__(c, "_b200_counts", counts)
+        if recycle:
+            object.__setattr__(c, _POOL_KEY, key)
         jobs.append(dict(src=source, side=c.sign_mantissa, encoded=c.data, center=c.center,
                          decode_table=c.decode_table, counts=counts,
                          descriptor=c.fallback_descriptor, blocks=c.fallback_blocks, size=size,

@@ -55,7 +55,7 @@ class _Group:
         if not waiting:
             return
         results = compress_many([h._pending for h in waiting], self.cache.distribution,
-                                self.cache.buffer)
+                                self.cache.buffer, recycle=True)    # handles own them exclusively
         for handle, compressed in zip(waiting, results):
             handle._compressed, handle._pending = compressed, None
 
@@ -65,9 +65,10 @@ class _Group:
             return
         for handle, dense in zip(held, decompress_many([h._compressed for h in held])):
             handle._dense = dense
-        free_many([h._compressed for h in held])
+        compressed = [h._compressed for h in held]
         for handle in held:
             handle._compressed = None
+        free_many(compressed, recycle=True)
 
 
 class _Handle:

@@ -64,13 +64,14 @@ def decompress(data: CompressedTensor) -> Tensor:
 
 @torch.compiler.disable
 def compress_many(tensors: list[Tensor], distribution: Distribution | None = None,
-                  buffer: TensorBuffer | None = None) -> list[CompressedTensor]:
+                  buffer: TensorBuffer | None = None, *, recycle: bool = False) -> list[CompressedTensor]:
     """``compress`` of every tensor of a list with one codebook: four launches in all when a
-    ``buffer`` is given (one call per tensor without one).  Same results, same arena."""
+    ``buffer`` is given (one call per tensor without one).  Same results, same arena.
+    ``recycle``: reuse the storage of results released by ``free_many(..., recycle=True)``."""
     distribution = distribution if distribution is not None else Distribution()
     if buffer is None:
         return [compress(t, distribution, None) for t in tensors]
-    return _encode.encode_many(list(tensors), distribution, buffer)
+    return _encode.encode_many(list(tensors), distribution, buffer, recycle=recycle)
 
 
 @torch.compiler.disable
@@ -79,15 +80,18 @@ def decompress_many(items: list[CompressedTensor]) -> list[Tensor]:
     return _decode.decode_many(list(items))
 
 
-def free_many(items: list[CompressedTensor]) -> None:
+def free_many(items: list[CompressedTensor], *, recycle: bool = False) -> None:
     """``free()`` of every item: one launch per arena instead of one per tensor, the regions
-    returned in list order."""
+    returned in list order.  ``recycle``: the items' storage becomes available to later
+    ``compress_many(..., recycle=True)`` calls; the items must not be used afterwards."""
     arenas: dict = {}
     for item in items:
         if item.buffer is not None and item.fallback_descriptor is not None:
             arenas.setdefault(id(item.buffer), (item.buffer, []))[1].append(item.fallback_descriptor)
     for buffer, descriptors in arenas.values():
         buffer.free_many(descriptors)
+    if recycle:
+        _encode.give_back(items)
 
 
 # ---- matrix products through a decoded weight ----------------------------------------------

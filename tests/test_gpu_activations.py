@@ -162,9 +162,14 @@ def test_batching_cache_keeps_gradients_bit_identical(batch):
     assert not first.is_compressed and first.load() is not None
     cache.flush()
     assert second.is_compressed and third.is_compressed and not first.is_compressed
+    storage = {second._compressed.data.data_ptr(), third._compressed.data.data_ptr()}
     assert torch.equal(second.load(), a * 2)            # decodes the whole group ...
     assert not third.is_compressed and torch.equal(third.load(), a * 3)
     assert _free_regions_snapshot(buffer) == [(0, 4 << 20)]     # ... and releases it
+    fourth = cache.store(a * 5)
+    cache.flush()
+    assert fourth._compressed.data.data_ptr() in storage        # the released storage is reused
+    assert torch.equal(fourth.load(), a * 5)
     fourth = cache.store(a)
     cache.flush()
     del fourth
