@@ -171,18 +171,21 @@ scan_allocate_kernel(int32_t* summaries, int32_t* counts, int32_t* descriptor, v
   if (arena_storage != nullptr) {
     // Two metadata bytes per overflowing stream (lane, start) ahead of the tails.
     const Arena arena = arena_of(arena_storage, regions);
-    arena_allocate(arena, regions, running_bytes + 2 * running_count, descriptor, alloc_scratch);
-    if (release_descriptor != nullptr) {
-      // An in-place update: the region of the value that was just replaced goes back, after
-      // the new one has been reserved (the order of a separate allocate and free).
-      __syncthreads();
-      if (!arena_lock(arena, alloc_scratch)) {
-        if (threadIdx.x == 0) *release_status = kStatusLockTimeout;
-        return;
-      }
-      arena_free_locked(arena, regions, release_descriptor, release_status, alloc_scratch);
-      arena_unlock(arena);
+    const int32_t request = running_bytes + 2 * running_count;
+    if (release_descriptor == nullptr) {
+      arena_allocate(arena, regions, request, descriptor, alloc_scratch);
+      return;
     }
+    // An in-place update: the region of the value that was just replaced goes back after the
+    // new one has been reserved (the order of a separate allocate and free), under one lock.
+    if (!arena_lock(arena, alloc_scratch)) {
+      arena_allocate_timed_out(arena, descriptor);
+      if (threadIdx.x == 0) *release_status = kStatusLockTimeout;
+      return;
+    }
+    arena_allocate_locked(arena, regions, request, descriptor, alloc_scratch);
+    arena_free_locked(arena, regions, release_descriptor, release_status, alloc_scratch);
+    arena_unlock(arena);
   }
 }
 

@@ -218,16 +218,9 @@ __device__ __forceinline__ void arena_unlock(const Arena& a) {
 // First-fit reservation by a whole CTA (same results as the reference's
 // single-program allocator: lowest-index region that fits; exact fit removes
 // the region, otherwise it shrinks from the front).  `scratch` needs 2 ints.
-__device__ inline void arena_allocate(const Arena& a, int regions, int32_t request,
-                                      int32_t* descriptor, int* scratch) {
-  const int32_t generation = *a.generation;
-  if (!arena_lock(a, scratch)) {
-    if (threadIdx.x == 0) {
-      descriptor[0] = -1; descriptor[1] = 0; descriptor[2] = kStatusLockTimeout;
-      descriptor[3] = generation;
-    }
-    return;
-  }
+// The reservation itself, by a CTA that holds the arena lock.
+__device__ inline void arena_allocate_locked(const Arena& a, int regions, int32_t request,
+                                             int32_t* descriptor, int* scratch) {
   const int32_t size = (request + 15) / 16 * 16;
   const int count = *a.count;
   if (threadIdx.x == 0) scratch[1] = regions;
@@ -262,6 +255,24 @@ __device__ inline void arena_allocate(const Arena& a, int regions, int32_t reque
     descriptor[2] = request <= 0 ? 2 : (success ? 0 : 1);
     descriptor[3] = *a.generation;
   }
+  __syncthreads();
+}
+
+// Descriptor of a reservation that gave up waiting for the lock.
+__device__ inline void arena_allocate_timed_out(const Arena& a, int32_t* descriptor) {
+  if (threadIdx.x == 0) {
+    descriptor[0] = -1; descriptor[1] = 0; descriptor[2] = kStatusLockTimeout;
+    descriptor[3] = *a.generation;
+  }
+}
+
+__device__ inline void arena_allocate(const Arena& a, int regions, int32_t request,
+                                      int32_t* descriptor, int* scratch) {
+  if (!arena_lock(a, scratch)) {
+    arena_allocate_timed_out(a, descriptor);
+    return;
+  }
+  arena_allocate_locked(a, regions, request, descriptor, scratch);
   arena_unlock(a);
 }
 
