@@ -155,9 +155,12 @@ int lct_compact_tails(const void *src, uint8_t *lanes, uint8_t *starts, uint8_t 
  * image, one per GPU that loads the library, held until the process exits.
  * The caller passes only the source, the outputs side[size] and
  * encoded[streams*fixed_words + 4], and counts[4], which receives the number of
- * overflow streams and their tail bytes (counts[2..3] = 0); counts[0] == 0
- * means side + encoded are the complete compressed form, otherwise finish with
- * the regular lct_encode / lct_compact_tails sequence.
+ * overflow streams and their tail bytes (counts[2..3] = 0).  The result is
+ * complete only when counts[0] == 0: then side + encoded are the whole
+ * compressed form.  With overflow streams this entry point yields the totals
+ * only (the per-lane overflow starts stay in the built-in array, which the ABI
+ * does not expose), and the tensor must be encoded again through lct_encode +
+ * lct_scan_allocate + lct_compact_tails with caller-provided scratch.
  *   - Limit: at most 1024 codec blocks (64 Mi elements in the 65536-element
  *     layouts, 32 Mi in the 32768-element ones); a larger tensor is rejected
  *     with LCT_E_SCRATCH_LIMIT before anything is launched.
