@@ -3,12 +3,16 @@
     python tests/reference_runner.py bits    --out f.npz [--sizes RxC,RxC --steps S]
     python tests/reference_runner.py bench   --out f.json [--iters N] [--autotune]
     python tests/reference_runner.py dropin  --out f.json
+    python tests/reference_runner.py interchange --out f.json
 
 ``bits`` and ``bench`` import the UNMODIFIED reference (a copy of its checkout under
 ``baseline/_ref``, made by ``__graft_entry__.build()`` where the checkout exists) with its Triton
 kernels compiled for the GPU at hand: the configuration-4 recurrence through the reference's own
 fused path, dumped step by step for the parity test, and the reference's kernels timed on
 configurations 2 and 4 as the bar this library's kernels are measured against.
+
+``interchange`` loads both codecs side by side and lets each decode what the other compressed
+(through the reference's generic kernels and through its A100 decoder).
 
 ``dropin`` does the opposite: it installs THIS library under the name ``LCT``
 (``compat.install_as_lct``), lets the reference's callers - ``examples/benchmarks`` and
@@ -296,9 +300,109 @@ def mode_dropin(args) -> None:
         json.dump(report, handle)
 
 
+def mode_interchange(args) -> None:
+    """Both codecs in one process (the reference as ``LCT``, this library under its own name):
+    what one compresses the other must decode, for private and arena-held overflow, all layouts,
+    ragged sizes - through the reference's generic kernels and through its A100 decoder, whose
+    docstring promises the same payload (``LCT/kernels/a100/decode.py:13-15``)."""
+    import dataclasses
+
+    import torch
+
+    _load_reference(autotune=False)
+    import LCT.kernels.backends as ref_backends
+    import LCT.kernels.dispatch as ref_dispatch
+    from LCT import comp_format as rf, operations as ref_ops
+    from LCT.comp_tensor import CompressedTensor as RefTensor
+    from LCT.tensor_buffer import TensorBuffer as RefBuffer
+
+    sys.path.insert(0, ROOT)
+    from losslessly_compressed_tensors_b200 import comp_format as of, operations as our_ops
+    from losslessly_compressed_tensors_b200.comp_tensor import CompressedTensor as OurTensor
+    from losslessly_compressed_tensors_b200.tensor_buffer import TensorBuffer as OurBuffer
+
+    def translate(c, target_cls, fmt):
+        """The same fields under the other library's types (tensors are shared, not copied)."""
+        values = {}
+        for f in dataclasses.fields(target_cls):
+            v = getattr(c, f.name)
+            if f.name == "distribution":
+                v = fmt.Distribution(fmt.DistType[v.family.name], param=v.param, mean=v.mean,
+                                     zero_prob=v.zero_prob, noise_level=fmt.NoiseLevel[v.noise_level.name])
+            elif f.name == "layout":
+                v = fmt.StorageLayout[v.name]
+            elif f.name == "buffer":
+                v = None                     # only free() uses it
+            values[f.name] = v
+        return target_cls(**values)
+
+    g = torch.Generator().manual_seed(11)
+
+    def tensor(shape, kind):
+        x = torch.randn(shape, generator=g)
+        if kind == "heavy":                  # a wide spread of exponents: overflow lanes
+            x = x * torch.exp(torch.randn(shape, generator=g) * 4)
+        elif kind == "relu":
+            x = x.relu()
+        else:
+            x = x * 0.02
+        return x.to(torch.bfloat16).cuda()
+
+    cases = [("laplace-clean", dict(family="LAPLACE", param=0.02), "plain", (1024, 1024)),
+             ("laplace-clean-overflow", dict(family="LAPLACE", param=0.02), "heavy", (1000, 777)),
+             ("gaussian-clean", dict(family="GAUSSIAN"), "heavy", (300, 700)),
+             ("gaussian-medium", dict(family="GAUSSIAN", noise_level="MEDIUM"), "plain", (2048, 512)),
+             ("sparse-relu", dict(family="LAPLACE", zero_prob=0.5, noise_level="SPARSE"), "relu", (512, 4096)),
+             ("empirical-high", dict(family="EMPIRICAL", noise_level="HIGH"), "heavy", (65537,))]
+
+    def dist_of(fmt, spec):
+        return fmt.Distribution(fmt.DistType[spec["family"]], param=spec.get("param", 1.0),
+                                zero_prob=spec.get("zero_prob", 0.0),
+                                noise_level=fmt.NoiseLevel[spec.get("noise_level", "CLEAN")])
+
+    report = {"cases": {}}
+    stock = ref_dispatch.backend_for
+    for backend in ("generic", "a100"):
+        if backend == "a100":
+            try:
+                a100 = ref_backends._a100_backend()
+            except Exception as error:          # the backend does not build here: say so, go on
+                report["a100"] = f"unavailable: {type(error).__name__}: {error}"[:300]
+                break
+            ref_dispatch.backend_for = lambda device: a100
+        try:
+            for name, spec, kind, shape in cases:
+                x = tensor(shape, kind)
+                for buffered in (False, True):
+                    ours = our_ops.compress(x, dist_of(of, spec), OurBuffer(4 << 20) if buffered else None)
+                    theirs = ref_ops.compress(x, dist_of(rf, spec),
+                                              RefBuffer(4 << 20, device="cuda") if buffered else None)
+                    by_reference = ref_ops.decompress(translate(ours, RefTensor, rf))
+                    by_this = our_ops.decompress(translate(theirs, OurTensor, of))
+                    key = f"{backend}/{name}/{'arena' if buffered else 'private'}"
+                    report["cases"][key] = {
+                        "overflow_streams": int(ours.fallback_count.item()),
+                        "reference_decodes_ours": bool(torch.equal(by_reference.view(torch.int16),
+                                                                   x.view(torch.int16))),
+                        "this_decodes_reference": bool(torch.equal(by_this.view(torch.int16),
+                                                                   x.view(torch.int16))),
+                        "same_memory_size": int(ours.memory_size()) == int(theirs.memory_size()),
+                    }
+        except Exception as error:
+            if backend == "generic":
+                raise
+            report["a100"] = f"unavailable: {type(error).__name__}: {error}"[:300]
+        finally:
+            ref_dispatch.backend_for = stock
+    report.setdefault("a100", "ran")
+    torch.cuda.synchronize()
+    with open(args.out, "w") as handle:
+        json.dump(report, handle)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("mode", choices=("bits", "bench", "dropin"))
+    parser.add_argument("mode", choices=("bits", "bench", "dropin", "interchange"))
     parser.add_argument("--out", required=True)
     parser.add_argument("--sizes", default="1024x1024,4096x4096")
     parser.add_argument("--steps", type=int, default=20)
@@ -309,7 +413,8 @@ def main() -> None:
     if not available():
         raise SystemExit("baseline/_ref is missing: run __graft_entry__.build() where the "
                          "reference checkout exists")
-    {"bits": mode_bits, "bench": mode_bench, "dropin": mode_dropin}[args.mode](args)
+    {"bits": mode_bits, "bench": mode_bench, "dropin": mode_dropin,
+     "interchange": mode_interchange}[args.mode](args)
 
 
 if __name__ == "__main__":

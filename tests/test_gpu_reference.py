@@ -85,3 +85,24 @@ def test_reference_callers_run_unmodified_on_this_library(tmp_path):
     assert report["benchmark_lct_cases"] == 5
     assert report["benchmark_pointwise_checks"] == 10
     assert "identical" in report["rms_linear"]
+
+
+def test_each_codec_decodes_what_the_other_compressed(tmp_path):
+    """Payload interchange on the GPU: this library's compressed tensors decode bit-exactly
+    through the reference's kernels (its generic decoder and, where it builds, its A100 decoder,
+    ``LCT/kernels/a100/decode.py:13-15``: "payloads are interchangeable") and the reference's
+    through this library's, private and arena-held overflow, every layout, ragged sizes; and
+    both report the same ``memory_size()``."""
+    out = tmp_path / "interchange.json"
+    _run("interchange", out)
+    with open(out) as handle:
+        report = json.load(handle)
+    generic = {k: v for k, v in report["cases"].items() if k.startswith("generic/")}
+    assert len(generic) == 12
+    assert any(v["overflow_streams"] > 0 for v in generic.values())
+    for key, result in report["cases"].items():
+        assert result["reference_decodes_ours"], key
+        assert result["this_decodes_reference"], key
+        assert result["same_memory_size"], key
+    print("A100 decoder of the reference:", report["a100"],
+          sum(k.startswith("a100/") for k in report["cases"]), "cases")
