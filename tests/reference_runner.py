@@ -295,6 +295,55 @@ def mode_dropin(args) -> None:
     for dense_value, compressed_value in zip(grads[False], grads[True]):
         assert torch.equal(dense_value, compressed_value), "RMSLinear: compressed activation changed a result"
     report["rms_linear"] = "forward and backward identical with the saved activation compressed"
+
+    # 4. The other activation layers of the reference, same criterion (outputs and every gradient
+    #    bit-identical with the saved activations compressed into the shared arena), and the arena
+    #    empty afterwards: Relu2Linear (layers.py:182-227), the shared-input Q/K/V projection
+    #    (rms_norm_qkv, :75-140), RMSNormFunction (:143-179), FFN and RMSFFN (mlps.py:41-150), whose
+    #    saved tensors are LCTTensor wrappers.
+    from LCT.components.layers import Relu2Linear, RMSNormFunction, rms_norm_qkv
+    from LCT.components.mlps import FFN, RMSFFN
+    from LCT.tensor_buffer import _free_regions_snapshot
+
+    def bf16(*shape, scale=1.0, grad=True):
+        return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16).requires_grad_(grad)
+
+    def same_with_and_without(name, leaves, run):
+        results = {}
+        for compressed in (False, True):
+            for t in leaves:
+                t.grad = None
+            outputs = run(compressed)
+            outputs = outputs if isinstance(outputs, tuple) else (outputs,)
+            sum(o.float().square().mean() for o in outputs).backward()
+            results[compressed] = [t.grad.clone() for t in leaves] + [o.detach().clone() for o in outputs]
+        for dense_value, compressed_value in zip(results[False], results[True]):
+            assert torch.equal(dense_value, compressed_value), f"{name}: compressed activation changed a result"
+        assert _free_regions_snapshot(buffer) == free_before, f"{name}: arena regions not returned"
+        report[name] = "forward and backward identical with the saved activations compressed"
+
+    for c in (a_comp, b_comp):
+        c.free()
+    free_before = _free_regions_snapshot(buffer)
+    z, w2, b2 = bf16(512, 1024), bf16(256, 1024, scale=0.02), torch.zeros(256, device="cuda", requires_grad=True)
+    same_with_and_without("relu2_linear", (z, w2, b2),
+                          lambda c: Relu2Linear.apply(z, w2, b2, buffer, c, None, 1))
+    xq = bf16(512, 256)
+    gain_q = torch.ones(256, device="cuda", requires_grad=True)
+    projections = [torch.nn.Linear(256, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    leaves = [xq, gain_q] + [p for m in projections for p in (m.weight, m.bias)]
+    same_with_and_without("rms_norm_qkv", leaves,
+                          lambda c: rms_norm_qkv(xq, gain_q, *projections, buffer=buffer, compressed=c,
+                                                 min_elements=1))
+    xn, gains = bf16(512, 256), torch.ones(256, device="cuda", requires_grad=True)
+    same_with_and_without("rms_norm_function", (xn, gains),
+                          lambda c: RMSNormFunction.apply(xn, gains, buffer, c, None, 1))
+    xf, w1f, w2f = bf16(512, 256), bf16(1024, 256, scale=0.05), bf16(256, 1024, scale=0.05)
+    same_with_and_without("ffn", (xf, w1f, w2f), lambda c: FFN.apply(xf, w1f, w2f, buffer, c))
+    if hasattr(torch.ops.aten, "_fused_rms_norm"):      # the operator RMSFFN is written on
+        same_with_and_without("rms_ffn", (xf, w1f, w2f), lambda c: RMSFFN.apply(xf, w1f, w2f, buffer, c))
+    else:
+        report["rms_ffn"] = "not run: this PyTorch has no aten._fused_rms_norm"
     torch.cuda.synchronize()
     with open(args.out, "w") as handle:
         json.dump(report, handle)

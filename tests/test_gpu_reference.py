@@ -77,7 +77,8 @@ def test_config4_recurrence_matches_the_compiled_reference(oracle, tmp_path):
 def test_reference_callers_run_unmodified_on_this_library(tmp_path):
     """``examples/benchmarks/benchmark_lct.py`` (its ``run_case``: round trip and ratio ceiling
     for all five cases), ``benchmark_pointwise.py`` (its ``check_result`` on every fused operation
-    with dense and compressed output) and ``LCT/components/layers.py`` (``RMSLinear`` forward and
+    with dense and compressed output), ``LCT/components/layers.py`` and ``mlps.py`` (``Relu2Linear``,
+    the shared-input Q/K/V projection, ``RMSNormFunction``, ``FFN``, ``RMSFFN``; ``RMSLinear`` forward and
     backward with the saved activation compressed) on ``compat.install_as_lct()``."""
     out = tmp_path / "dropin.json"
     _run("dropin", out)
@@ -85,6 +86,9 @@ def test_reference_callers_run_unmodified_on_this_library(tmp_path):
     assert report["benchmark_lct_cases"] == 5
     assert report["benchmark_pointwise_checks"] == 10
     assert "identical" in report["rms_linear"]
+    for layer in ("relu2_linear", "rms_norm_qkv", "rms_norm_function", "ffn"):
+        assert "identical" in report[layer], layer
+    assert "identical" in report["rms_ffn"] or report["rms_ffn"].startswith("not run"), report["rms_ffn"]
 
 
 def test_each_codec_decodes_what_the_other_compressed(tmp_path):
