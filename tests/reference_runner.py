@@ -344,6 +344,24 @@ def mode_dropin(args) -> None:
         same_with_and_without("rms_ffn", (xf, w1f, w2f), lambda c: RMSFFN.apply(xf, w1f, w2f, buffer, c))
     else:
         report["rms_ffn"] = "not run: this PyTorch has no aten._fused_rms_norm"
+    # FlashAttention (layers.py:253-305): Q, K, V and the attention output cached compressed
+    # (BHTD views of contiguous BTHD storage, as its trainer supplies them).
+    from LCT.components.layers import FlashAttention
+
+    batch, length, heads, head_dim = 2, 256, 4, 64
+    qkv = [(torch.randn(batch, length, heads, head_dim, device="cuda") * 0.5).to(torch.bfloat16)
+           .requires_grad_() for _ in range(3)]
+    w_o = bf16(128, heads * head_dim, scale=0.05)
+    b_o = torch.zeros(128, device="cuda", requires_grad=True)
+    try:
+        same_with_and_without(
+            "flash_attention", (*qkv, w_o, b_o),
+            lambda c: FlashAttention.apply(*(t.transpose(1, 2) for t in qkv), w_o, b_o, buffer, c,
+                                           None, 1))
+    except (RuntimeError, NotImplementedError) as error:
+        if "flash" not in str(error).lower():
+            raise
+        report["flash_attention"] = f"not run: {error}"[:200]   # no flash kernel for this GPU in this PyTorch
     torch.cuda.synchronize()
     with open(args.out, "w") as handle:
         json.dump(report, handle)

@@ -88,7 +88,9 @@ def test_reference_callers_run_unmodified_on_this_library(tmp_path):
     assert "identical" in report["rms_linear"]
     for layer in ("relu2_linear", "rms_norm_qkv", "rms_norm_function", "ffn"):
         assert "identical" in report[layer], layer
-    assert "identical" in report["rms_ffn"] or report["rms_ffn"].startswith("not run"), report["rms_ffn"]
+    for optional in ("rms_ffn", "flash_attention"):     # need operators of the installed PyTorch
+        assert "identical" in report[optional] or report[optional].startswith("not run"), report[optional]
+    print({k: v[:40] for k, v in report.items() if isinstance(v, str)})
 
 
 def test_each_codec_decodes_what_the_other_compressed(tmp_path):
