@@ -362,6 +362,71 @@ def mode_dropin(args) -> None:
         if "flash" not in str(error).lower():
             raise
         report["flash_attention"] = f"not run: {error}"[:200]   # no flash kernel for this GPU in this PyTorch
+    # 5. The reference's own optimizers (LCT/components/sparse_utils.py, loaded from its file under
+    #    another module name: this library has a module of that name too), unmodified, with their
+    #    state compressed by this library: Muon and AdamW must follow their dense-state
+    #    trajectories bit for bit (the codec is lossless), SGDM must run its fused updates.
+    import importlib.util
+
+    source_path = os.path.join(REFERENCE, "LCT", "components", "sparse_utils.py")
+    with open(source_path) as handle:
+        source = "from __future__ import annotations\n" + handle.read()
+    spec = importlib.util.spec_from_loader("reference_sparse_utils", loader=None)
+    reference_optimizers = importlib.util.module_from_spec(spec)
+    reference_optimizers.__file__ = source_path
+    exec(compile(source, source_path, "exec"), reference_optimizers.__dict__)
+    from LCT.LCTensor import LCTTensor as OurWrapper
+
+    shapes = [(256, 384), (384, 256), (128, 128)]
+
+    def fresh(seed):
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        return [(torch.randn(shape, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+                for shape in shapes]
+
+    def gradients(step):
+        gen = torch.Generator(device="cuda").manual_seed(100 + step)
+        return [(torch.randn(shape, device="cuda", generator=gen) * 0.01).to(torch.bfloat16)
+                for shape in shapes]
+
+    def make(kind, params, compressed):
+        if kind == "muon":
+            return reference_optimizers.SparseMuon(params, lr=0.02, weight_decay=0.01, buffer=buffer,
+                                                   compressed=compressed, ns_iters=3)
+        return reference_optimizers.SparseAdamW([dict(params=params, lr=1e-2)], weight_decay=0.1,
+                                                compressed=compressed, buffer=buffer)
+
+    for kind in ("muon", "adamw"):
+        with_state, dense_state = fresh(7), fresh(7)
+        opt_a, opt_b = make(kind, with_state, True), make(kind, dense_state, False)
+        for step in range(3):
+            for pa, pb, grad in zip(with_state, dense_state, gradients(step)):
+                pa.grad, pb.grad = grad.clone(), grad.clone()
+            opt_a.step()
+            opt_b.step()
+            for pa, pb in zip(with_state, dense_state):
+                assert torch.equal(pa, pb), f"{kind}: parameters differ at step {step}"
+        if kind == "muon":
+            states = list(zip(opt_a.momentums, opt_b.momentums))
+        else:
+            states = [(opt_a.state[pa][key], opt_b.state[pb][key])
+                      for pa, pb in zip(with_state, dense_state) for key in ("exp_avg", "exp_avg_sq")]
+        for compressed_state, dense_value in states:
+            assert isinstance(compressed_state, OurWrapper), f"{kind}: state is not compressed"
+            assert torch.equal(compressed_state.decompress(), dense_value), f"{kind}: state differs"
+            compressed_state.free()
+        report["reference_" + kind] = "compressed-state trajectory identical to the dense-state one"
+    params = fresh(8)
+    sgdm = reference_optimizers.SparseSGDM(params, lr=0.1, momentum=0.9, buffer=buffer, compressed=True)
+    for step in range(3):
+        for p, grad in zip(params, gradients(step)):
+            p.grad = grad
+        sgdm.step()
+    assert all(torch.isfinite(p.float()).all() for p in params)
+    for state in sgdm.momentums:
+        state.free()
+    assert _free_regions_snapshot(buffer) == free_before, "optimizers: arena regions not returned"
+    report["reference_sgdm"] = "three fused steps"
     torch.cuda.synchronize()
     with open(args.out, "w") as handle:
         json.dump(report, handle)

@@ -78,7 +78,9 @@ def test_reference_callers_run_unmodified_on_this_library(tmp_path):
     """``examples/benchmarks/benchmark_lct.py`` (its ``run_case``: round trip and ratio ceiling
     for all five cases), ``benchmark_pointwise.py`` (its ``check_result`` on every fused operation
     with dense and compressed output), ``LCT/components/layers.py`` and ``mlps.py`` (``Relu2Linear``,
-    the shared-input Q/K/V projection, ``RMSNormFunction``, ``FFN``, ``RMSFFN``; ``RMSLinear`` forward and
+    the shared-input Q/K/V projection, ``RMSNormFunction``, ``FlashAttention``, ``FFN``, ``RMSFFN``, and the
+    reference's own optimizers ``SparseMuon`` / ``SparseAdamW`` / ``SparseSGDM`` with their state compressed
+    by this library; ``RMSLinear`` forward and
     backward with the saved activation compressed) on ``compat.install_as_lct()``."""
     out = tmp_path / "dropin.json"
     _run("dropin", out)
@@ -90,6 +92,8 @@ def test_reference_callers_run_unmodified_on_this_library(tmp_path):
         assert "identical" in report[layer], layer
     for optional in ("rms_ffn", "flash_attention"):     # need operators of the installed PyTorch
         assert "identical" in report[optional] or report[optional].startswith("not run"), report[optional]
+    assert "identical" in report["reference_muon"] and "identical" in report["reference_adamw"]
+    assert report["reference_sgdm"] == "three fused steps"
     print({k: v[:40] for k, v in report.items() if isinstance(v, str)})
 
 
