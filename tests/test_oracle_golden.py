@@ -165,3 +165,33 @@ def test_float_rounding_helpers(oracle):
     finite = np.isfinite(want)
     assert np.array_equal(got[finite], want_bits[finite])
     assert np.array_equal(got[~finite] & 0x7FFF, np.full((~finite).sum(), 0x7F80, np.uint16))
+
+
+def test_optimizer_operations_known_answers(oracle):
+    """LERP and EMA_SQUARE of the oracle (PyTorch's float32 formulas, pinned against torch itself
+    on the GPU in tests/test_gpu_momentum.py) on values whose results are exact or known: both
+    branches of the lerp formula, its end points, and the two roundings of the squared average."""
+    def bf16(*values):
+        f = np.asarray(values, np.float32)
+        return (f.view(np.uint32) >> 16).astype(np.uint16)
+
+    def floats(bits):
+        return (np.asarray(bits, np.uint32) << 16).view(np.float32)
+
+    start, end = bf16(1.0, -2.0, 0.5, 3.0, 0.0), bf16(3.0, 6.0, 0.5, -1.0, 8.0)
+    assert np.array_equal(floats(oracle.lerp_dense(start, end, 0.25)), [1.5, 0.0, 0.5, 2.0, 2.0])   # w < 0.5
+    assert np.array_equal(floats(oracle.lerp_dense(start, end, 0.75)), [2.5, 4.0, 0.5, 0.0, 6.0])   # w >= 0.5
+    assert np.array_equal(oracle.lerp_dense(start, end, 0.0), start)
+    assert np.array_equal(oracle.lerp_dense(start, end, 1.0), end)          # exact only on the second branch
+    # 1 + 2^-9 is not a BF16 value: round to nearest even, from either branch
+    assert np.array_equal(floats(oracle.lerp_dense(bf16(1.0), bf16(1.0 + 2.0 ** -7), 0.25)), [1.0])
+    assert np.array_equal(floats(oracle.lerp_dense(bf16(1.0), bf16(1.0 + 2.0 ** -7), 0.75)), [1.0078125])
+    # the same two operations on a compressed operand
+    dist = dist_of(dict(family="GAUSSIAN"))
+    values = np.tile(bf16(1.0, -2.0, 0.5, 3.0), 64)
+    c = oracle_compress(oracle, values.view(np.int16), dist)
+    other = np.tile(bf16(3.0, 6.0, 0.5, -1.0), 64)
+    got = oracle.pointwise(c, other, oracle.OP_LERP, 0.25, alpha_is_one=False)
+    assert np.array_equal(floats(got[:4]), [1.5, 0.0, 0.5, 2.0])
+    got = oracle.pointwise(c, other, oracle.OP_EMA_SQUARE, 0.5, 0.25, alpha_is_one=False, beta_is_one=False)
+    assert np.array_equal(floats(got[:4]), [0.5 + 2.25, -1.0 + 9.0, 0.25 + 0.0625, 1.5 + 0.25])
