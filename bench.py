@@ -237,7 +237,7 @@ def run_reference(args, rank: int):
         cpu_leg(bits, cores, 0.0, 1)
     value, steps, used, ms = cpu_leg(bits, cores, 1e9, args.steps)
     sample = f"full workload ({ROWS}x{COLS} BF16), {steps} step(s) of compress+decompress"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
@@ -245,7 +245,7 @@ def run_reference(args, rank: int):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })
 
 
 def triton_reference_leg(timeout_s: int = 420) -> dict:
@@ -974,7 +974,7 @@ def run_ours(args, rank: int, world: int, local: int):
     # GPU, and the multi-GPU weight-set step.
     line["triton_reference"] = triton_reference
     line["sharded"] = sharded
-    print(json.dumps(line))
+    emit(line)
 
 
 def full_size_oracle_check(host_x: torch.Tensor, c, dist_cfg) -> bool:
@@ -994,7 +994,31 @@ def full_size_oracle_check(host_x: torch.Tensor, c, dist_cfg) -> bool:
     return bool(same)
 
 
+_RESULT_FD = None
+
+
+def _keep_stdout_for_the_result() -> None:
+    """The contract is ONE JSON line on standard output.  Libraries print there too (NCCL its
+    version line when asked to), so from here on file descriptor 1 is standard error's, and the
+    result line goes to a private copy of the original."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
+
+
 def main():
+    _keep_stdout_for_the_result()
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
